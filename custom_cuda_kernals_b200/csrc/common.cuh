@@ -1,0 +1,148 @@
+// Shared device helpers for the bandwidth-bound kernels: storage-type traits,
+// 16-byte streaming loads/stores, warp and CTA reductions.
+//
+// Covers the role of the reference's csrc/includes/common.cuh:28-153 (dtype
+// tags, to_float/from_float, warp/block reductions) with a different design:
+// every global access is a 128-bit vector, reductions use xor-shuffles so all
+// lanes end with the result, and loads that are read once bypass L1.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cck {
+
+// dtype tags of the C ABI (values fixed by the reference: src/kernels/dtype.rs:6-12).
+enum : int32_t { kF32 = 0, kF16 = 1, kBF16 = 2, kF8E4M3 = 3, kF8E5M2 = 4 };
+
+constexpr int kNumSMs = 148;  // B200
+
+// ---------------------------------------------------------------- 16-byte vectors
+struct alignas(16) Vec16 {
+    uint32_t w[4];
+};
+
+// Read-once data: non-coherent path, do not keep in L1.
+__device__ __forceinline__ Vec16 ld_stream(const void* p) {
+    Vec16 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+                 : "l"(p));
+    return v;
+}
+// Re-used data (weights, tables): default caching.
+__device__ __forceinline__ Vec16 ld_cached(const void* p) {
+    return *reinterpret_cast<const Vec16*>(p);
+}
+// Write-once data: streaming store (evict-first).
+__device__ __forceinline__ void st_stream(void* p, const Vec16& v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3])
+                 : "memory");
+}
+__device__ __forceinline__ void st_stream8(void* p, uint32_t a, uint32_t b) {
+    asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" :: "l"(p), "r"(a), "r"(b) : "memory");
+}
+
+// ---------------------------------------------------------------- storage traits
+template <typename T> struct Store;
+
+template <> struct Store<float> {
+    static constexpr int kPerVec = 4;
+    __device__ static __forceinline__ float get(const Vec16& v, int i) { return __uint_as_float(v.w[i]); }
+    __device__ static __forceinline__ void put(Vec16& v, int i, float f) { v.w[i] = __float_as_uint(f); }
+    __device__ static __forceinline__ float load1(const float* p) { return *p; }
+    __device__ static __forceinline__ void store1(float* p, float f) { *p = f; }
+    // value after one rounding to the storage type
+    __device__ static __forceinline__ float round(float f) { return f; }
+};
+
+template <> struct Store<__nv_bfloat16> {
+    static constexpr int kPerVec = 8;
+    __device__ static __forceinline__ float get(const Vec16& v, int i) {
+        const uint32_t w = v.w[i >> 1];
+        return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
+    }
+    // put() is only used through put2 below
+    __device__ static __forceinline__ float load1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    __device__ static __forceinline__ void store1(__nv_bfloat16* p, float f) { *p = __float2bfloat16_rn(f); }
+    __device__ static __forceinline__ float round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+    __device__ static __forceinline__ uint32_t pack2(float lo, float hi) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+};
+
+template <> struct Store<__half> {
+    static constexpr int kPerVec = 8;
+    __device__ static __forceinline__ float get(const Vec16& v, int i) {
+        const uint32_t w = v.w[i >> 1];
+        const __half_raw r{static_cast<unsigned short>((i & 1) ? (w >> 16) : (w & 0xffffu))};
+        return __half2float(__half(r));
+    }
+    __device__ static __forceinline__ float load1(const __half* p) { return __half2float(*p); }
+    __device__ static __forceinline__ void store1(__half* p, float f) { *p = __float2half_rn(f); }
+    __device__ static __forceinline__ float round(float f) { return __half2float(__float2half_rn(f)); }
+    __device__ static __forceinline__ uint32_t pack2(float lo, float hi) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+};
+
+// Unpack a 16-byte vector into floats / pack floats (one rounding) into a vector.
+template <typename T>
+__device__ __forceinline__ void unpack(const Vec16& v, float (&f)[Store<T>::kPerVec]) {
+#pragma unroll
+    for (int i = 0; i < Store<T>::kPerVec; ++i) f[i] = Store<T>::get(v, i);
+}
+template <typename T>
+__device__ __forceinline__ Vec16 pack(const float (&f)[Store<T>::kPerVec]) {
+    Vec16 v;
+    if constexpr (Store<T>::kPerVec == 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v.w[i] = __float_as_uint(f[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v.w[i] = Store<T>::pack2(f[2 * i], f[2 * i + 1]);
+    }
+    return v;
+}
+
+// ---------------------------------------------------------------- reductions
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// CTA-wide reductions over THREADS threads (multiple of 32, <= 1024).  `slots`
+// is a shared array of >= THREADS/32 floats.  All threads get the result; the
+// trailing barrier makes `slots` reusable right away.
+template <int THREADS, bool IS_MAX>
+__device__ __forceinline__ float cta_reduce(float v, float* slots) {
+    constexpr int kWarps = THREADS / 32;
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    if constexpr (kWarps == 1) return v;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) slots[warp] = v;
+    __syncthreads();
+    float r = IS_MAX ? -INFINITY : 0.0f;
+#pragma unroll
+    for (int i = 0; i < kWarps; ++i) r = IS_MAX ? fmaxf(r, slots[i]) : r + slots[i];
+    __syncthreads();
+    return r;
+}
+
+__host__ __device__ constexpr int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace cck

@@ -1,0 +1,278 @@
+// Persistent, warp-specialised tcgen05 GEMM mainloop for sm_100a, shared by
+// matmul_add_bias (bf16/fp16/fp8) and the fused linear + cross-entropy kernel.
+//
+//   D[128 x 256] (fp32, in TMEM) = A[128 x K] * B[256 x K]^T,  A and B both K-major.
+//
+// One CTA per SM, 192 threads:
+//   warp 0  (one lane)  TMA producer: 128-byte-wide K slabs of A (128 rows) and
+//                       B (256 rows) into a 4-stage shared-memory ring, 128-byte
+//                       swizzle, completion by mbarrier transaction bytes.
+//   warp 1  (one lane)  MMA issuer: four tcgen05.mma (K = 32 bytes each) per
+//                       stage into one of two 256-column TMEM accumulators;
+//                       tcgen05.commit releases the stage / publishes the tile.
+//   warps 2-5           epilogue: tcgen05.ld of the finished accumulator (each
+//                       thread owns one output row) while the MMA warp already
+//                       fills the other accumulator.
+// Tiles come from a scheduler policy, the epilogue from an epilogue policy.
+// No cluster launch and no multicast: every CTA fetches its own tiles.
+// All waits are bounded; a time-out sets bit 0 of *status and the CTA leaves.
+#pragma once
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace cck {
+namespace tc {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kRowBytes = 128;                 // K slab width in bytes (= swizzle span)
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kRowBytes;       // 16 KiB
+constexpr int kBBytes = kBN * kRowBytes;       // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes; // 48 KiB
+constexpr int kThreads = 192;
+constexpr int kEpiWarps = 4;
+constexpr int kTmemCols = 512;                 // two 256-column fp32 accumulators
+constexpr int kScratchFloatsPerWarp = 2 * kBN; // per-epilogue-warp staging (bias / scales)
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+                           kEpiWarps * kScratchFloatsPerWarp * 4;
+
+struct TileWork {
+    int m_tile, n_tile;
+    int split;          // LCE: vocabulary split this tile belongs to
+    bool first, last;   // first / last tile of a unit (a unit = tiles sharing epilogue row state)
+};
+
+// ---- scheduler: plain GEMM, m fastest so that concurrently running CTAs share B panels
+struct SchedGemm {
+    struct Params { int m_tiles, n_tiles; };
+    struct Iter {
+        int t, total, m_tiles;
+        __device__ explicit Iter(const Params& p) : t(blockIdx.x), total(p.m_tiles * p.n_tiles), m_tiles(p.m_tiles) {}
+        __device__ bool next(TileWork& w) {
+            if (t >= total) return false;
+            w.m_tile = t % m_tiles;
+            w.n_tile = t / m_tiles;
+            w.split = 0;
+            w.first = w.last = true;
+            t += gridDim.x;
+            return true;
+        }
+    };
+};
+
+// ---- kernel
+template <bool kFp8, class Sched, class Epi>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const typename Sched::Params sp, const typename Epi::Params ep, int k_blocks, uint32_t idesc,
+            unsigned int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;            // stage ring, 1024-byte aligned
+    uint8_t* gen = smem_raw + (base - raw);
+    const uint32_t bar0 = base + kStages * kStageBytes;       // mbarriers, 8 bytes each
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
+    auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
+    uint8_t* misc = gen + kStages * kStageBytes + 8 * (2 * kStages + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
+    float* scratch = reinterpret_cast<float*>(gen + kStages * kStageBytes + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kElemsPerSlab = kFp8 ? 128 : 64;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(tfull_bar(b), 1);
+            ptx::mbar_init(tempty_bar(b), kEpiWarps);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_addr(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            typename Sched::Iter it(sp);
+            TileWork w;
+            while (ok && it.next(w)) {
+                const int m0 = w.m_tile * kBM, n0 = w.n_tile * kBN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+                    const uint32_t a_dst = base + stage * kStageBytes;
+                    ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kElemsPerSlab, m0);
+                    ptx::tma_load_2d(a_dst + kABytes, &tmap_b, full_bar(stage), kb * kElemsPerSlab, n0);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc_iter = 0;
+            bool ok = true;
+            typename Sched::Iter it(sp);
+            TileWork w;
+            while (ok && it.next(w)) {
+                const int buf = acc_iter & 1;
+                const uint32_t acc_phase = (acc_iter >> 1) & 1;
+                if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag)) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t d = tmem_base + buf * kBN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_src = base + stage * kStageBytes;
+                    const uint64_t da = ptx::smem_desc_k_sw128(a_src);
+                    const uint64_t db = ptx::smem_desc_k_sw128(a_src + kABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {        // 4 x 32 bytes of K per slab
+                        const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
+                        if (kFp8) ptx::mma_f8(d, da + 2 * k, db + 2 * k, idesc, acc);
+                        else      ptx::mma_f16(d, da + 2 * k, db + 2 * k, idesc, acc);
+                    }
+                    ptx::mma_commit(empty_bar(stage));   // stage reusable once these MMAs have read it
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::mma_commit(tfull_bar(buf));  // accumulator complete
+                ++acc_iter;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;                     // TMEM lanes this warp may read
+        const int row_in_tile = quarter * 32 + lane;
+        float* my_scratch = scratch + (warp - 2) * kScratchFloatsPerWarp;
+        typename Epi::Thread th;
+        int acc_iter = 0;
+        typename Sched::Iter it(sp);
+        TileWork w;
+        while (it.next(w)) {
+            const int buf = acc_iter & 1;
+            const uint32_t acc_phase = (acc_iter >> 1) & 1;
+            __syncwarp();
+            Epi::tile_begin(ep, th, w, my_scratch, lane, row_in_tile);
+            __syncwarp();
+            const bool got = ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
+#pragma unroll 1
+            for (int c = 0; c < kBN / 32; ++c) {
+                float acc[32];
+                ptx::tmem_ld32(t0 + c * 32, acc);
+                Epi::chunk(ep, th, w, row_in_tile, c * 32, acc, my_scratch);
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+            Epi::tile_end(ep, th, w, row_in_tile);
+            ++acc_iter;
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies / MMAs that may still be in flight a bounded time to land
+        const unsigned long long t0 = ptx::globaltimer();
+        while (ptx::globaltimer() - t0 < 200000ull) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicOr(status, 1u);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Row-major [rows, cols] matrix of `elem_bytes`-wide elements; box = 128 bytes x box_rows, 128-byte swizzle.
+inline cudaError_t make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr,
+                             int64_t rows, int64_t cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * elem_bytes};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+inline int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return kNumSMs;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return kNumSMs;
+        return v;
+    }();
+    return n;
+}
+
+// Device word that collects wait time-outs of the tensor-core kernels (bit 0).
+unsigned int* status_word();
+
+template <bool kFp8, class Sched, class Epi>
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const typename Sched::Params& sp,
+                   const typename Epi::Params& ep, int64_t k_elems, uint32_t idesc, int ctas, cudaStream_t s) {
+    auto kern = gemm_kernel<kFp8, Sched, Epi>;
+    static bool configured = false;   // per instantiation
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    unsigned int* st = status_word();
+    if (!st) return cudaErrorMemoryAllocation;
+    const int slab = kFp8 ? 128 : 64;
+    const int k_blocks = static_cast<int>((k_elems + slab - 1) / slab);
+    kern<<<ctas, kThreads, kSmemBytes, s>>>(ta, tb, sp, ep, k_blocks, idesc, st);
+    return cudaGetLastError();
+}
+
+}  // namespace tc
+}  // namespace cck

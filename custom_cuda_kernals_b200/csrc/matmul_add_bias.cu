@@ -1,0 +1,220 @@
+// y = x @ weight^T + bias   (x [M,K], weight [N,K], bias [N] or null, y [M,N])
+//
+// Replaces the reference's csrc/kernels/matmul_add_bias.cu:53-222, a CUDA-core
+// shared-memory GEMM.  Here f16/bf16 problems run on the 5th-generation tensor
+// cores: TMA-fed, tcgen05.mma into TMEM, fp32 accumulation, bias added in fp32
+// in the epilogue and one rounding to the storage type (gemm_tcgen05.cuh).
+// An FP8 entry point (e4m3 operands, per-token and per-channel scales folded
+// into the epilogue) has no counterpart in the reference.
+// fp32 inputs and shapes TMA cannot address (K not a multiple of 8 elements,
+// fewer rows than one box) use the CUDA-core kernel in gemm_simt.cuh.
+//
+// Tensor-bound: 2*M*N*K flops per launch.
+#include <type_traits>
+
+#include "gemm_simt.cuh"
+#include "gemm_tcgen05.cuh"
+
+namespace cck {
+namespace tc {
+
+__device__ unsigned int g_status_word = 0;
+
+unsigned int* status_word() {
+    static unsigned int* ptr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+        ptr[dev] = static_cast<unsigned int*>(p);
+    }
+    return ptr[dev];
+}
+
+// ---- epilogue: + bias, round once, store
+template <typename T>
+struct EpiBias {
+    struct Params {
+        const T* bias;
+        T* y;
+        int64_t m, n;
+        int vec_ok;     // rows of y start 16-byte aligned
+    };
+    struct Thread {};
+    __device__ static __forceinline__ void tile_begin(const Params& p, Thread&, const TileWork& w, float* scratch,
+                                                      int lane, int) {
+        const int64_t n0 = static_cast<int64_t>(w.n_tile) * kBN;
+#pragma unroll
+        for (int i = 0; i < kBN / 32; ++i) {
+            const int64_t col = n0 + lane + 32 * i;
+            scratch[lane + 32 * i] = (p.bias != nullptr && col < p.n) ? Store<T>::load1(p.bias + col) : 0.0f;
+        }
+    }
+    __device__ static __forceinline__ void chunk(const Params& p, Thread&, const TileWork& w, int row_in_tile,
+                                                 int c0, float (&acc)[32], const float* scratch) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        const int64_t col = static_cast<int64_t>(w.n_tile) * kBN + c0;
+        if (row >= p.m || col >= p.n) return;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] += scratch[c0 + j];
+        T* out = p.y + row * p.n + col;
+        if (p.vec_ok && col + 32 <= p.n) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                Vec16 o;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) o.w[q] = Store<T>::pack2(acc[8 * v + 2 * q], acc[8 * v + 2 * q + 1]);
+                st_stream(out + 8 * v, o);
+            }
+        } else {
+            for (int j = 0; j < 32 && col + j < p.n; ++j) Store<T>::store1(out + j, acc[j]);
+        }
+    }
+    __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
+};
+
+// ---- epilogue: acc * a_scale[row] * w_scale[col] + bias, round once, store
+template <typename T>
+struct EpiScaledBias {
+    struct Params {
+        const float* a_scale;   // [M]
+        const float* w_scale;   // [N]
+        const T* bias;          // [N] or null
+        T* y;
+        int64_t m, n;
+        int vec_ok;
+    };
+    struct Thread { float a_scale; };
+    __device__ static __forceinline__ void tile_begin(const Params& p, Thread& th, const TileWork& w, float* scratch,
+                                                      int lane, int row_in_tile) {
+        const int64_t n0 = static_cast<int64_t>(w.n_tile) * kBN;
+#pragma unroll
+        for (int i = 0; i < kBN / 32; ++i) {
+            const int64_t col = n0 + lane + 32 * i;
+            const bool in = col < p.n;
+            scratch[lane + 32 * i] = in ? p.w_scale[col] : 0.0f;
+            scratch[kBN + lane + 32 * i] = (in && p.bias != nullptr) ? Store<T>::load1(p.bias + col) : 0.0f;
+        }
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        th.a_scale = row < p.m ? p.a_scale[row] : 0.0f;
+    }
+    __device__ static __forceinline__ void chunk(const Params& p, Thread& th, const TileWork& w, int row_in_tile,
+                                                 int c0, float (&acc)[32], const float* scratch) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        const int64_t col = static_cast<int64_t>(w.n_tile) * kBN + c0;
+        if (row >= p.m || col >= p.n) return;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(acc[j] * th.a_scale, scratch[c0 + j], scratch[kBN + c0 + j]);
+        T* out = p.y + row * p.n + col;
+        if (p.vec_ok && col + 32 <= p.n) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                Vec16 o;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) o.w[q] = Store<T>::pack2(acc[8 * v + 2 * q], acc[8 * v + 2 * q + 1]);
+                st_stream(out + 8 * v, o);
+            }
+        } else {
+            for (int j = 0; j < 32 && col + j < p.n; ++j) Store<T>::store1(out + j, acc[j]);
+        }
+    }
+    __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
+};
+
+template <typename T>
+bool tc_applicable(const void* x, const void* w, int64_t m, int64_t k, int64_t n) {
+    return k % 8 == 0 && k >= 64 && m >= kBM && n >= kBN && aligned16(x) && aligned16(w) &&
+           m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31);
+}
+
+template <typename T>
+cudaError_t gemm_tc(const void* x, const void* w, const void* bias, void* y, int64_t m, int64_t k, int64_t n,
+                    cudaStream_t s) {
+    constexpr bool is_bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+    const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap ta, tb;
+    cudaError_t e = make_tmap(&ta, dt, 2, x, m, k, kBM);
+    if (e != cudaSuccess) return e;
+    e = make_tmap(&tb, dt, 2, w, n, k, kBN);
+    if (e != cudaSuccess) return e;
+    SchedGemm::Params sp{static_cast<int>(ceil_div64(m, kBM)), static_cast<int>(ceil_div64(n, kBN))};
+    typename EpiBias<T>::Params ep{static_cast<const T*>(bias), static_cast<T*>(y), m, n,
+                                   (n % 8 == 0 && aligned16(y)) ? 1 : 0};
+    const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
+    const int ctas = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    const uint32_t fmt = is_bf16 ? 1u : 0u;
+    return launch<false, SchedGemm, EpiBias<T>>(ta, tb, sp, ep, k, ptx::instr_desc(fmt, fmt, kBM, kBN), ctas, s);
+}
+
+}  // namespace tc
+}  // namespace cck
+
+extern "C" int32_t launch_matmul_add_bias_fwd(const void* x, const void* weight, const void* bias, void* y,
+                                              int64_t m, int64_t k, int64_t n, int32_t dtype, void* stream) {
+    using namespace cck;
+    if (m <= 0 || n <= 0 || k <= 0) return cudaSuccess;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case kF32:
+            return gemm_simt<float>(x, weight, bias, y, m, k, n, s);
+        case kF16:
+            return tc::tc_applicable<__half>(x, weight, m, k, n) ? tc::gemm_tc<__half>(x, weight, bias, y, m, k, n, s)
+                                                                 : gemm_simt<__half>(x, weight, bias, y, m, k, n, s);
+        case kBF16:
+            return tc::tc_applicable<__nv_bfloat16>(x, weight, m, k, n)
+                       ? tc::gemm_tc<__nv_bfloat16>(x, weight, bias, y, m, k, n, s)
+                       : gemm_simt<__nv_bfloat16>(x, weight, bias, y, m, k, n, s);
+        default:
+            return cudaErrorInvalidValue;
+    }
+}
+
+extern "C" int32_t launch_matmul_add_bias_fp8_fwd(const uint8_t* a_codes, const float* a_scale,
+                                                  const uint8_t* w_codes, const float* w_scale, const void* bias,
+                                                  void* y, int64_t m, int64_t k, int64_t n, int32_t out_dtype,
+                                                  void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (m <= 0 || n <= 0 || k <= 0) return cudaSuccess;
+    // e4m3 operands only; TMA needs 16-byte row strides and at least one full box per operand
+    if (k % 16 != 0 || k < 128 || m < kBM || n < kBN || !aligned16(a_codes) || !aligned16(w_codes) ||
+        m >= (1LL << 31) || n >= (1LL << 31) || k >= (1LL << 31))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    CUtensorMap ta, tb;
+    cudaError_t e = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_codes, m, k, kBM);
+    if (e != cudaSuccess) return e;
+    e = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_codes, n, k, kBN);
+    if (e != cudaSuccess) return e;
+    SchedGemm::Params sp{static_cast<int>(ceil_div64(m, kBM)), static_cast<int>(ceil_div64(n, kBN))};
+    const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
+    const int ctas = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    const uint32_t idesc = ptx::instr_desc(0u, 0u, kBM, kBN);   // e4m3 x e4m3
+    const int vec_ok = (n % 8 == 0 && aligned16(y)) ? 1 : 0;
+    if (out_dtype == kBF16) {
+        EpiScaledBias<__nv_bfloat16>::Params ep{a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias),
+                                                static_cast<__nv_bfloat16*>(y), m, n, vec_ok};
+        return launch<true, SchedGemm, EpiScaledBias<__nv_bfloat16>>(ta, tb, sp, ep, k, idesc, ctas, s);
+    }
+    if (out_dtype == kF16) {
+        EpiScaledBias<__half>::Params ep{a_scale, w_scale, static_cast<const __half*>(bias),
+                                         static_cast<__half*>(y), m, n, vec_ok};
+        return launch<true, SchedGemm, EpiScaledBias<__half>>(ta, tb, sp, ep, k, idesc, ctas, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+// Returns the tensor-core kernels' error word of the current device and clears
+// it (bit 0: a bounded wait ran out).  Synchronises the device.
+extern "C" int32_t cck_take_device_status(uint32_t* out) {
+    unsigned int* st = cck::tc::status_word();
+    if (!st || !out) return cudaErrorInvalidValue;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    unsigned int v = 0, zero = 0;
+    e = cudaMemcpy(&v, st, sizeof(v), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    *out = v;
+    return cudaMemcpy(st, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+}

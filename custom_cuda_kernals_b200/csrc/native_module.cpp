@@ -1,0 +1,451 @@
+// `_native`: the Python-facing validation + FFI layer over the C ABI in
+// include/custom_cuda_b200.h.
+//
+// C++ stand-in for the reference's Rust/PyO3 module (src/lib.rs:11-29 and
+// src/kernels/*.rs): the same function names and argument orders, the same
+// checks in the same spirit (device type, contiguity, dtype set, dtype and
+// shape relations -> ValueError; a non-zero cudaError_t from a launcher ->
+// RuntimeError), the same zero-copy contract (raw data_ptr() of caller-owned
+// tensors, launch on torch's current stream of the first tensor's device, no
+// allocation or synchronisation).  Two additions the reference lacks: every
+// tensor of a call must live on the same device, and the device is made
+// current for the duration of the call.
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/custom_cuda_b200.h"
+
+namespace {
+
+namespace py = pybind11;
+
+std::string shape_str(const at::Tensor& t) {
+    std::ostringstream os;
+    os << "[";
+    for (int64_t i = 0; i < t.dim(); ++i) os << (i ? ", " : "") << t.size(i);
+    os << "]";
+    return os.str();
+}
+
+const char* tag_name(int32_t tag) {
+    switch (tag) {
+        case CCK_F32: return "F32";
+        case CCK_F16: return "F16";
+        case CCK_BF16: return "BF16";
+        case CCK_F8E4M3: return "F8E4M3";
+        case CCK_F8E5M2: return "F8E5M2";
+        default: return "?";
+    }
+}
+
+[[noreturn]] void value_error(const std::string& msg) { throw py::value_error(msg); }
+
+// device type + contiguity (src/kernels/tensor.rs:38-62)
+void check_cuda_contiguous(const char* name, const at::Tensor& t) {
+    if (!t.is_cuda())
+        value_error(std::string("argument '") + name + "' must be a CUDA tensor, got device type '" +
+                    c10::DeviceTypeName(t.device().type(), /*lower_case=*/true) + "'");
+    if (!t.is_contiguous()) value_error(std::string("argument '") + name + "' must be contiguous");
+}
+
+// compute / storage dtype tag (src/kernels/dtype.rs:14-25)
+int32_t tag_of(const char* name, const at::Tensor& t) {
+    check_cuda_contiguous(name, t);
+    switch (t.scalar_type()) {
+        case at::kFloat: return CCK_F32;
+        case at::kHalf: return CCK_F16;
+        case at::kBFloat16: return CCK_BF16;
+        case at::kFloat8_e4m3fn: return CCK_F8E4M3;
+        case at::kFloat8_e5m2: return CCK_F8E5M2;
+        default:
+            value_error(std::string("unsupported dtype '") + c10::toString(t.scalar_type()) +
+                        "'; expected float32, float16, or bfloat16");
+    }
+}
+
+void expect_float_input(const char* name, int32_t tag) {
+    if (tag != CCK_F32 && tag != CCK_F16 && tag != CCK_BF16)
+        value_error(std::string("unsupported dtype '") + tag_name(tag) + "' for '" + name +
+                    "'; expected float32, float16, or bfloat16");
+}
+
+void expect_same_dtype(const char* name, int32_t got, int32_t want) {
+    if (got != want)
+        value_error(std::string("dtype mismatch: '") + name + "' is " + tag_name(got) + " but expected " +
+                    tag_name(want) + " (must match 'x')");
+}
+
+void expect_f32(const char* name, int32_t tag, const char* why = "") {
+    if (tag != CCK_F32)
+        value_error(std::string("unsupported dtype '") + name + " must be float32" + why + ", got " + tag_name(tag) + "'");
+}
+
+void expect_int(const char* name, const at::Tensor& t, at::ScalarType want, const char* want_name) {
+    check_cuda_contiguous(name, t);
+    if (t.scalar_type() != want)
+        value_error(std::string("unsupported dtype '") + name + " must be " + want_name + ", got " +
+                    c10::toString(t.scalar_type()) + "'");
+}
+
+// All tensors of a call on one device; returns a guard-ready device index.
+struct Launch {
+    c10::cuda::CUDAGuard guard;
+    void* stream;
+    explicit Launch(const at::Tensor& first, std::initializer_list<const at::Tensor*> rest)
+        : guard(first.device()), stream(nullptr) {
+        for (const at::Tensor* t : rest)
+            if (t->defined() && t->device() != first.device())
+                value_error("all tensors must be on the same CUDA device; got " + first.device().str() + " and " +
+                            t->device().str());
+        stream = c10::cuda::getCurrentCUDAStream(first.device().index()).stream();
+    }
+};
+
+void check_launch(const char* fn, int32_t err) {
+    if (err != 0)
+        throw std::runtime_error(std::string("CUDA error: ") + fn + " failed, cudaError_t = " + std::to_string(err));
+}
+
+int32_t parse_fp8_format(const std::string& s) {
+    if (s == "e4m3") return CCK_F8E4M3;
+    if (s == "e5m2") return CCK_F8E5M2;
+    value_error("fp8_format must be 'e4m3' or 'e5m2', got '" + s + "'");
+}
+
+int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ------------------------------------------------------------------ src/kernels/rmsnorm_residual.rs:46-115
+void rmsnorm_residual_fwd(const at::Tensor& x, const at::Tensor& residual, const at::Tensor& weight,
+                          const at::Tensor& y, const at::Tensor& residual_out, double eps) {
+    const int32_t dt = tag_of("x", x);
+    expect_float_input("x", dt);
+    expect_same_dtype("residual", tag_of("residual", residual), dt);
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_same_dtype("y", tag_of("y", y), dt);
+    expect_same_dtype("residual_out", tag_of("residual_out", residual_out), dt);
+    if (residual.sizes() != x.sizes() || y.sizes() != x.sizes() || residual_out.sizes() != x.sizes())
+        value_error("shape mismatch: x/residual/y/residual_out must share the same shape; got x=" + shape_str(x) +
+                    ", residual=" + shape_str(residual) + ", y=" + shape_str(y) +
+                    ", residual_out=" + shape_str(residual_out));
+    if (x.dim() < 1) value_error("shape mismatch: x must have at least 1 dimension");
+    const int64_t cols = x.size(-1);
+    if (weight.dim() != 1 || weight.size(0) != cols)
+        value_error("shape mismatch: weight shape " + shape_str(weight) + " must be [" + std::to_string(cols) +
+                    "] (x's last dimension)");
+    const int64_t rows = cols > 0 ? x.numel() / cols : 0;
+    Launch l(x, {&residual, &weight, &y, &residual_out});
+    check_launch("launch_rmsnorm_residual_fwd",
+                 launch_rmsnorm_residual_fwd(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), y.data_ptr(),
+                                             residual_out.data_ptr(), rows, cols, static_cast<float>(eps), dt,
+                                             l.stream));
+}
+
+// ------------------------------------------------------------------ src/kernels/swiglu.rs:31-79
+void swiglu_fwd(const at::Tensor& gate, const at::Tensor& up, const at::Tensor& y) {
+    const int32_t dt = tag_of("gate", gate);
+    expect_float_input("gate", dt);
+    expect_same_dtype("up", tag_of("up", up), dt);
+    expect_same_dtype("y", tag_of("y", y), dt);
+    if (up.sizes() != gate.sizes() || y.sizes() != gate.sizes())
+        value_error("shape mismatch: gate/up/y must share the same shape; got gate=" + shape_str(gate) +
+                    ", up=" + shape_str(up) + ", y=" + shape_str(y));
+    Launch l(gate, {&up, &y});
+    check_launch("launch_swiglu_fwd",
+                 launch_swiglu_fwd(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.numel(), dt, l.stream));
+}
+
+// ------------------------------------------------------------------ src/kernels/rope.rs:42-153
+void rope_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& cos, const at::Tensor& sin,
+              const at::Tensor& q_out, const at::Tensor& k_out) {
+    const int32_t dt = tag_of("q", q);
+    expect_float_input("q", dt);
+    const int32_t kdt = tag_of("k", k);
+    const int32_t cdt = tag_of("cos", cos), sdt = tag_of("sin", sin);
+    expect_same_dtype("k", kdt, dt);
+    expect_same_dtype("q_out", tag_of("q_out", q_out), dt);
+    expect_same_dtype("k_out", tag_of("k_out", k_out), kdt);
+    expect_f32("cos", cdt, " (RoPE tables are always fp32)");
+    expect_f32("sin", sdt, " (RoPE tables are always fp32)");
+    if (q.dim() != 4)
+        value_error("shape mismatch: q must be 4-D [batch, seq_len, n_q_heads, head_dim], got " + shape_str(q));
+    if (k.dim() != 4)
+        value_error("shape mismatch: k must be 4-D [batch, seq_len, n_kv_heads, head_dim], got " + shape_str(k));
+    if (q_out.sizes() != q.sizes()) value_error("shape mismatch: q_out must match q's shape");
+    if (k_out.sizes() != k.sizes()) value_error("shape mismatch: k_out must match k's shape");
+    const int64_t batch = q.size(0), seq = q.size(1), hq = q.size(2), d = q.size(3);
+    if (k.size(0) != batch || k.size(1) != seq || k.size(3) != d)
+        value_error("shape mismatch: q and k must share batch/seq_len/head_dim; got q=" + shape_str(q) +
+                    ", k=" + shape_str(k));
+    if (d % 2 != 0) value_error("shape mismatch: head_dim must be even, got " + std::to_string(d));
+    const int64_t half = d / 2;
+    if (cos.dim() != 2 || sin.dim() != 2 || cos.size(0) != seq || cos.size(1) != half || sin.size(0) != seq ||
+        sin.size(1) != half)
+        value_error("shape mismatch: cos/sin must have shape [" + std::to_string(seq) + ", " + std::to_string(half) +
+                    "]; got cos=" + shape_str(cos) + ", sin=" + shape_str(sin));
+    Launch l(q, {&k, &cos, &sin, &q_out, &k_out});
+    check_launch("launch_rope_fwd",
+                 launch_rope_fwd(q.data_ptr(), k.data_ptr(), cos.data_ptr(), sin.data_ptr(), q_out.data_ptr(),
+                                 k_out.data_ptr(), batch, seq, hq, k.size(2), d, dt, l.stream));
+}
+
+// ------------------------------------------------------------------ src/kernels/fp8_quant.rs:62-210 (+ token)
+struct Fp8Args {
+    int32_t dt, fmt;
+    int64_t m, n;
+};
+
+Fp8Args fp8_common(const at::Tensor& x, const at::Tensor& x_fp8, const at::Tensor& scale, const std::string& format) {
+    Fp8Args a;
+    a.fmt = parse_fp8_format(format);
+    a.dt = tag_of("x", x);
+    expect_float_input("x", a.dt);
+    const int32_t odt = tag_of("x_fp8", x_fp8);
+    const int32_t sdt = tag_of("scale", scale);
+    if (odt != a.fmt)
+        value_error(std::string("unsupported dtype 'x_fp8 dtype ") + tag_name(odt) +
+                    " does not match requested fp8_format \"" + format + "\"'");
+    expect_f32("scale", sdt);
+    if (x.dim() != 2) value_error("shape mismatch: x must be 2-D [M, N]; got " + shape_str(x));
+    a.m = x.size(0);
+    a.n = x.size(1);
+    if (x_fp8.dim() != 2 || x_fp8.size(0) != a.m || x_fp8.size(1) != a.n)
+        value_error("shape mismatch: x_fp8 shape " + shape_str(x_fp8) + " must be [" + std::to_string(a.m) + ", " +
+                    std::to_string(a.n) + "]");
+    return a;
+}
+
+void fp8_quant_block_fwd(const at::Tensor& x, const at::Tensor& x_fp8, const at::Tensor& scale,
+                         const std::string& fp8_format) {
+    const Fp8Args a = fp8_common(x, x_fp8, scale, fp8_format);
+    const int64_t rb = ceil_div(a.m, 128), cb = ceil_div(a.n, 128);
+    if (scale.dim() != 2 || scale.size(0) != rb || scale.size(1) != cb)
+        value_error("shape mismatch: scale shape " + shape_str(scale) + " must be [" + std::to_string(rb) + ", " +
+                    std::to_string(cb) + "] (ceil(M/128), ceil(N/128))");
+    Launch l(x, {&x_fp8, &scale});
+    check_launch("launch_fp8_quant_block_fwd",
+                 launch_fp8_quant_block_fwd(x.data_ptr(), static_cast<uint8_t*>(x_fp8.data_ptr()),
+                                            static_cast<float*>(scale.data_ptr()), a.m, a.n, a.dt, a.fmt, l.stream));
+}
+
+void fp8_quant_tensor_fwd(const at::Tensor& x, const at::Tensor& x_fp8, const at::Tensor& scale,
+                          const at::Tensor& amax_scratch, const std::string& fp8_format) {
+    const Fp8Args a = fp8_common(x, x_fp8, scale, fp8_format);
+    expect_int("amax_scratch", amax_scratch, at::kInt, "int32");
+    if (amax_scratch.numel() != 1)
+        value_error("shape mismatch: amax_scratch must have exactly 1 element; got shape " + shape_str(amax_scratch));
+    if (scale.numel() != 1)
+        value_error("shape mismatch: scale must have exactly 1 element; got shape " + shape_str(scale));
+    Launch l(x, {&x_fp8, &scale, &amax_scratch});
+    check_launch("launch_fp8_quant_tensor_fwd",
+                 launch_fp8_quant_tensor_fwd(x.data_ptr(), static_cast<uint8_t*>(x_fp8.data_ptr()),
+                                             static_cast<float*>(scale.data_ptr()),
+                                             static_cast<int32_t*>(amax_scratch.data_ptr()), a.m, a.n, a.dt, a.fmt,
+                                             l.stream));
+}
+
+void fp8_quant_token_fwd(const at::Tensor& x, const at::Tensor& x_fp8, const at::Tensor& scale,
+                         const std::string& fp8_format) {
+    const Fp8Args a = fp8_common(x, x_fp8, scale, fp8_format);
+    if (scale.numel() != a.m || scale.dim() < 1 || scale.size(0) != a.m)
+        value_error("shape mismatch: scale shape " + shape_str(scale) + " must be [" + std::to_string(a.m) + ", 1]");
+    Launch l(x, {&x_fp8, &scale});
+    check_launch("launch_fp8_quant_token_fwd",
+                 launch_fp8_quant_token_fwd(x.data_ptr(), static_cast<uint8_t*>(x_fp8.data_ptr()),
+                                            static_cast<float*>(scale.data_ptr()), a.m, a.n, a.dt, a.fmt, l.stream));
+}
+
+// ------------------------------------------------------------------ src/kernels/matmul_add_bias.rs:36-122
+void matmul_add_bias_fwd(const at::Tensor& x, const at::Tensor& weight, const c10::optional<at::Tensor>& bias,
+                         const at::Tensor& y) {
+    const int32_t dt = tag_of("x", x);
+    expect_float_input("x", dt);
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_same_dtype("y", tag_of("y", y), dt);
+    const bool has_bias = bias.has_value() && bias->defined();
+    if (has_bias) expect_same_dtype("bias", tag_of("bias", *bias), dt);
+    if (x.dim() != 2 || weight.dim() != 2)
+        value_error("shape mismatch: x and weight must be 2-D; got x=" + shape_str(x) + ", weight=" + shape_str(weight));
+    const int64_t m = x.size(0), k = x.size(1), n = weight.size(0);
+    if (weight.size(1) != k)
+        value_error("shape mismatch: weight's in_features (" + std::to_string(weight.size(1)) +
+                    ") must match x's last dim (" + std::to_string(k) + ")");
+    if (y.dim() != 2 || y.size(0) != m || y.size(1) != n)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " +
+                    std::to_string(n) + "]");
+    if (has_bias && (bias->dim() != 1 || bias->size(0) != n))
+        value_error("shape mismatch: bias shape " + shape_str(*bias) + " must be [" + std::to_string(n) + "]");
+    at::Tensor none;
+    Launch l(x, {&weight, &y, has_bias ? &*bias : &none});
+    check_launch("launch_matmul_add_bias_fwd",
+                 launch_matmul_add_bias_fwd(x.data_ptr(), weight.data_ptr(), has_bias ? bias->data_ptr() : nullptr,
+                                            y.data_ptr(), m, k, n, dt, l.stream));
+}
+
+void matmul_add_bias_fp8_fwd(const at::Tensor& a, const at::Tensor& a_scale, const at::Tensor& w,
+                             const at::Tensor& w_scale, const c10::optional<at::Tensor>& bias, const at::Tensor& y) {
+    if (tag_of("a_fp8", a) != CCK_F8E4M3 || tag_of("w_fp8", w) != CCK_F8E4M3)
+        value_error("unsupported dtype 'a_fp8 and w_fp8 must be float8_e4m3fn'");
+    expect_f32("a_scale", tag_of("a_scale", a_scale));
+    expect_f32("w_scale", tag_of("w_scale", w_scale));
+    const int32_t odt = tag_of("y", y);
+    if (odt != CCK_BF16 && odt != CCK_F16) value_error("unsupported dtype 'y must be bfloat16 or float16'");
+    const bool has_bias = bias.has_value() && bias->defined();
+    if (has_bias) expect_same_dtype("bias", tag_of("bias", *bias), odt);
+    if (a.dim() != 2 || w.dim() != 2)
+        value_error("shape mismatch: a_fp8 and w_fp8 must be 2-D; got a_fp8=" + shape_str(a) + ", w_fp8=" + shape_str(w));
+    const int64_t m = a.size(0), k = a.size(1), n = w.size(0);
+    if (w.size(1) != k)
+        value_error("shape mismatch: w_fp8's in_features (" + std::to_string(w.size(1)) +
+                    ") must match a_fp8's last dim (" + std::to_string(k) + ")");
+    if (a_scale.numel() != m) value_error("shape mismatch: a_scale must have " + std::to_string(m) + " elements");
+    if (w_scale.numel() != n) value_error("shape mismatch: w_scale must have " + std::to_string(n) + " elements");
+    if (y.dim() != 2 || y.size(0) != m || y.size(1) != n)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " +
+                    std::to_string(n) + "]");
+    if (has_bias && (bias->dim() != 1 || bias->size(0) != n))
+        value_error("shape mismatch: bias shape " + shape_str(*bias) + " must be [" + std::to_string(n) + "]");
+    if (k % 16 != 0) value_error("shape mismatch: the FP8 GEMM needs K to be a multiple of 16, got " + std::to_string(k));
+    at::Tensor none;
+    Launch l(a, {&a_scale, &w, &w_scale, &y, has_bias ? &*bias : &none});
+    check_launch("launch_matmul_add_bias_fp8_fwd",
+                 launch_matmul_add_bias_fp8_fwd(static_cast<const uint8_t*>(a.data_ptr()),
+                                                static_cast<const float*>(a_scale.data_ptr()),
+                                                static_cast<const uint8_t*>(w.data_ptr()),
+                                                static_cast<const float*>(w_scale.data_ptr()),
+                                                has_bias ? bias->data_ptr() : nullptr, y.data_ptr(), m, k, n, odt,
+                                                l.stream));
+}
+
+// ------------------------------------------------------------------ src/kernels/linear_cross_entropy.rs:44-133
+void linear_ce_chunk_update(const at::Tensor& logits_chunk, const at::Tensor& targets, int64_t v_start,
+                            const at::Tensor& running_max, const at::Tensor& running_sum,
+                            const at::Tensor& target_logit) {
+    const int32_t dt = tag_of("logits_chunk", logits_chunk);
+    expect_float_input("logits_chunk", dt);
+    expect_int("targets", targets, at::kLong, "int64");
+    expect_f32("running_max", tag_of("running_max", running_max));
+    expect_f32("running_sum", tag_of("running_sum", running_sum));
+    expect_f32("target_logit", tag_of("target_logit", target_logit));
+    if (logits_chunk.dim() != 2)
+        value_error("shape mismatch: logits_chunk must be 2-D [N, chunk_v], got " + shape_str(logits_chunk));
+    const int64_t n = logits_chunk.size(0), chunk_v = logits_chunk.size(1);
+    if (targets.dim() != 1 || targets.size(0) != n)
+        value_error("shape mismatch: targets shape " + shape_str(targets) + " must be [" + std::to_string(n) +
+                    "] (logits_chunk's row count)");
+    const std::pair<const char*, const at::Tensor*> accs[] = {
+        {"running_max", &running_max}, {"running_sum", &running_sum}, {"target_logit", &target_logit}};
+    for (const auto& a : accs)
+        if (a.second->dim() != 1 || a.second->size(0) != n)
+            value_error(std::string("shape mismatch: ") + a.first + " shape " + shape_str(*a.second) + " must be [" +
+                        std::to_string(n) + "]");
+    Launch l(logits_chunk, {&targets, &running_max, &running_sum, &target_logit});
+    check_launch("launch_linear_ce_chunk_update",
+                 launch_linear_ce_chunk_update(logits_chunk.data_ptr(), static_cast<const int64_t*>(targets.data_ptr()),
+                                               v_start, n, chunk_v, static_cast<float*>(running_max.data_ptr()),
+                                               static_cast<float*>(running_sum.data_ptr()),
+                                               static_cast<float*>(target_logit.data_ptr()), dt, l.stream));
+}
+
+// fused path (no counterpart in the reference)
+void linear_cross_entropy_fwd(const at::Tensor& hidden, const at::Tensor& weight, const at::Tensor& targets,
+                              int64_t v_start, const at::Tensor& row_stats, const at::Tensor& workspace) {
+    const int32_t dt = tag_of("hidden", hidden);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "' for the fused path; expected float16 or bfloat16");
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_int("targets", targets, at::kLong, "int64");
+    expect_f32("row_stats", tag_of("row_stats", row_stats));
+    check_cuda_contiguous("workspace", workspace);
+    if (hidden.dim() != 2 || weight.dim() != 2)
+        value_error("shape mismatch: hidden and weight must be 2-D; got hidden=" + shape_str(hidden) +
+                    ", weight=" + shape_str(weight));
+    const int64_t n = hidden.size(0), h = hidden.size(1), v = weight.size(0);
+    if (weight.size(1) != h)
+        value_error("shape mismatch: weight's hidden dim (" + std::to_string(weight.size(1)) +
+                    ") must match hidden's last dim (" + std::to_string(h) + ")");
+    if (targets.dim() != 1 || targets.size(0) != n)
+        value_error("shape mismatch: targets shape " + shape_str(targets) + " must be [" + std::to_string(n) + "]");
+    if (row_stats.dim() != 2 || row_stats.size(0) != 3 || row_stats.size(1) != n)
+        value_error("shape mismatch: row_stats shape " + shape_str(row_stats) + " must be [3, " + std::to_string(n) + "]");
+    if (h % 8 != 0) value_error("shape mismatch: the fused path needs hidden dim to be a multiple of 8");
+    const int64_t ws_bytes = static_cast<int64_t>(workspace.numel()) * workspace.element_size();
+    if (ws_bytes < cck_lce_workspace_bytes(n, v))
+        value_error("shape mismatch: workspace has " + std::to_string(ws_bytes) + " bytes, needs " +
+                    std::to_string(cck_lce_workspace_bytes(n, v)));
+    Launch l(hidden, {&weight, &targets, &row_stats, &workspace});
+    check_launch("launch_linear_cross_entropy_fwd",
+                 launch_linear_cross_entropy_fwd(hidden.data_ptr(), weight.data_ptr(),
+                                                 static_cast<const int64_t*>(targets.data_ptr()), v_start, n, h, v,
+                                                 static_cast<float*>(row_stats.data_ptr()), workspace.data_ptr(),
+                                                 ws_bytes, dt, l.stream));
+}
+
+int64_t lce_workspace_bytes(const at::Tensor& like, int64_t n, int64_t v) {
+    c10::cuda::CUDAGuard guard(like.device());
+    return cck_lce_workspace_bytes(n, v);
+}
+
+void lce_finalize(const at::Tensor& stats, const at::Tensor& targets, int64_t ignore_index,
+                  const c10::optional<at::Tensor>& loss_rows, const at::Tensor& reduce_out) {
+    expect_f32("stats", tag_of("stats", stats));
+    expect_int("targets", targets, at::kLong, "int64");
+    expect_f32("reduce_out", tag_of("reduce_out", reduce_out));
+    const int64_t n = targets.numel();
+    if (stats.dim() != 3 || stats.size(1) != 3 || stats.size(2) != n || stats.size(0) < 1)
+        value_error("shape mismatch: stats shape " + shape_str(stats) + " must be [shards, 3, " + std::to_string(n) + "]");
+    if (reduce_out.numel() != 2) value_error("shape mismatch: reduce_out must have 2 elements");
+    const bool want_rows = loss_rows.has_value() && loss_rows->defined();
+    if (want_rows) {
+        expect_f32("loss_rows", tag_of("loss_rows", *loss_rows));
+        if (loss_rows->numel() != n) value_error("shape mismatch: loss_rows must have " + std::to_string(n) + " elements");
+    }
+    at::Tensor none;
+    Launch l(stats, {&targets, &reduce_out, want_rows ? &*loss_rows : &none});
+    check_launch("launch_lce_finalize",
+                 launch_lce_finalize(static_cast<const float*>(stats.data_ptr()),
+                                     static_cast<const int64_t*>(targets.data_ptr()), n, stats.size(0), ignore_index,
+                                     want_rows ? static_cast<float*>(loss_rows->data_ptr()) : nullptr,
+                                     static_cast<float*>(reduce_out.data_ptr()), l.stream));
+}
+
+uint32_t take_device_status(const at::Tensor& like) {
+    c10::cuda::CUDAGuard guard(like.device());
+    uint32_t v = 0;
+    check_launch("cck_take_device_status", cck_take_device_status(&v));
+    return v;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_native, m) {
+    m.doc() = "validation + FFI layer over libcustom_cuda_b200 (C ABI in include/custom_cuda_b200.h)";
+    m.def("rmsnorm_residual_fwd", &rmsnorm_residual_fwd, py::arg("x"), py::arg("residual"), py::arg("weight"),
+          py::arg("y"), py::arg("residual_out"), py::arg("eps"));
+    m.def("swiglu_fwd", &swiglu_fwd, py::arg("gate"), py::arg("up"), py::arg("y"));
+    m.def("rope_fwd", &rope_fwd, py::arg("q"), py::arg("k"), py::arg("cos"), py::arg("sin"), py::arg("q_out"),
+          py::arg("k_out"));
+    m.def("linear_ce_chunk_update", &linear_ce_chunk_update, py::arg("logits_chunk"), py::arg("targets"),
+          py::arg("v_start"), py::arg("running_max"), py::arg("running_sum"), py::arg("target_logit"));
+    m.def("matmul_add_bias_fwd", &matmul_add_bias_fwd, py::arg("x"), py::arg("weight"), py::arg("bias").none(true),
+          py::arg("y"));
+    m.def("fp8_quant_block_fwd", &fp8_quant_block_fwd, py::arg("x"), py::arg("x_fp8"), py::arg("scale"),
+          py::arg("fp8_format"));
+    m.def("fp8_quant_tensor_fwd", &fp8_quant_tensor_fwd, py::arg("x"), py::arg("x_fp8"), py::arg("scale"),
+          py::arg("amax_scratch"), py::arg("fp8_format"));
+    // additions
+    m.def("fp8_quant_token_fwd", &fp8_quant_token_fwd, py::arg("x"), py::arg("x_fp8"), py::arg("scale"),
+          py::arg("fp8_format"));
+    m.def("matmul_add_bias_fp8_fwd", &matmul_add_bias_fp8_fwd, py::arg("a_fp8"), py::arg("a_scale"), py::arg("w_fp8"),
+          py::arg("w_scale"), py::arg("bias").none(true), py::arg("y"));
+    m.def("linear_cross_entropy_fwd", &linear_cross_entropy_fwd, py::arg("hidden"), py::arg("weight"),
+          py::arg("targets"), py::arg("v_start"), py::arg("row_stats"), py::arg("workspace"));
+    m.def("lce_workspace_bytes", &lce_workspace_bytes, py::arg("like"), py::arg("n"), py::arg("v_count"));
+    m.def("lce_finalize", &lce_finalize, py::arg("stats"), py::arg("targets"), py::arg("ignore_index"),
+          py::arg("loss_rows").none(true), py::arg("reduce_out"));
+    m.def("take_device_status", &take_device_status, py::arg("like"));
+}

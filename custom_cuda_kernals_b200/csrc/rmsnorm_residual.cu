@@ -1,0 +1,159 @@
+// Fused residual add + RMSNorm:
+//   residual_out = x + residual;  y = residual_out * rsqrt(mean(residual_out^2) + eps) * weight
+//
+// Replaces the reference's csrc/kernels/rmsnorm_residual.cu:36-119, which
+// walks every row twice with scalar loads.  Here a row is read from HBM exactly
+// once: each thread issues all of its 16-byte loads of `x` and `residual`
+// up front, keeps the summed row in registers across the reduction, and writes
+// both outputs with 16-byte streaming stores.  One CTA per row; the CTA width is
+// chosen so that every thread owns at most kVecPerThread vectors.
+//
+// Rounding follows the PyTorch baseline (baselines/rmsnorm_residual.py:130-136):
+// the sum is rounded to the storage type first, the statistics are taken from
+// the rounded sum in fp32, the normalised value is rounded to the storage type
+// and then multiplied by `weight` in the storage type.
+//
+// HBM-bound: 4 tensors * rows * cols * sizeof(T) bytes per launch (+ weight once).
+#include "common.cuh"
+
+namespace cck {
+namespace {
+
+// CTA reduction for a runtime CTA width (multiple of 32).
+__device__ __forceinline__ float cta_sum_dyn(float v, float* slots) {
+    v = warp_sum(v);
+    const int warps = blockDim.x >> 5;
+    if (warps == 1) return v;
+    if ((threadIdx.x & 31) == 0) slots[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.0f;
+    for (int i = 0; i < warps; ++i) r += slots[i];
+    return r;
+}
+
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024)
+rmsnorm_rowreg_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
+                      T* __restrict__ y, T* __restrict__ res_out, int cols, int n_vec, float eps) {
+    constexpr int kPer = Store<T>::kPerVec;
+    __shared__ float slots[32];
+    const int64_t row_off = static_cast<int64_t>(blockIdx.x) * n_vec;
+    const Vec16* x16 = reinterpret_cast<const Vec16*>(x) + row_off;
+    const Vec16* r16 = reinterpret_cast<const Vec16*>(res) + row_off;
+    const Vec16* w16 = reinterpret_cast<const Vec16*>(w);
+    Vec16* y16 = reinterpret_cast<Vec16*>(y) + row_off;
+    Vec16* o16 = reinterpret_cast<Vec16*>(res_out) + row_off;
+
+    Vec16 xv[VPT], rv[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) {
+            xv[j] = ld_stream(x16 + i);
+            rv[j] = ld_stream(r16 + i);
+        }
+    }
+
+    // the rounded sum stays packed in the storage type (it is exact there)
+    Vec16 sv[VPT];
+    float sq = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) {
+            float a[kPer], b[kPer];
+            unpack<T>(xv[j], a);
+            unpack<T>(rv[j], b);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) a[e] += b[e];
+            sv[j] = pack<T>(a);
+            unpack<T>(sv[j], a);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) sq = fmaf(a[e], a[e], sq);
+            st_stream(o16 + i, sv[j]);
+        }
+    }
+    const float total = cta_sum_dyn(sq, slots);
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(cols) + eps);
+
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) {
+            float a[kPer], g[kPer];
+            unpack<T>(sv[j], a);
+            unpack<T>(ld_cached(w16 + i), g);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) a[e] = Store<T>::round(a[e] * inv) * g[e];
+            st_stream(y16 + i, pack<T>(a));
+        }
+    }
+}
+
+// Any column count / alignment: scalar accesses, the row sum is written to
+// residual_out in pass one and read back (by the thread that wrote it) in pass two.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_generic_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
+                       T* __restrict__ y, T* res_out, int64_t cols, float eps) {
+    __shared__ float slots[32];
+    const int64_t off = static_cast<int64_t>(blockIdx.x) * cols;
+    float sq = 0.0f;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float s = Store<T>::round(Store<T>::load1(x + off + c) + Store<T>::load1(res + off + c));
+        Store<T>::store1(res_out + off + c, s);
+        sq = fmaf(s, s, sq);
+    }
+    const float total = cta_sum_dyn(sq, slots);
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(cols) + eps);
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float s = Store<T>::load1(res_out + off + c);
+        Store<T>::store1(y + off + c, Store<T>::round(s * inv) * Store<T>::load1(w + c));
+    }
+}
+
+template <typename T>
+cudaError_t run(const void* x, const void* res, const void* w, void* y, void* res_out,
+                int64_t rows, int64_t cols, float eps, cudaStream_t stream) {
+    constexpr int kPer = Store<T>::kPerVec;
+    const T* xp = static_cast<const T*>(x);
+    const T* rp = static_cast<const T*>(res);
+    const T* wp = static_cast<const T*>(w);
+    T* yp = static_cast<T*>(y);
+    T* op = static_cast<T*>(res_out);
+    if (rows > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const unsigned grid = static_cast<unsigned>(rows);
+    const bool vec_ok = (cols % kPer == 0) && aligned16(x) && aligned16(res) && aligned16(w) &&
+                        aligned16(y) && aligned16(res_out);
+    const int64_t n_vec = cols / kPer;
+    if (vec_ok && n_vec <= 8 * 1024) {
+        const int vpt = n_vec <= 4 * 1024 ? 4 : 8;
+        int threads = static_cast<int>(ceil_div64(ceil_div64(n_vec, vpt), 32) * 32);
+        if (threads < 32) threads = 32;
+        if (vpt == 4)
+            rmsnorm_rowreg_kernel<T, 4><<<grid, threads, 0, stream>>>(
+                xp, rp, wp, yp, op, static_cast<int>(cols), static_cast<int>(n_vec), eps);
+        else
+            rmsnorm_rowreg_kernel<T, 8><<<grid, threads, 0, stream>>>(
+                xp, rp, wp, yp, op, static_cast<int>(cols), static_cast<int>(n_vec), eps);
+    } else {
+        rmsnorm_generic_kernel<T><<<grid, 256, 0, stream>>>(xp, rp, wp, yp, op, cols, eps);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace cck
+
+extern "C" int32_t launch_rmsnorm_residual_fwd(const void* x, const void* residual, const void* weight,
+                                               void* y, void* residual_out, int64_t rows, int64_t cols,
+                                               float eps, int32_t dtype, void* stream) {
+    if (rows <= 0 || cols <= 0) return cudaSuccess;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case cck::kF32:  return cck::run<float>(x, residual, weight, y, residual_out, rows, cols, eps, s);
+        case cck::kF16:  return cck::run<__half>(x, residual, weight, y, residual_out, rows, cols, eps, s);
+        case cck::kBF16: return cck::run<__nv_bfloat16>(x, residual, weight, y, residual_out, rows, cols, eps, s);
+        default:         return cudaErrorInvalidValue;
+    }
+}

@@ -1,0 +1,115 @@
+/* C ABI of libcustom_cuda_b200.so - B200 (sm_100a) kernels for the Llama-block ops.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers and sizes,
+ * returns a cudaError_t as int32_t (0 = success), launches asynchronously on
+ * the given stream (a cudaStream_t passed as void*), and - unless stated
+ * otherwise - never allocates, frees, copies or synchronises.  All buffers
+ * are owned by the caller, row-major and contiguous.  `dtype` is one of the
+ * CCK_* tags below; empty problems return success without launching.
+ *
+ * The first seven functions are binary-compatible replacements for the
+ * launchers the reference project (BhargavKumarNath/custom_cuda_kernals)
+ * binds from Rust; each comment cites the declaration it replaces.  The rest
+ * are additions that follow the same conventions.
+ */
+#ifndef CUSTOM_CUDA_B200_H_
+#define CUSTOM_CUDA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype tags; values fixed by csrc/includes/common.cuh:28-34 and src/kernels/dtype.rs:6-12 */
+enum {
+    CCK_F32 = 0,
+    CCK_F16 = 1,
+    CCK_BF16 = 2,
+    CCK_F8E4M3 = 3,
+    CCK_F8E5M2 = 4
+};
+
+/* residual_out = x + residual;  y = residual_out * rsqrt(mean(residual_out^2) + eps) * weight.
+ * x, residual, y, residual_out: [rows, cols]; weight: [cols]; one dtype (f32/f16/bf16).
+ * Replaces csrc/includes/rmsnorm_residual.h:17-27. */
+int32_t launch_rmsnorm_residual_fwd(const void* x, const void* residual, const void* weight, void* y,
+                                    void* residual_out, int64_t rows, int64_t cols, float eps,
+                                    int32_t dtype, void* stream);
+
+/* y = silu(gate) * up over n elements.  Replaces csrc/includes/swiglu.h:16-22. */
+int32_t launch_swiglu_fwd(const void* gate, const void* up, void* y, int64_t n, int32_t dtype, void* stream);
+
+/* Half-split rotary embedding of q [batch, seq_len, n_q_heads, head_dim] and
+ * k [batch, seq_len, n_kv_heads, head_dim]; cos_table/sin_table [seq_len, head_dim/2] float32.
+ * head_dim must be even.  Replaces csrc/includes/rope.h:23-36. */
+int32_t launch_rope_fwd(const void* q, const void* k, const void* cos_table, const void* sin_table,
+                        void* q_out, void* k_out, int64_t batch, int64_t seq_len, int64_t n_q_heads,
+                        int64_t n_kv_heads, int64_t head_dim, int32_t dtype, void* stream);
+
+/* FP8 quantisation with one scale per 128x128 tile: scale = max(amax/FP8_MAX, 1e-12),
+ * x_fp8 = fp8(x / scale).  x [m, n]; x_fp8 [m, n] bytes; scale [ceil(m/128), ceil(n/128)].
+ * fp8_format is CCK_F8E4M3 or CCK_F8E5M2.  Replaces csrc/includes/fp8_quant.h:41-49. */
+int32_t launch_fp8_quant_block_fwd(const void* x, uint8_t* x_fp8, float* scale, int64_t m, int64_t n,
+                                   int32_t dtype, int32_t fp8_format, void* stream);
+
+/* FP8 quantisation with one scale for the whole matrix (two kernels on the stream).
+ * scale [1]; amax_scratch [1] int32, zeroed by the caller before every call.
+ * Replaces csrc/includes/fp8_quant.h:51-60. */
+int32_t launch_fp8_quant_tensor_fwd(const void* x, uint8_t* x_fp8, float* scale, int32_t* amax_scratch,
+                                    int64_t m, int64_t n, int32_t dtype, int32_t fp8_format, void* stream);
+
+/* y = x @ weight^T + bias.  x [m, k]; weight [n, k]; bias [n] or NULL; y [m, n]; one dtype.
+ * Replaces csrc/includes/matmul_add_bias.h:20-29. */
+int32_t launch_matmul_add_bias_fwd(const void* x, const void* weight, const void* bias, void* y,
+                                   int64_t m, int64_t k, int64_t n, int32_t dtype, void* stream);
+
+/* Online-softmax update with one materialised chunk of logits [n, chunk_v] covering
+ * vocabulary columns [v_start, v_start + chunk_v).  running_max / running_sum / target_logit:
+ * [n] float32, initialised by the caller to -inf / 0 / 0.  targets [n] int64.
+ * Replaces csrc/includes/linear_cross_entropy.h:31-41. */
+int32_t launch_linear_ce_chunk_update(const void* logits_chunk, const int64_t* targets, int64_t v_start,
+                                      int64_t n, int64_t chunk_v, float* running_max, float* running_sum,
+                                      float* target_logit, int32_t dtype, void* stream);
+
+/* ---- additions (no counterpart in the reference) ------------------------------------------ */
+
+/* FP8 quantisation with one scale per row (per token).  scale [m] (viewed as [m, 1]). */
+int32_t launch_fp8_quant_token_fwd(const void* x, uint8_t* x_fp8, float* scale, int64_t m, int64_t n,
+                                   int32_t dtype, int32_t fp8_format, void* stream);
+
+/* y = (a_codes * a_scale[row]) @ (w_codes * w_scale[col])^T + bias with e4m3 operands on the
+ * tensor cores.  a_codes [m, k], w_codes [n, k] e4m3 bytes; a_scale [m], w_scale [n] float32;
+ * bias [n] in out_dtype or NULL; y [m, n] in out_dtype (CCK_BF16 or CCK_F16).
+ * Requires k % 16 == 0 and 16-byte aligned operands; otherwise cudaErrorInvalidValue. */
+int32_t launch_matmul_add_bias_fp8_fwd(const uint8_t* a_codes, const float* a_scale, const uint8_t* w_codes,
+                                       const float* w_scale, const void* bias, void* y, int64_t m, int64_t k,
+                                       int64_t n, int32_t out_dtype, void* stream);
+
+/* Fused linear + softmax statistics, logits never materialised.  hidden [n, h]; weight
+ * [v_count, h] = rows v_start .. v_start+v_count-1 of the LM head; targets [n] int64 global ids.
+ * row_stats [3][n] float32 receives per row: max logit, sum exp(logit - max), target logit
+ * (0 when the target is outside this slice).  workspace: at least cck_lce_workspace_bytes(n,
+ * v_count) bytes of device memory, contents irrelevant.  dtype CCK_BF16 or CCK_F16, h % 8 == 0,
+ * 16-byte aligned operands; otherwise cudaErrorInvalidValue. */
+int32_t launch_linear_cross_entropy_fwd(const void* hidden, const void* weight, const int64_t* targets,
+                                        int64_t v_start, int64_t n, int64_t h, int64_t v_count,
+                                        float* row_stats, void* workspace, int64_t workspace_bytes,
+                                        int32_t dtype, void* stream);
+int64_t cck_lce_workspace_bytes(int64_t n, int64_t v_count);
+int64_t cck_lce_num_splits(int64_t n, int64_t v_count);
+
+/* Merge row_stats of n_shards vocabulary slices (stats [n_shards][3][n]) into per-row losses:
+ * loss_rows [n] (0 where targets == ignore_index; may be NULL) and reduce_out [2] =
+ * { sum of losses, number of rows whose target is not ignore_index }. */
+int32_t launch_lce_finalize(const float* stats, const int64_t* targets, int64_t n, int64_t n_shards,
+                            int64_t ignore_index, float* loss_rows, float* reduce_out, void* stream);
+
+/* Reads and clears the error word of the tensor-core kernels on the current device (bit 0: a
+ * bounded wait inside a kernel ran out and the kernel gave up).  Synchronises the device. */
+int32_t cck_take_device_status(uint32_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUSTOM_CUDA_B200_H_ */

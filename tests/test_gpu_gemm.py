@@ -1,0 +1,98 @@
+"""GPU parity: matmul_add_bias (tensor-core and CUDA-core paths) and the FP8 GEMM
+against the CPU oracle (baselines/matmul_add_bias.py cases and tolerances)."""
+
+import pytest
+import torch
+
+from oracle import cases, ops, workloads
+from tests.gpu_util import DEV, check, device_status_clean, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("case", cases.GEMM_CASES, ids=lambda c: c.name)
+def test_matmul_add_bias_cases(case):
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    x, w, b = cases.gemm_inputs(case)
+    y = matmul_add_bias(*to_dev(x, w, b))
+    assert y.shape == (case.m, case.n) and y.dtype == case.dtype
+    if case.m == 0:
+        return
+    check(y.double(), ops.matmul_add_bias_fp64(x, w, b), case.dtype, ops.TOLERANCE_GEMM)
+    if case.m * case.k * case.n <= 2048 * 4096 * 4096 or case.dtype != torch.float32:
+        check(y, ops.matmul_add_bias(x, w, b), case.dtype, ops.TOLERANCE_GEMM)
+    assert device_status_clean(y)
+
+
+def test_none_bias_equals_zero_bias():
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(384, 512, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(640, 512, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    a = matmul_add_bias(x, w, None)
+    b = matmul_add_bias(x, w, torch.zeros(640, dtype=torch.bfloat16, device=DEV))
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 256), (129, 72, 257), (300, 200, 520), (1000, 4096, 264),
+                                   (4, 512, 1024), (2048, 8, 512), (131, 1032, 777)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tensor_core_path_ragged_shapes(shape, dtype):
+    """K a multiple of 8 goes to the tcgen05 kernel: partial tiles in M, N and K are
+    zero-filled by TMA and masked in the epilogue; N not a multiple of 8 takes scalar stores."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    m, k, n = shape
+    g = torch.Generator().manual_seed(m * 7 + n)
+    x = (torch.randn(m, k, generator=g) * 0.5).to(dtype)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(dtype)
+    b = torch.randn(n, generator=g).to(dtype)
+    y = matmul_add_bias(*to_dev(x, w, b))
+    check(y.double(), ops.matmul_add_bias_fp64(x, w, b), dtype, ops.TOLERANCE_GEMM)
+    assert device_status_clean(y)
+
+
+def test_matmul_identity_is_exact():
+    """x @ I + 0 reproduces x bit for bit (every product is exact, one addend per sum)."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(512, 1024, generator=g).to(torch.bfloat16).to(DEV)
+    eye = torch.eye(1024, dtype=torch.bfloat16, device=DEV)
+    assert torch.equal(matmul_add_bias(x, eye, None), x)
+
+
+def test_matmul_config3_full_size():
+    """Benchmark config 3: A [8192,4096], W [14336,4096], bias [14336], bf16."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    a, w, b = workloads.gemm_bf16()
+    y = matmul_add_bias(*to_dev(a, w, b))
+    rows = torch.arange(0, 8192, 61)           # every 61st row through the fp64 oracle
+    check(y[rows.to(DEV)].double(), ops.matmul_add_bias_fp64(a[rows], w, b), torch.bfloat16, ops.TOLERANCE_GEMM)
+    check(y, ops.matmul_add_bias(a, w, b), torch.bfloat16, ops.TOLERANCE_GEMM)
+    # linearity in x: (2x) W^T + b - (x W^T + b) == x W^T, on the whole output
+    y2 = matmul_add_bias((a * 2).to(DEV), w.to(DEV), b.to(DEV))
+    y0 = matmul_add_bias(a.to(DEV), w.to(DEV), None)
+    torch.testing.assert_close((y2.float() - y.float()), y0.float(), rtol=2e-2, atol=4e-2)
+    assert device_status_clean(y)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 512), (1024, 4096, 1792), (200, 144, 300)])
+def test_fp8_gemm_matches_oracle(shape):
+    """e4m3 A with per-token scales x e4m3 W with per-channel scales, both from the per-token
+    quantiser; oracle = dequantise, fp32 matmul, + bias (unpinned by the reference)."""
+    from custom_cuda.kernels.fp8_quant import fp8_quant
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias_fp8
+    m, k, n = shape
+    g = torch.Generator().manual_seed(k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    b = (0.02 * torch.randn(n, generator=g)).to(torch.bfloat16)
+    a8, a_s = fp8_quant(a.to(DEV), "e4m3", "token")
+    w8, w_s = fp8_quant(w.to(DEV), "e4m3", "token")
+    y = matmul_add_bias_fp8(a8, a_s, w8, w_s, b.to(DEV))
+    want = ops.matmul_add_bias_fp8(a8.cpu(), a_s.cpu(), w8.cpu(), w_s.cpu(), b)
+    check(y, want, torch.bfloat16, ops.TOLERANCE_GEMM)
+    # and it approximates the unquantised product to FP8 accuracy
+    full = ops.matmul_add_bias_fp64(a, w, b)
+    rel = (y.cpu().double() - full).norm() / full.norm()
+    assert rel < 0.08, rel
+    assert device_status_clean(y)
