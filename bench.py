@@ -1,0 +1,481 @@
+"""Benchmark of the Llama-block op path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--skip-ops]
+
+One step = one forward pass of a Llama-3-8B decoder block (hidden 4096, 32 q / 8 kv
+heads, FFN 14336, bf16) over batch 8 x seq 2048 of synthetic activations; with N ranks
+(one process per GPU, launched by torch.distributed.run) the 8 sequences are split
+across the ranks and the weights replicated - strong scaling, no collective on the
+block path.  Rank 0 prints ONE JSON line:
+
+  value / ms_per_step   tokens/s of the whole job with inputs resident in HBM, timed on
+                        the device with CUDA events, max over ranks
+  e2e                   the same through LlamaBlock.forward_host: pinned host input
+                        copied in and the output copied back inside the timed region
+  roofline              the dominant kernel (the tcgen05 GEMM): algorithmic flops of the
+                        seven projections / their summed CUDA-event time inside the
+                        timed steps, against the measured cuBLAS bf16 peak
+  ops                   each fused op alone at the configuration sizes (HBM GB/s or
+                        TFLOP/s, fraction of the measured peak), row / column / vocab
+                        sharded over the ranks
+  cpu_baseline          (N=1) the CPU oracle of the same block on a bounded sample
+  clocks                SM clock and throttle reasons sampled during the timed region
+
+`--impl reference` times the reference path's CPU implementation (the oracle's
+restatement of examples/llama_block.py BaselineLlamaBlock with the eager baselines) on
+the host cores, on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+METRIC = "llama3_8b_block_tokens_per_s"
+UNIT = "tokens/s"
+BATCH, SEQ = 8, 2048
+CFG = dict(hidden=4096, ffn=14336, n_heads=32, n_kv_heads=8, head_dim=128, eps=1e-5, theta=500000.0)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
+# ncu capture summarised under profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES = {"gemm": None}
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:  # malformed file: fall through to the stated fallback
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) every 100 ms."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self.nv, self.err = None, repr(e)
+
+    def _loop(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.nv:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "error": self.err}
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------- helpers
+def device_weights(dev, seed=1006):
+    """Block parameters N(0, 0.02) in bf16, norm weights 1, generated on the device."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    hid, ffn, kv = CFG["hidden"], CFG["ffn"], CFG["n_kv_heads"] * CFG["head_dim"]
+
+    def lin(o, i):
+        return (0.02 * torch.randn(o, i, device=dev, generator=g)).to(torch.bfloat16)
+
+    return {"input_layernorm_weight": torch.ones(hid, device=dev, dtype=torch.bfloat16),
+            "post_attention_layernorm_weight": torch.ones(hid, device=dev, dtype=torch.bfloat16),
+            "q_proj": lin(hid, hid), "k_proj": lin(kv, hid), "v_proj": lin(kv, hid), "o_proj": lin(hid, hid),
+            "gate_proj": lin(ffn, hid), "up_proj": lin(ffn, hid), "down_proj": lin(hid, ffn)}
+
+
+def timed_loop(fn, arg_sets, iters, warm=3):
+    """Average device time per call of fn over rotating argument sets (CUDA events on the
+    current stream, back-to-back launches)."""
+    for i in range(warm):
+        fn(*arg_sets[i % len(arg_sets)])
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fn(*arg_sets[i % len(arg_sets)])
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e-3 / iters
+
+
+def bench_ops(dev, rank, world, peaks, src):
+    """Each fused op alone at the configuration sizes, sharded over the ranks; inputs rotate
+    through sets whose total size exceeds the 126 MB L2."""
+    from custom_cuda_kernals_b200 import dist
+    from custom_cuda_kernals_b200.kernels.fp8_quant import fp8_quant
+    from custom_cuda_kernals_b200.kernels.linear_cross_entropy import lce_loss_from_stats, lce_row_stats
+    from custom_cuda_kernals_b200.kernels.matmul_add_bias import matmul_add_bias, matmul_add_bias_fp8
+    from custom_cuda_kernals_b200.kernels.rmsnorm_residual import rmsnorm_residual
+    from custom_cuda_kernals_b200.kernels.rope import rope
+    from custom_cuda_kernals_b200.kernels.swiglu import swiglu
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(77 + rank)
+
+    def rn(*shape, dtype=bf, scale=1.0):
+        return (scale * torch.randn(*shape, device=dev, generator=g)).to(dtype)
+
+    out = {}
+
+    def record(name, bound, work, seconds, note):
+        seconds = dist.max_over_ranks(seconds, dev)
+        if bound == "hbm":
+            ach, peak, unit = work * world / seconds / 1e9, peaks["hbm_gbs"] * world, "GB/s"
+        else:
+            ach, peak, unit = work * world / seconds / 1e12, peaks["bf16_tflops"] * world, "TFLOP/s"
+        out[name] = {"bound": bound, "achieved": round(ach, 1), "peak": round(peak, 1), "unit": unit,
+                     "frac": round(ach / peak, 4), "us_per_launch": round(seconds * 1e6, 2),
+                     "peak_source": src, "shard": note}
+
+    # config 1: rmsnorm+residual fp32 [2048, 4096], rows sharded
+    r0, r1 = dist.row_range(2048, rank, world)
+    rows = r1 - r0
+    sets = [(rn(rows, 4096, dtype=torch.float32), rn(rows, 4096, dtype=torch.float32),
+             1 + 0.1 * rn(4096, dtype=torch.float32), 1e-5) for _ in range(max(6, 6 * world))]
+    record("rmsnorm_residual_fp32", "hbm", rows * 4096 * 4 * 4, timed_loop(rmsnorm_residual, sets, 120),
+           f"rows {rows} of 2048")
+    del sets
+    # config 2a: swiglu bf16 [8192, 14336]
+    r0, r1 = dist.row_range(8192, rank, world)
+    rows = r1 - r0
+    sets = [(rn(rows, 14336), rn(rows, 14336)) for _ in range(2 if world == 1 else 3)]
+    record("swiglu_bf16", "hbm", rows * 14336 * 2 * 3, timed_loop(swiglu, sets, 30), f"rows {rows} of 8192")
+    del sets
+    # config 2b: rope bf16 q [4,2048,32,128], k [4,2048,8,128]; sequences sharded, then positions
+    if world <= 4:
+        b, s0, s1 = 4 // world, 0, 2048
+    else:
+        b, per = 1, 2048 * 4 // world
+        s0 = (rank % (world // 4)) * per
+        s1 = s0 + per
+    from custom_cuda_kernals_b200.llama_block import rope_tables
+    cos, sin = rope_tables(2048, 128, 500000.0, dev)
+    cos, sin = cos[s0:s1].contiguous(), sin[s0:s1].contiguous()
+    sets = [(rn(b, s1 - s0, 32, 128), rn(b, s1 - s0, 8, 128), cos, sin) for _ in range(6)]
+    record("rope_bf16", "hbm", b * (s1 - s0) * 40 * 128 * 2 * 2, timed_loop(rope, sets, 120),
+           f"batch {b} x positions {s0}..{s1}")
+    del sets
+    # config 2c: per-token fp8 quant bf16 [8192, 4096] with 0.1 % outliers x50
+    r0, r1 = dist.row_range(8192, rank, world)
+    rows = r1 - r0
+    sets = []
+    for _ in range(max(6, 3 * world)):
+        x = torch.randn(rows, 4096, device=dev, generator=g)
+        hot = torch.rand(rows, 4096, device=dev, generator=g) < 1e-3
+        sets.append((torch.where(hot, x * 50, x).to(bf), "e4m3", "token"))
+    record("fp8_quant_token_bf16", "hbm", rows * 4096 * 3, timed_loop(fp8_quant, sets, 120), f"rows {rows} of 8192")
+    record("fp8_quant_block_bf16", "hbm", rows * 4096 * 3,
+           timed_loop(fp8_quant, [(s[0], "e4m3", "block") for s in sets], 120), f"rows {rows} of 8192")
+    # config 3: matmul_add_bias bf16 8192 x 4096 x 14336, output columns sharded
+    n0, n1 = dist.column_range(14336, rank, world)
+    a, w, bias = rn(8192, 4096), rn(n1 - n0, 4096, scale=0.02), rn(n1 - n0, scale=0.02)
+    record("matmul_add_bias_bf16", "tensor", 2 * 8192 * 4096 * (n1 - n0),
+           timed_loop(matmul_add_bias, [(a, w, bias)], 20), f"columns {n1 - n0} of 14336")
+    a8, a_s = fp8_quant(sets[0][0], "e4m3", "token") if rows == 8192 else fp8_quant(a, "e4m3", "token")
+    w8, w_s = fp8_quant(w, "e4m3", "token")
+    record("matmul_add_bias_fp8", "tensor", 2 * 8192 * 4096 * (n1 - n0),
+           timed_loop(matmul_add_bias_fp8, [(a8, a_s, w8, w_s, bias)], 20), f"columns {n1 - n0} of 14336")
+    out["matmul_add_bias_fp8"]["note"] = "fraction is against the bf16 dense peak"
+    del sets, a, w, a8, w8
+    # config 5: linear cross entropy 16384 x 4096 x 128256, vocabulary sharded + one all-gather
+    v0, v1 = dist.vocab_range(128256, rank, world)
+    h = rn(16384, 4096)
+    wv = rn(v1 - v0, 4096, scale=0.02)
+    gt = torch.Generator(device=dev).manual_seed(5)      # same labels on every rank
+    t = torch.randint(0, 128256, (16384,), device=dev, generator=gt)
+    t = torch.where(torch.rand(16384, device=dev, generator=gt) < 0.05, torch.full_like(t, -100), t)
+
+    def lce(hh, ww, tt):
+        return lce_loss_from_stats(dist.gather_row_stats(lce_row_stats(hh, ww, tt, v0)), tt)
+
+    record("linear_cross_entropy_bf16", "tensor", 2 * 16384 * 4096 * (v1 - v0),
+           timed_loop(lce, [(h, wv, t)], 4 if world == 1 else 8, warm=2), f"vocab rows {v1 - v0} of 128256")
+    return out
+
+
+def cpu_block_step(x, w):
+    from oracle import ops
+    with torch.no_grad():
+        return ops.llama_block(x, w, CFG["n_heads"], CFG["n_kv_heads"], CFG["eps"], CFG["theta"])
+
+
+def cpu_sample_tokens_per_s(w_cpu, steps, warm, seed=7):
+    """The oracle block on batch 1 x seq 2048 (1/8 of one step's tokens) on all host cores."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(seed)
+    x = (0.02 * torch.randn(1, SEQ, CFG["hidden"], generator=g)).to(torch.bfloat16)
+    for _ in range(warm):
+        cpu_block_step(x, w_cpu)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_block_step(x, w_cpu)
+    dt = (time.perf_counter() - t0) / steps
+    return SEQ / dt, dt
+
+
+def cpu_weights(seed=1006):
+    from oracle import workloads
+    return workloads.block_weights(dict(workloads.LLAMA3_8B))
+
+
+def base_line(args, world, value, ms):
+    return {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "Llama-3-8B decoder block forward, batch 8 x seq 2048 (BASELINE configs[3])",
+                       "global_batch": BATCH, "seq_len": SEQ, "hidden": CFG["hidden"], "ffn": CFG["ffn"],
+                       "heads": "32q/8kv x 128", "parallelism": f"token-dp{world} (sequences sharded, weights replicated)",
+                       "l2": "working set (436 MB weights + >1 GB activations) exceeds the 126 MB L2"}}
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    w = cpu_weights()
+    tps, dt = cpu_sample_tokens_per_s(w, steps, warm)
+    line = base_line(args, world, tps, dt * 1e3)
+    line.update({"impl": "reference", "scaling": "strong",
+                 "cpu_baseline": {"value": tps, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                                  "sample": f"oracle block (eager baselines' op chain) on batch 1 x seq {SEQ}, "
+                                            f"{steps} timed step(s) after {warm} warm-up; tokens/s = {SEQ} / step time"},
+                 "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                 })
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- our arm
+def run_ours(args, rank, world, local):
+    from custom_cuda_kernals_b200 import dist
+    from custom_cuda_kernals_b200.llama_block import LlamaBlock, OpTimer
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peaks, src = load_peaks()
+    b0, b1 = dist.sequence_range(BATCH, rank, world)
+    nb = b1 - b0
+    weights = device_weights(dev)
+    block = LlamaBlock(weights, CFG["n_heads"], CFG["n_kv_heads"], CFG["eps"], CFG["theta"], SEQ)
+    g = torch.Generator().manual_seed(2006)
+    x_all = (0.02 * torch.randn(BATCH, SEQ, CFG["hidden"], generator=g)).to(torch.bfloat16)
+    x_host = x_all[b0:b1].contiguous().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    x_dev = x_host.to(dev)
+
+    # parity gate on a slice (rank 0): the GPU block against the CPU oracle with the same weights
+    parity = None
+    if rank == 0:
+        from oracle import ops
+        w_cpu = {k: v.cpu() for k, v in weights.items()}
+        xs = x_all[:1, :256]
+        want = cpu_block_step(xs, w_cpu)
+        got = block(xs.to(dev)).cpu()
+        err = (got.float() - want.float()).abs()
+        bad = float((err > 2e-2 + 1e-2 * want.float().abs()).float().mean())
+        parity = {"sample": "batch 1 x seq 256 vs CPU oracle", "max_abs_err": float(err.max()),
+                  "outside_rtol1e-2_atol2e-2": bad, "ok": bad <= 1e-5}
+        log("parity", parity)
+        del ops
+
+    with torch.no_grad():
+        for _ in range(max(3, args.warmup)):
+            block(x_dev)
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+
+        timer = OpTimer()
+        with ClockSampler(local) as clocks:
+            torch.cuda.synchronize()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for _ in range(args.steps):
+                block(x_dev, timer=timer)
+            ev1.record()
+            torch.cuda.synchronize()
+            if world > 1:
+                torch.distributed.barrier()
+            secs = dist.max_over_ranks(ev0.elapsed_time(ev1) * 1e-3, dev)
+
+            # end to end: pinned host input in, output back out, every step
+            for _ in range(2):
+                block.forward_host(x_host, out_host)
+            torch.cuda.synchronize()
+            if world > 1:
+                torch.distributed.barrier()
+            ev0.record()
+            for _ in range(args.steps):
+                block.forward_host(x_host, out_host)
+            ev1.record()
+            torch.cuda.synchronize()
+            if world > 1:
+                torch.distributed.barrier()
+            e2e_secs = dist.max_over_ranks(ev0.elapsed_time(ev1) * 1e-3, dev)
+
+    tokens = BATCH * SEQ
+    totals = timer.totals()
+    gemm_ms = dist.max_over_ranks(totals["gemm"]["ms"], dev)
+    gemm_flops = block.gemm_flops(nb * SEQ) * args.steps               # per rank
+    ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops_sustained"]
+    line = base_line(args, world, tokens * args.steps / secs, secs / args.steps * 1e3)
+    line["roofline"] = {"kernel": "gemm_kernel<bf16> (matmul_add_bias, 7 launches per step)", "bound": "tensor",
+                        "achieved": round(ach, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
+                        "traffic": NCU_TRAFFIC_BYTES["gemm"], "peak_source": f"{src} (cuBLAS bf16, sustained)",
+                        "flops_per_launch_avg": gemm_flops // (7 * args.steps),
+                        "us_per_launch_avg": round(gemm_ms * 1e3 / totals["gemm"]["calls"], 1), "per_gpu": True}
+    line["step_breakdown_ms"] = {k: round(v["ms"] / args.steps, 4) for k, v in sorted(totals.items())}
+    line["e2e"] = {"value": tokens * args.steps / e2e_secs, "unit": UNIT,
+                   "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": out_host.numel() * 2 * world,
+                   "ms_per_step": e2e_secs / args.steps * 1e3,
+                   "api": "LlamaBlock.forward_host(pinned x, pinned out): H2D, 11 library kernels + SDPA, D2H"}
+    line["gpu_launches"] = LlamaBlock.LAUNCHES_PER_FORWARD * args.steps * world
+    line["clocks"] = clocks.summary()
+    line["parity"] = parity
+    if not args.skip_ops:
+        line["ops"] = bench_ops(dev, rank, world, peaks, src)
+    if rank == 0 and world == 1:
+        w_cpu = {k: v.cpu() for k, v in weights.items()}
+        tps, dt = cpu_sample_tokens_per_s(w_cpu, 2, 1)
+        line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"CPU oracle block on batch 1 x seq {SEQ} (1/8 of a step), 2 timed steps "
+                                          f"of {dt:.2f} s after 1 warm-up"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+PROFILE_CASES = ("gemm", "gemm_fp8", "lce", "swiglu", "rmsnorm", "rope", "fp8_token", "fp8_block")
+
+
+def run_profile_case(name, launches=3):
+    """A few launches of ONE kernel on a small case (inputs larger than the L2, a few hundred
+    MB on the device) for a profiler capture; prints nothing but a done line."""
+    from custom_cuda_kernals_b200.kernels.fp8_quant import fp8_quant
+    from custom_cuda_kernals_b200.kernels.linear_cross_entropy import linear_cross_entropy
+    from custom_cuda_kernals_b200.kernels.matmul_add_bias import matmul_add_bias, matmul_add_bias_fp8
+    from custom_cuda_kernals_b200.kernels.rmsnorm_residual import rmsnorm_residual
+    from custom_cuda_kernals_b200.kernels.rope import rope
+    from custom_cuda_kernals_b200.kernels.swiglu import swiglu
+    from custom_cuda_kernals_b200.llama_block import rope_tables
+    dev, bf = torch.device("cuda", 0), torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def rn(*shape, dtype=bf, scale=1.0):
+        return (scale * torch.randn(*shape, device=dev, generator=g)).to(dtype)
+
+    if name == "gemm":          # 4096 x 4096 x 8192: 33 + 67 + 67 MB
+        a, w, b = rn(4096, 4096), rn(8192, 4096, scale=0.02), rn(8192, scale=0.02)
+        fn = lambda: matmul_add_bias(a, w, b)
+    elif name == "gemm_fp8":
+        a8, a_s = fp8_quant(rn(4096, 4096), "e4m3", "token")
+        w8, w_s = fp8_quant(rn(16384, 4096, scale=0.02), "e4m3", "token")
+        b = rn(16384, scale=0.02)
+        fn = lambda: matmul_add_bias_fp8(a8, a_s, w8, w_s, b)
+    elif name == "lce":         # 2048 x 4096 x 32064: W 263 MB
+        h, w = rn(2048, 4096), rn(32064, 4096, scale=0.02)
+        t = torch.randint(0, 32064, (2048,), device=dev)
+        fn = lambda: linear_cross_entropy(h, w, t)
+    elif name == "swiglu":      # config 2a at 1/4 of the rows: 3 x 59 MB
+        a, b = rn(2048, 14336), rn(2048, 14336)
+        fn = lambda: swiglu(a, b)
+    elif name == "rmsnorm":     # config 1
+        x, r, w = rn(2048, 4096, dtype=torch.float32), rn(2048, 4096, dtype=torch.float32), rn(4096, dtype=torch.float32)
+        fn = lambda: rmsnorm_residual(x, r, w, 1e-5)
+    elif name == "rope":        # config 2b
+        q, k = rn(4, 2048, 32, 128), rn(4, 2048, 8, 128)
+        cos, sin = rope_tables(2048, 128, 500000.0, dev)
+        fn = lambda: rope(q, k, cos, sin)
+    elif name in ("fp8_token", "fp8_block"):   # config 2c
+        x = rn(8192, 4096)
+        gran = name.split("_")[1]
+        fn = lambda: fp8_quant(x, "e4m3", gran)
+    else:
+        raise SystemExit(f"unknown profile case {name!r}; choose from {PROFILE_CASES}")
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)   # 256 MB written between launches
+    for _ in range(launches):
+        flush.fill_(1.0)
+        fn()
+    torch.cuda.synchronize()
+    print(f"profile case {name}: {launches} launches done", flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-ops", action="store_true", help="only the block step, not the per-op table")
+    ap.add_argument("--profile-case", default=None, help=f"run one small kernel case and exit: {PROFILE_CASES}")
+    args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+        return
+    if args.impl == "reference":
+        rank = int(os.environ.get("RANK", "0"))
+        run_reference(args, rank, int(os.environ.get("WORLD_SIZE", "1")))
+        return
+    from custom_cuda_kernals_b200 import dist
+    rank, world, local = dist.init_from_env()
+    if world != args.gpus and rank == 0:
+        log(f"note: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE")
+    try:
+        run_ours(args, rank, world, local)
+    finally:
+        if torch.distributed.is_initialized():
+            torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -10,7 +10,11 @@
 //     as in the PyTorch baseline (baselines/fp8_quant.py:162-178), so codes and
 //     scales are bit-identical to it.  The reference kernel multiplies by an
 //     approximate reciprocal and is off by one code on ~5e-4 of the elements.
-//     This file must not be compiled with --use_fast_math.
+//     `x / scale` is evaluated as a correctly rounded quotient from the correctly
+//     rounded reciprocal of the (row / tile / tensor-wide) scale and two
+//     FMA residual corrections (struct ExactDiv) - 6 instructions per element
+//     instead of a full division.  This file must not be compiled with
+//     --use_fast_math.
 //   * The row / tile is held in registers between the amax pass and the cast,
 //     so HBM is read once; loads are 16-byte, stores are 16 codes (16 bytes).
 //
@@ -41,9 +45,28 @@ template <bool E5M2>
 __device__ __forceinline__ float scale_of(float amax) {
     return fmaxf(__fdiv_rn(amax, Fmt<E5M2>::kMax), kScaleFloor);
 }
+// a / s, correctly rounded, for a fixed positive finite divisor s.
+// With y = RN(1/s): q0 = RN(a*y) is within 1.5 ulp of a/s; one residual step
+// makes it faithful (within 1 ulp); for a faithful q the residual a - s*q is
+// exact in an FMA and RN(q + r*y) is the correctly rounded quotient (Markstein's
+// theorem).  No intermediate can underflow while the quotient still matters:
+// s >= 1e-12 and |a/s| <= FP8_MAX, and a quotient below 2^-11 becomes a zero code
+// whatever its last bits are.  The sign is taken from `a` so that -0.0 stays -0.0.
+struct ExactDiv {
+    float s, y;
+    __device__ __forceinline__ explicit ExactDiv(float scale) : s(scale), y(__frcp_rn(scale)) {}
+    __device__ __forceinline__ float operator()(float a) const {
+        const float q0 = __fmul_rn(a, y);
+        const float r0 = __fmaf_rn(-s, q0, a);
+        const float q1 = __fmaf_rn(r0, y, q0);
+        const float r1 = __fmaf_rn(-s, q1, a);
+        return copysignf(__fmaf_rn(r1, y, q1), a);
+    }
+};
+
 template <bool E5M2>
 __device__ __forceinline__ uint8_t quant1(float x, float scale) {
-    return static_cast<uint8_t>(Fmt<E5M2>::cvt2(__fdiv_rn(x, scale), 0.0f) & 0xffu);
+    return static_cast<uint8_t>(Fmt<E5M2>::cvt2(ExactDiv(scale)(x), 0.0f) & 0xffu);
 }
 
 // A "unit" is 16 consecutive elements: 16*sizeof(T) bytes in, 16 bytes out.
@@ -66,11 +89,12 @@ template <typename T> struct Unit {
     __device__ __forceinline__ Vec16 quantise(float scale) const {
         Vec16 out;
         float f[16];
+        const ExactDiv div(scale);
 #pragma unroll
         for (int i = 0; i < kVecs; ++i)
 #pragma unroll
             for (int e = 0; e < Store<T>::kPerVec; ++e)
-                f[i * Store<T>::kPerVec + e] = __fdiv_rn(Store<T>::get(v[i], e), scale);
+                f[i * Store<T>::kPerVec + e] = div(Store<T>::get(v[i], e));
 #pragma unroll
         for (int w = 0; w < 4; ++w)
             out.w[w] = Fmt<E5M2>::cvt2(f[4 * w], f[4 * w + 1]) | (Fmt<E5M2>::cvt2(f[4 * w + 2], f[4 * w + 3]) << 16);

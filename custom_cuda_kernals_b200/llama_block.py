@@ -1,0 +1,146 @@
+"""Llama-3 style decoder block forward built from this library's ops.
+
+Host-side mirror of the reference's integration example
+(examples/llama_block.py:83-204, ``CustomCUDA_LlamaBlock``): pre-norm, GQA,
+RoPE, SwiGLU FFN, with the same op order
+
+    norm -> q/k/v projections -> rope -> causal attention -> o_proj
+         -> norm(+residual) -> gate/up -> swiglu -> down -> + residual
+
+The reference swaps in its three bandwidth-bound kernels and leaves every
+projection to ``nn.Linear`` (cuBLAS); here the seven projections also run on this
+library's tcgen05 GEMM (``matmul_add_bias`` with no bias).  The attention core
+stays ``torch.nn.functional.scaled_dot_product_attention`` as in the reference.
+Forward only, no autograd.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.nn.functional as F
+
+from .kernels.matmul_add_bias import matmul_add_bias
+from .kernels.rmsnorm_residual import rmsnorm_residual
+from .kernels.rope import rope
+from .kernels.swiglu import swiglu
+
+__all__ = ["LlamaBlock", "rope_tables", "OpTimer", "PARAM_NAMES"]
+
+PARAM_NAMES = ("input_layernorm_weight", "post_attention_layernorm_weight", "q_proj", "k_proj", "v_proj",
+               "o_proj", "gate_proj", "up_proj", "down_proj")
+
+
+def rope_tables(seq_len: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 ``cos, sin [seq_len, head_dim/2]`` (baselines/rope.py:103-115)."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    angle = torch.outer(torch.arange(seq_len, dtype=torch.float32, device=device), inv_freq)
+    return angle.cos().contiguous(), angle.sin().contiguous()
+
+
+class OpTimer:
+    """Optional per-op CUDA-event timing inside a forward pass.
+
+    ``forward(x, timer=t)`` records an event pair around every op on the current
+    stream; ``t.totals()`` (after a synchronize) returns milliseconds and call
+    counts per op kind.  Recording costs about a microsecond per event.
+    """
+
+    def __init__(self):
+        self.spans: list[tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
+
+    def run(self, kind: str, fn: Callable, *args, **kwargs):
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = fn(*args, **kwargs)
+        b.record()
+        self.spans.append((kind, a, b))
+        return out
+
+    def totals(self) -> dict[str, dict[str, float]]:
+        out: dict[str, dict[str, float]] = {}
+        for kind, a, b in self.spans:
+            slot = out.setdefault(kind, {"ms": 0.0, "calls": 0})
+            slot["ms"] += a.elapsed_time(b)
+            slot["calls"] += 1
+        return out
+
+
+class _NoTimer:
+    @staticmethod
+    def run(kind, fn, *args, **kwargs):
+        return fn(*args, **kwargs)
+
+
+class LlamaBlock:
+    """One decoder block; ``weights`` maps PARAM_NAMES to CUDA tensors
+    (projections as ``[out_features, in_features]``, the nn.Linear layout)."""
+
+    #: kernels of this library launched per forward call (2 norms, 7 GEMMs, rope, swiglu)
+    LAUNCHES_PER_FORWARD = 11
+
+    def __init__(self, weights: dict[str, torch.Tensor], n_heads: int = 32, n_kv_heads: int = 8,
+                 eps: float = 1e-5, theta: float = 500000.0, max_seq_len: int = 2048):
+        missing = [n for n in PARAM_NAMES if n not in weights]
+        if missing:
+            raise ValueError(f"missing block parameters: {missing}")
+        self.w = {n: weights[n] for n in PARAM_NAMES}
+        for name, t in self.w.items():
+            if not t.is_cuda or not t.is_contiguous():
+                raise ValueError(f"parameter '{name}' must be a contiguous CUDA tensor")
+        self.hidden = self.w["q_proj"].shape[1]
+        self.n_heads, self.n_kv_heads = n_heads, n_kv_heads
+        self.head_dim = self.w["q_proj"].shape[0] // n_heads
+        self.eps = eps
+        dev = self.w["q_proj"].device
+        self.cos, self.sin = rope_tables(max_seq_len, self.head_dim, theta, dev)
+
+    def forward(self, x: torch.Tensor, timer: OpTimer | None = None, pos_offset: int = 0) -> torch.Tensor:
+        """x ``[B, S, hidden]`` -> ``[B, S, hidden]``.  ``pos_offset`` is the position of
+        ``x[:, 0]`` when the caller holds only a slice of each sequence's prefix-free chunk
+        (only meaningful for a single chunk starting at that offset: attention is causal
+        within the chunk)."""
+        t = timer if timer is not None else _NoTimer
+        w = self.w
+        b, s, hid = x.shape
+        if pos_offset + s > self.cos.shape[0]:
+            raise ValueError(f"sequence positions {pos_offset}..{pos_offset + s - 1} exceed the RoPE table "
+                             f"({self.cos.shape[0]} rows)")
+        x2 = x.view(b * s, hid)
+        zero = t.run("fill", torch.zeros_like, x2)
+        h, res = t.run("rmsnorm", rmsnorm_residual, x2, zero, w["input_layernorm_weight"], self.eps)
+        q = t.run("gemm", matmul_add_bias, h, w["q_proj"]).view(b, s, self.n_heads, self.head_dim)
+        k = t.run("gemm", matmul_add_bias, h, w["k_proj"]).view(b, s, self.n_kv_heads, self.head_dim)
+        v = t.run("gemm", matmul_add_bias, h, w["v_proj"]).view(b, s, self.n_kv_heads, self.head_dim)
+        q, k = t.run("rope", rope, q, k, self.cos[pos_offset:pos_offset + s], self.sin[pos_offset:pos_offset + s])
+        att = t.run("sdpa", F.scaled_dot_product_attention, q.transpose(1, 2), k.transpose(1, 2),
+                    v.transpose(1, 2), is_causal=True, enable_gqa=self.n_heads != self.n_kv_heads)
+        att = t.run("copy", lambda a: a.transpose(1, 2).contiguous().view(b * s, hid), att)
+        att = t.run("gemm", matmul_add_bias, att, w["o_proj"])
+        h2, res2 = t.run("rmsnorm", rmsnorm_residual, att, res, w["post_attention_layernorm_weight"], self.eps)
+        gate = t.run("gemm", matmul_add_bias, h2, w["gate_proj"])
+        up = t.run("gemm", matmul_add_bias, h2, w["up_proj"])
+        act = t.run("swiglu", swiglu, gate, up)
+        mlp = t.run("gemm", matmul_add_bias, act, w["down_proj"])
+        out = t.run("add", torch.add, mlp, res2)
+        return out.view(b, s, hid)
+
+    __call__ = forward
+
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
+        """Host-buffer entry point: ``x_host`` / ``out_host`` are pinned CPU tensors
+        ``[B, S, hidden]``; the input is copied to the device, the block runs, and the
+        result is copied back, all on the current stream.  Returns ``out_host`` after
+        synchronising that stream."""
+        dev = self.w["q_proj"].device
+        xd = x_host.to(dev, non_blocking=True)
+        out_host.copy_(self.forward(xd), non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        return out_host
+
+    def gemm_flops(self, tokens: int) -> int:
+        """2*M*K*N summed over the seven projections for ``tokens`` rows."""
+        return sum(2 * tokens * self.w[n].shape[0] * self.w[n].shape[1]
+                   for n in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"))

@@ -1,0 +1,87 @@
+"""CPU: the multi-rank host logic - partition arithmetic, and the vocabulary-parallel
+statistics exchange run as two gloo ranks (no GPU involved; the per-rank statistics
+come from the oracle, the collective and the merge contract are what is tested)."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as td
+import torch.multiprocessing as mp
+
+from custom_cuda_kernals_b200 import dist
+from oracle import cases, ops
+
+
+def test_ranges_cover_and_align():
+    for total, world, mult in [(128256, 8, 128), (128256, 4, 128), (1009, 3, 128), (14336, 8, 8), (10, 4, 1), (3, 8, 1)]:
+        spans = [dist._even_range(total, r, world, mult) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == total
+        for (a, b), (c, d) in zip(spans[:-1], spans[1:]):
+            assert b == c and a <= b and a % mult == 0
+        sizes = [b - a for a, b in spans]
+        assert max(sizes) - min(sizes) <= 2 * mult
+
+
+def test_vocab_range_llama3_at_8_ranks():
+    spans = [dist.vocab_range(128256, r, 8) for r in range(8)]
+    tiles = [(b - a) // 128 for a, b in spans]
+    assert sorted(set(tiles)) == [125, 126] and sum(tiles) == 1002
+
+
+def test_column_and_sequence_ranges():
+    assert [dist.column_range(14336, r, 8) for r in (0, 7)] == [(0, 1792), (12544, 14336)]
+    assert [dist.sequence_range(8, r, 4) for r in range(4)] == [(0, 2), (2, 4), (4, 6), (6, 8)]
+    with pytest.raises(ValueError):
+        dist.sequence_range(8, 0, 3)
+    with pytest.raises(ValueError):
+        dist.row_range(8, 4, 4)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    r, w, _ = dist.init_from_env(timeout_s=60)
+    assert (r, w) == (rank, world) and td.get_backend() == "gloo"
+    case = cases.by_name(cases.LCE_CASES, "with_ignored_float32")
+    h, wt, t = cases.lce_inputs(case)                       # replicated inputs, same seed on every rank
+    v0, v1 = dist.vocab_range(case.vocab_size, rank, world)
+    mx, sm, tg = ops.lce_partials(h, wt[v0:v1], t, v0)      # stand-in for the GPU kernel's row statistics
+    stats = torch.stack([mx, sm, tg]).float()
+    gathered = dist.gather_row_stats(stats)                 # the one collective
+    assert gathered.shape == (world, 3, case.n_tokens)
+    per_row = ops.lce_merge([(g[0].double(), g[1].double(), g[2].double()) for g in gathered])
+    keep = t != -100
+    loss = per_row[keep].sum() / keep.sum()
+    slowest = dist.max_over_ranks(float(rank + 1))
+    torch.save({"loss": loss, "slowest": slowest, "range": (v0, v1)}, os.path.join(out_dir, f"r{rank}.pt"))
+    td.destroy_process_group()
+
+
+def test_vocab_parallel_exchange_two_gloo_ranks(tmp_path):
+    world = 2
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    outs = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
+    case = cases.by_name(cases.LCE_CASES, "with_ignored_float32")
+    want = ops.linear_cross_entropy_fp64(*cases.lce_inputs(case))
+    for o in outs:
+        torch.testing.assert_close(o["loss"], want, rtol=1e-5, atol=1e-6)
+        assert o["slowest"] == float(world)
+    assert outs[0]["loss"] == outs[1]["loss"]               # every rank computes the identical loss
+    assert outs[0]["range"][1] == outs[1]["range"][0]
+
+
+def test_single_process_needs_no_group():
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    assert dist.init_from_env() == (0, 1, 0)
+    s = torch.zeros(3, 5)
+    assert dist.gather_row_stats(s).shape == (1, 3, 5)
+    assert dist.max_over_ranks(3.5) == 3.5

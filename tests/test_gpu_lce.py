@@ -28,10 +28,16 @@ def test_lce_cases(case):
     if case.name.startswith("all_ignored"):
         assert torch.isnan(got).all() if case.reduction == "mean" else True
         return
-    # the reference's own bar: against the eager loss in the storage dtype
+    # the reference's own bar: against the eager loss in the storage dtype.  On the CPU a 16-bit
+    # F.cross_entropy also accumulates its mean in 16 bits, so 16-bit cases are compared row by row.
     if not heavy:
-        eager = ops.linear_cross_entropy(h, w, t, reduction=case.reduction).float()
-        torch.testing.assert_close(got.cpu(), eager, rtol=TOL[case.dtype][0], atol=TOL[case.dtype][1])
+        if case.dtype == torch.float32 or case.reduction == "none":
+            eager = ops.linear_cross_entropy(h, w, t, reduction=case.reduction).float()
+            torch.testing.assert_close(got.cpu(), eager, rtol=TOL[case.dtype][0], atol=TOL[case.dtype][1])
+        else:
+            rows = linear_cross_entropy(*to_dev(h, w, t), reduction="none").cpu()
+            eager = ops.linear_cross_entropy(h, w, t, reduction="none").float()
+            torch.testing.assert_close(rows, eager, rtol=TOL[case.dtype][0], atol=TOL[case.dtype][1])
     # the stricter bar: fp32 logits never rounded, so 1e-4 relative against fp64 on the same inputs
     torch.testing.assert_close(got.cpu().double(), want64, rtol=1e-4, atol=1e-6)
     assert device_status_clean(got)
