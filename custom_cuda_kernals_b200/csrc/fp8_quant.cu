@@ -16,9 +16,14 @@
 //     instead of a full division.  This file must not be compiled with
 //     --use_fast_math.
 //   * The row / tile is held in registers between the amax pass and the cast,
-//     so HBM is read once; loads are 16-byte, stores are 16 codes (16 bytes).
+//     so HBM is read once.  Every load is one 16-byte vector per lane with
+//     consecutive lanes on consecutive vectors (a warp reads 512 contiguous
+//     bytes per instruction); the codes of one vector (8 for 16-bit inputs,
+//     4 for fp32) go out as one 8- or 4-byte store, again contiguous per warp.
 //
 // HBM-bound: M*N*(sizeof(T) + 1) bytes per launch (+ scales).
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace cck {
@@ -54,7 +59,12 @@ __device__ __forceinline__ float scale_of(float amax) {
 // whatever its last bits are.  The sign is taken from `a` so that -0.0 stays -0.0.
 struct ExactDiv {
     float s, y;
-    __device__ __forceinline__ explicit ExactDiv(float scale) : s(scale), y(__frcp_rn(scale)) {}
+    __device__ static __forceinline__ ExactDiv make(float scale) {
+        ExactDiv d;
+        d.s = scale;
+        d.y = __frcp_rn(scale);
+        return d;
+    }
     __device__ __forceinline__ float operator()(float a) const {
         const float q0 = __fmul_rn(a, y);
         const float r0 = __fmaf_rn(-s, q0, a);
@@ -65,40 +75,44 @@ struct ExactDiv {
 };
 
 template <bool E5M2>
-__device__ __forceinline__ uint8_t quant1(float x, float scale) {
-    return static_cast<uint8_t>(Fmt<E5M2>::cvt2(ExactDiv(scale)(x), 0.0f) & 0xffu);
+__device__ __forceinline__ uint8_t quant1(float x, const ExactDiv& div) {
+    return static_cast<uint8_t>(Fmt<E5M2>::cvt2(div(x), 0.0f) & 0xffu);
 }
 
-// A "unit" is 16 consecutive elements: 16*sizeof(T) bytes in, 16 bytes out.
-template <typename T> struct Unit {
-    static constexpr int kVecs = 16 / Store<T>::kPerVec;  // Vec16 per unit: 2 (16-bit) or 4 (fp32)
-    Vec16 v[kVecs];
-    __device__ __forceinline__ void load(const T* p) {
+// One 16-byte vector of input -> kPer codes (8 bytes for 16-bit inputs, 4 for fp32).
+template <typename T> struct Chunk {
+    static constexpr int kPer = Store<T>::kPerVec;
+    // largest magnitude in the vector
+    __device__ static __forceinline__ float amax(const Vec16& v) {
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+            __nv_bfloat162 m = __float2bfloat162_rn(0.0f);
 #pragma unroll
-        for (int i = 0; i < kVecs; ++i) v[i] = ld_stream(p + i * Store<T>::kPerVec);
-    }
-    __device__ __forceinline__ float amax() const {
-        float m = 0.0f;
+            for (int i = 0; i < 4; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&v.w[i])));
+            return fmaxf(__low2float(m), __high2float(m));
+        } else if constexpr (std::is_same<T, __half>::value) {
+            __half2 m = __float2half2_rn(0.0f);
 #pragma unroll
-        for (int i = 0; i < kVecs; ++i)
+            for (int i = 0; i < 4; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __half2*>(&v.w[i])));
+            return fmaxf(__low2float(m), __high2float(m));
+        } else {
+            float m = 0.0f;
 #pragma unroll
-            for (int e = 0; e < Store<T>::kPerVec; ++e) m = fmaxf(m, fabsf(Store<T>::get(v[i], e)));
-        return m;
+            for (int i = 0; i < 4; ++i) m = fmaxf(m, fabsf(__uint_as_float(v.w[i])));
+            return m;
+        }
     }
     template <bool E5M2>
-    __device__ __forceinline__ Vec16 quantise(float scale) const {
-        Vec16 out;
-        float f[16];
-        const ExactDiv div(scale);
+    __device__ static __forceinline__ void quantise_store(const Vec16& v, const ExactDiv& div, uint8_t* dst) {
+        float f[kPer];
 #pragma unroll
-        for (int i = 0; i < kVecs; ++i)
-#pragma unroll
-            for (int e = 0; e < Store<T>::kPerVec; ++e)
-                f[i * Store<T>::kPerVec + e] = div(Store<T>::get(v[i], e));
-#pragma unroll
-        for (int w = 0; w < 4; ++w)
-            out.w[w] = Fmt<E5M2>::cvt2(f[4 * w], f[4 * w + 1]) | (Fmt<E5M2>::cvt2(f[4 * w + 2], f[4 * w + 3]) << 16);
-        return out;
+        for (int e = 0; e < kPer; ++e) f[e] = div(Store<T>::get(v, e));
+        const uint32_t w0 = Fmt<E5M2>::cvt2(f[0], f[1]) | (Fmt<E5M2>::cvt2(f[2], f[3]) << 16);
+        if constexpr (kPer == 8) {
+            const uint32_t w1 = Fmt<E5M2>::cvt2(f[4], f[5]) | (Fmt<E5M2>::cvt2(f[6], f[7]) << 16);
+            st_stream8(dst, w0, w1);
+        } else {
+            asm volatile("st.global.cs.u32 [%0], %1;" :: "l"(dst), "r"(w0) : "memory");
+        }
     }
 };
 
@@ -115,32 +129,41 @@ __device__ __forceinline__ float cta_max_dyn(float v, float* slots) {
 }
 
 // ------------------------------------------------------------------ token granularity
-template <typename T, bool E5M2, int UPT>
+// One CTA per row; thread t owns vectors t, t + blockDim, ... (VPT of them, in registers).
+template <typename T, bool E5M2, int VPT>
 __global__ void __launch_bounds__(1024)
 fp8_token_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, float* __restrict__ scale,
-                 int64_t n, int units) {
+                 int64_t n, int n_vec) {
+    constexpr int kPer = Store<T>::kPerVec;
     __shared__ float slots[32];
     const int64_t row = blockIdx.x;
     const T* xr = x + row * n;
     uint8_t* cr = codes + row * n;
-    Unit<T> u[UPT];
+    Vec16 v[VPT];
+    const bool full = static_cast<int>(blockDim.x) * VPT == n_vec;   // no ragged last pass (the usual case)
     float m = 0.0f;
+    if (full) {
 #pragma unroll
-    for (int j = 0; j < UPT; ++j) {
-        const int i = threadIdx.x + j * blockDim.x;
-        if (i < units) u[j].load(xr + static_cast<int64_t>(i) * 16);
-    }
+        for (int j = 0; j < VPT; ++j) v[j] = ld_stream(xr + static_cast<int64_t>(threadIdx.x + j * blockDim.x) * kPer);
 #pragma unroll
-    for (int j = 0; j < UPT; ++j) {
-        const int i = threadIdx.x + j * blockDim.x;
-        if (i < units) m = fmaxf(m, u[j].amax());
+        for (int j = 0; j < VPT; ++j) m = fmaxf(m, Chunk<T>::amax(v[j]));
+    } else {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < n_vec) v[j] = ld_stream(xr + static_cast<int64_t>(i) * kPer);
+        }
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+            if (static_cast<int>(threadIdx.x + j * blockDim.x) < n_vec) m = fmaxf(m, Chunk<T>::amax(v[j]));
     }
     const float sc = scale_of<E5M2>(cta_max_dyn(m, slots));
     if (threadIdx.x == 0) scale[row] = sc;
+    const ExactDiv div = ExactDiv::make(sc);
 #pragma unroll
-    for (int j = 0; j < UPT; ++j) {
+    for (int j = 0; j < VPT; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
-        if (i < units) st_stream(cr + static_cast<int64_t>(i) * 16, u[j].template quantise<E5M2>(sc));
+        if (full || i < n_vec) Chunk<T>::template quantise_store<E5M2>(v[j], div, cr + static_cast<int64_t>(i) * kPer);
     }
 }
 
@@ -156,38 +179,46 @@ fp8_token_generic_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, f
     for (int64_t c = threadIdx.x; c < n; c += blockDim.x) m = fmaxf(m, fabsf(Store<T>::load1(xr + c)));
     const float sc = scale_of<E5M2>(cta_max_dyn(m, slots));
     if (threadIdx.x == 0) scale[row] = sc;
+    const ExactDiv div = ExactDiv::make(sc);
     for (int64_t c = threadIdx.x; c < n; c += blockDim.x)
-        codes[row * n + c] = quant1<E5M2>(Store<T>::load1(xr + c), sc);
+        codes[row * n + c] = quant1<E5M2>(Store<T>::load1(xr + c), div);
 }
 
 // ------------------------------------------------------------------ block granularity
-// One CTA of 256 threads per 128x128 tile: 8 units per tile row, 4 units per thread.
+// One CTA of 256 threads per 128x128 tile; a tile row is 128/kPer vectors, so a warp
+// reads whole 256-byte (16-bit) or 512-byte (fp32) row segments.
 template <typename T, bool E5M2>
 __global__ void __launch_bounds__(256)
 fp8_block_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, float* __restrict__ scale,
                  int64_t m, int64_t n) {
+    constexpr int kPer = Store<T>::kPerVec;
+    constexpr int kVecPerRow = kTile / kPer;               // 16 or 32
+    constexpr int kVpt = kTile * kVecPerRow / 256;         // 8 or 16
     __shared__ float slots[32];
     const int64_t r0 = static_cast<int64_t>(blockIdx.y) * kTile, c0 = static_cast<int64_t>(blockIdx.x) * kTile;
-    Unit<T> u[4];
-    bool live[4];
-    int64_t off[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int id = threadIdx.x + j * 256;   // 0..1023
-        const int64_t r = r0 + (id >> 3), c = c0 + (id & 7) * 16;
-        live[j] = r < m && c < n;               // n % 16 == 0 on this path
-        off[j] = r * n + c;
-        if (live[j]) u[j].load(x + off[j]);
-    }
+    Vec16 v[kVpt];
     float mx = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-        if (live[j]) mx = fmaxf(mx, u[j].amax());
+    for (int j = 0; j < kVpt; ++j) {
+        const int id = threadIdx.x + j * 256;
+        const int64_t r = r0 + id / kVecPerRow, c = c0 + (id % kVecPerRow) * kPer;
+        if (r < m && c < n) v[j] = ld_stream(x + r * n + c);   // n % kPer == 0 on this path
+    }
+#pragma unroll
+    for (int j = 0; j < kVpt; ++j) {
+        const int id = threadIdx.x + j * 256;
+        const int64_t r = r0 + id / kVecPerRow, c = c0 + (id % kVecPerRow) * kPer;
+        if (r < m && c < n) mx = fmaxf(mx, Chunk<T>::amax(v[j]));
+    }
     const float sc = scale_of<E5M2>(cta_max_dyn(mx, slots));
     if (threadIdx.x == 0) scale[static_cast<int64_t>(blockIdx.y) * gridDim.x + blockIdx.x] = sc;
+    const ExactDiv div = ExactDiv::make(sc);
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-        if (live[j]) st_stream(codes + off[j], u[j].template quantise<E5M2>(sc));
+    for (int j = 0; j < kVpt; ++j) {
+        const int id = threadIdx.x + j * 256;
+        const int64_t r = r0 + id / kVecPerRow, c = c0 + (id % kVecPerRow) * kPer;
+        if (r < m && c < n) Chunk<T>::template quantise_store<E5M2>(v[j], div, codes + r * n + c);
+    }
 }
 
 template <typename T, bool E5M2>
@@ -203,9 +234,10 @@ fp8_block_generic_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, f
     }
     const float sc = scale_of<E5M2>(cta_max_dyn(mx, slots));
     if (threadIdx.x == 0) scale[static_cast<int64_t>(blockIdx.y) * gridDim.x + blockIdx.x] = sc;
+    const ExactDiv div = ExactDiv::make(sc);
     for (int id = threadIdx.x; id < kTile * kTile; id += 256) {
         const int64_t r = r0 + (id >> 7), c = c0 + (id & 127);
-        if (r < m && c < n) codes[r * n + c] = quant1<E5M2>(Store<T>::load1(x + r * n + c), sc);
+        if (r < m && c < n) codes[r * n + c] = quant1<E5M2>(Store<T>::load1(x + r * n + c), div);
     }
 }
 
@@ -222,11 +254,8 @@ fp8_amax_kernel(const T* __restrict__ x, int32_t* __restrict__ amax_bits, int64_
     int64_t done = 0;
     if (vec_ok) {
         const int64_t n_vec = total / kPer;
-        for (int64_t i = tid; i < n_vec; i += stride) {
-            const Vec16 v = ld_cached(x + i * kPer);   // default policy: the cast pass re-reads it from L2
-#pragma unroll
-            for (int e = 0; e < kPer; ++e) m = fmaxf(m, fabsf(Store<T>::get(v, e)));
-        }
+        for (int64_t i = tid; i < n_vec; i += stride)
+            m = fmaxf(m, Chunk<T>::amax(ld_cached(x + i * kPer)));   // default policy: the cast pass re-reads it from L2
         done = n_vec * kPer;
     }
     for (int64_t i = done + tid; i < total; i += stride) m = fmaxf(m, fabsf(Store<T>::load1(x + i)));
@@ -239,21 +268,20 @@ template <typename T, bool E5M2>
 __global__ void __launch_bounds__(256)
 fp8_cast_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, float* __restrict__ scale,
                 const int32_t* __restrict__ amax_bits, int64_t total, bool vec_ok) {
+    constexpr int kPer = Store<T>::kPerVec;
     const float sc = scale_of<E5M2>(__int_as_float(*amax_bits));
+    const ExactDiv div = ExactDiv::make(sc);
     const int64_t tid = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
     if (tid == 0) scale[0] = sc;
     int64_t done = 0;
     if (vec_ok) {
-        const int64_t units = total / 16;
-        for (int64_t i = tid; i < units; i += stride) {
-            Unit<T> u;
-            u.load(x + i * 16);
-            st_stream(codes + i * 16, u.template quantise<E5M2>(sc));
-        }
-        done = units * 16;
+        const int64_t n_vec = total / kPer;
+        for (int64_t i = tid; i < n_vec; i += stride)
+            Chunk<T>::template quantise_store<E5M2>(ld_stream(x + i * kPer), div, codes + i * kPer);
+        done = n_vec * kPer;
     }
-    for (int64_t i = done + tid; i < total; i += stride) codes[i] = quant1<E5M2>(Store<T>::load1(x + i), sc);
+    for (int64_t i = done + tid; i < total; i += stride) codes[i] = quant1<E5M2>(Store<T>::load1(x + i), div);
 }
 
 // ------------------------------------------------------------------ host dispatch
@@ -262,15 +290,16 @@ cudaError_t run_token(const void* x, uint8_t* codes, float* scale, int64_t m, in
     if (m > 0x7fffffffLL) return cudaErrorInvalidValue;
     const T* xp = static_cast<const T*>(x);
     const unsigned grid = static_cast<unsigned>(m);
-    const int64_t units = n / 16;
-    if (n % 16 == 0 && aligned16(x) && aligned16(codes) && units <= 8 * 1024) {
-        const int upt = units <= 2048 ? 2 : (units <= 4096 ? 4 : 8);
-        int threads = static_cast<int>(ceil_div64(ceil_div64(units, upt), 32) * 32);
+    constexpr int kPer = Store<T>::kPerVec;
+    const int64_t n_vec = n / kPer;
+    // codes of one vector are stored with one kPer-byte store: row starts must be kPer-byte aligned
+    if (n % kPer == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(codes) % kPer) == 0 && n_vec <= 8 * 1024) {
+        const int vpt = n_vec <= 4 * 1024 ? 4 : 8;
+        int threads = static_cast<int>(ceil_div64(ceil_div64(n_vec, vpt), 32) * 32);
         if (threads < 32) threads = 32;
-        const int un = static_cast<int>(units);
-        if (upt == 2) fp8_token_kernel<T, E5M2, 2><<<grid, threads, 0, s>>>(xp, codes, scale, n, un);
-        else if (upt == 4) fp8_token_kernel<T, E5M2, 4><<<grid, threads, 0, s>>>(xp, codes, scale, n, un);
-        else fp8_token_kernel<T, E5M2, 8><<<grid, threads, 0, s>>>(xp, codes, scale, n, un);
+        const int nv = static_cast<int>(n_vec);
+        if (vpt == 4) fp8_token_kernel<T, E5M2, 4><<<grid, threads, 0, s>>>(xp, codes, scale, n, nv);
+        else fp8_token_kernel<T, E5M2, 8><<<grid, threads, 0, s>>>(xp, codes, scale, n, nv);
     } else {
         fp8_token_generic_kernel<T, E5M2><<<grid, 256, 0, s>>>(xp, codes, scale, n);
     }
@@ -283,7 +312,7 @@ cudaError_t run_block(const void* x, uint8_t* codes, float* scale, int64_t m, in
     if (gy > 65535 || gx > 0x7fffffffLL) return cudaErrorInvalidValue;
     const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
     const T* xp = static_cast<const T*>(x);
-    if (n % 16 == 0 && aligned16(x) && aligned16(codes))
+    if (n % Store<T>::kPerVec == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(codes) % 8) == 0)
         fp8_block_kernel<T, E5M2><<<grid, 256, 0, s>>>(xp, codes, scale, m, n);
     else
         fp8_block_generic_kernel<T, E5M2><<<grid, 256, 0, s>>>(xp, codes, scale, m, n);
@@ -295,7 +324,7 @@ cudaError_t run_tensor(const void* x, uint8_t* codes, float* scale, int32_t* ama
                        cudaStream_t s) {
     const T* xp = static_cast<const T*>(x);
     const int64_t total = m * n;
-    const bool vec_ok = aligned16(x) && aligned16(codes);
+    const bool vec_ok = aligned16(x) && (reinterpret_cast<uintptr_t>(codes) % 8) == 0;
     int64_t ctas = ceil_div64(total, 256 * 16);
     const int64_t cap = static_cast<int64_t>(kNumSMs) * 8;
     if (ctas > cap) ctas = cap;
