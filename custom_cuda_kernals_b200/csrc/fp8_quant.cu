@@ -12,8 +12,8 @@
 //     approximate reciprocal and is off by one code on ~5e-4 of the elements.
 //     `x / scale` is evaluated as a correctly rounded quotient from the correctly
 //     rounded reciprocal of the (row / tile / tensor-wide) scale and two
-//     FMA residual corrections (struct ExactDiv) - 6 instructions per element
-//     instead of a full division.  This file must not be compiled with
+//     FMA residual corrections (struct ExactDiv), two elements per packed fp32x2
+//     instruction - 2.5 issue slots per element instead of a full division.  This file must not be compiled with
 //     --use_fast_math.
 //   * The row / tile is held in registers between the amax pass and the cast,
 //     so HBM is read once.  Every load is one 16-byte vector per lane with
@@ -56,21 +56,43 @@ __device__ __forceinline__ float scale_of(float amax) {
 // exact in an FMA and RN(q + r*y) is the correctly rounded quotient (Markstein's
 // theorem).  No intermediate can underflow while the quotient still matters:
 // s >= 1e-12 and |a/s| <= FP8_MAX, and a quotient below 2^-11 becomes a zero code
-// whatever its last bits are.  The sign is taken from `a` so that -0.0 stays -0.0.
+// whatever its last bits are.  The residuals are rounded toward -inf: an exact
+// residual is unchanged by the rounding mode, except that an exact zero comes out
+// as -0, and q + (-0) keeps q's own sign - so -0.0 / s stays -0.0 as IEEE
+// division gives, at no extra instruction.  pair() does two quotients per
+// instruction with the packed fp32x2 FMA of sm_100.
 struct ExactDiv {
     float s, y;
+    uint64_t neg_s2, y2;
+    __device__ static __forceinline__ uint64_t pack2(float lo, float hi) {
+        uint64_t r;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+        return r;
+    }
     __device__ static __forceinline__ ExactDiv make(float scale) {
         ExactDiv d;
         d.s = scale;
         d.y = __frcp_rn(scale);
+        d.neg_s2 = pack2(-scale, -scale);
+        d.y2 = pack2(d.y, d.y);
         return d;
     }
     __device__ __forceinline__ float operator()(float a) const {
         const float q0 = __fmul_rn(a, y);
-        const float r0 = __fmaf_rn(-s, q0, a);
+        const float r0 = __fmaf_rd(-s, q0, a);
         const float q1 = __fmaf_rn(r0, y, q0);
-        const float r1 = __fmaf_rn(-s, q1, a);
-        return copysignf(__fmaf_rn(r1, y, q1), a);
+        const float r1 = __fmaf_rd(-s, q1, a);
+        return __fmaf_rn(r1, y, q1);
+    }
+    __device__ __forceinline__ void pair(float a, float b, float& qa, float& qb) const {
+        const uint64_t ab = pack2(a, b);
+        uint64_t q0, r0, q1, r1, q2;
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q0) : "l"(ab), "l"(y2));
+        asm("fma.rm.f32x2 %0, %1, %2, %3;" : "=l"(r0) : "l"(neg_s2), "l"(q0), "l"(ab));
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q1) : "l"(r0), "l"(y2), "l"(q0));
+        asm("fma.rm.f32x2 %0, %1, %2, %3;" : "=l"(r1) : "l"(neg_s2), "l"(q1), "l"(ab));
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q2) : "l"(r1), "l"(y2), "l"(q1));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(qa), "=f"(qb) : "l"(q2));
     }
 };
 
@@ -105,7 +127,7 @@ template <typename T> struct Chunk {
     __device__ static __forceinline__ void quantise_store(const Vec16& v, const ExactDiv& div, uint8_t* dst) {
         float f[kPer];
 #pragma unroll
-        for (int e = 0; e < kPer; ++e) f[e] = div(Store<T>::get(v, e));
+        for (int e = 0; e < kPer; e += 2) div.pair(Store<T>::get(v, e), Store<T>::get(v, e + 1), f[e], f[e + 1]);
         const uint32_t w0 = Fmt<E5M2>::cvt2(f[0], f[1]) | (Fmt<E5M2>::cvt2(f[2], f[3]) << 16);
         if constexpr (kPer == 8) {
             const uint32_t w1 = Fmt<E5M2>::cvt2(f[4], f[5]) | (Fmt<E5M2>::cvt2(f[6], f[7]) << 16);
@@ -185,40 +207,40 @@ fp8_token_generic_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, f
 }
 
 // ------------------------------------------------------------------ block granularity
-// One CTA of 256 threads per 128x128 tile; a tile row is 128/kPer vectors, so a warp
-// reads whole 256-byte (16-bit) or 512-byte (fp32) row segments.
+// One CTA of 512 threads per 128x128 tile; a tile row is 128/kPer vectors, so a warp
+// reads whole 256-byte (16-bit) or 512-byte (fp32) row segments; 4 (8) vectors per thread.
+constexpr int kBlockThreads = 512;
 template <typename T, bool E5M2>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kBlockThreads, sizeof(T) == 4 ? 2 : 3)
 fp8_block_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, float* __restrict__ scale,
                  int64_t m, int64_t n) {
     constexpr int kPer = Store<T>::kPerVec;
-    constexpr int kVecPerRow = kTile / kPer;               // 16 or 32
-    constexpr int kVpt = kTile * kVecPerRow / 256;         // 8 or 16
+    constexpr int kVecPerRow = kTile / kPer;                        // 16 or 32
+    constexpr int kVpt = kTile * kVecPerRow / kBlockThreads;        // 4 or 8
     __shared__ float slots[32];
     const int64_t r0 = static_cast<int64_t>(blockIdx.y) * kTile, c0 = static_cast<int64_t>(blockIdx.x) * kTile;
+    const bool interior = r0 + kTile <= m && c0 + kTile <= n;      // no edge predicates needed
     Vec16 v[kVpt];
+    int64_t off[kVpt];
+    bool live[kVpt];
     float mx = 0.0f;
 #pragma unroll
     for (int j = 0; j < kVpt; ++j) {
-        const int id = threadIdx.x + j * 256;
+        const int id = threadIdx.x + j * kBlockThreads;
         const int64_t r = r0 + id / kVecPerRow, c = c0 + (id % kVecPerRow) * kPer;
-        if (r < m && c < n) v[j] = ld_stream(x + r * n + c);   // n % kPer == 0 on this path
+        off[j] = r * n + c;
+        live[j] = interior || (r < m && c < n);                     // n % kPer == 0 on this path
+        if (live[j]) v[j] = ld_stream(x + off[j]);
     }
 #pragma unroll
-    for (int j = 0; j < kVpt; ++j) {
-        const int id = threadIdx.x + j * 256;
-        const int64_t r = r0 + id / kVecPerRow, c = c0 + (id % kVecPerRow) * kPer;
-        if (r < m && c < n) mx = fmaxf(mx, Chunk<T>::amax(v[j]));
-    }
+    for (int j = 0; j < kVpt; ++j)
+        if (live[j]) mx = fmaxf(mx, Chunk<T>::amax(v[j]));
     const float sc = scale_of<E5M2>(cta_max_dyn(mx, slots));
     if (threadIdx.x == 0) scale[static_cast<int64_t>(blockIdx.y) * gridDim.x + blockIdx.x] = sc;
     const ExactDiv div = ExactDiv::make(sc);
 #pragma unroll
-    for (int j = 0; j < kVpt; ++j) {
-        const int id = threadIdx.x + j * 256;
-        const int64_t r = r0 + id / kVecPerRow, c = c0 + (id % kVecPerRow) * kPer;
-        if (r < m && c < n) Chunk<T>::template quantise_store<E5M2>(v[j], div, codes + r * n + c);
-    }
+    for (int j = 0; j < kVpt; ++j)
+        if (live[j]) Chunk<T>::template quantise_store<E5M2>(v[j], div, codes + off[j]);
 }
 
 template <typename T, bool E5M2>
@@ -313,7 +335,7 @@ cudaError_t run_block(const void* x, uint8_t* codes, float* scale, int64_t m, in
     const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
     const T* xp = static_cast<const T*>(x);
     if (n % Store<T>::kPerVec == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(codes) % 8) == 0)
-        fp8_block_kernel<T, E5M2><<<grid, 256, 0, s>>>(xp, codes, scale, m, n);
+        fp8_block_kernel<T, E5M2><<<grid, kBlockThreads, 0, s>>>(xp, codes, scale, m, n);
     else
         fp8_block_generic_kernel<T, E5M2><<<grid, 256, 0, s>>>(xp, codes, scale, m, n);
     return cudaGetLastError();

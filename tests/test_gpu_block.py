@@ -1,0 +1,85 @@
+"""GPU parity: the Llama decoder block (examples/llama_block.py:158-173 structure) built
+from this library's ops, against the CPU oracle block with the same weights.
+
+A seven-GEMM bf16 chain cannot be compared bit for bit across machines: torch's own eager
+bf16 block on GPU and on CPU differ on about 3 % of the elements at the reference's block
+tolerance (rtol 1e-2, atol 2e-2; examples/llama_block.py:271-283 compares two blocks that
+share cuBLAS and SDPA, so only its three fused ops differ).  The bars here: (1) measured
+against an fp32 evaluation of the same block, the GPU result is as accurate as the oracle's
+bf16 result; (2) elementwise against the oracle within the reference's tolerance on >= 95 %
+of the elements; (3) against the same block written with torch's own GPU ops (F.linear,
+eager norm / rope / swiglu), where only accumulation order differs, within that tolerance
+on all but 2e-3 of the elements (measured: 3e-5 to 6e-4)."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import ops, workloads
+from tests.gpu_util import DEV, device_status_clean
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpu_eager_block(x, w, n_heads, n_kv, eps, theta):
+    b, s, hid = x.shape
+    d = hid // n_heads
+    cos, sin = ops.rope_tables(s, d, theta)
+    cos, sin = cos.to(x.device), sin.to(x.device)
+    h, res = ops.rmsnorm_residual(x, torch.zeros_like(x), w["input_layernorm_weight"], eps)
+    q = F.linear(h, w["q_proj"]).view(b, s, n_heads, d)
+    k = F.linear(h, w["k_proj"]).view(b, s, n_kv, d)
+    v = F.linear(h, w["v_proj"]).view(b, s, n_kv, d)
+    q, k = ops.rope(q, k, cos, sin)
+    att = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                         is_causal=True, enable_gqa=n_heads != n_kv)
+    att = F.linear(att.transpose(1, 2).contiguous().view(b, s, hid), w["o_proj"])
+    h2, res2 = ops.rmsnorm_residual(att, res, w["post_attention_layernorm_weight"], eps)
+    return F.linear(ops.swiglu(F.linear(h2, w["gate_proj"]), F.linear(h2, w["up_proj"])), w["down_proj"]) + res2
+
+
+def _check(cfg, batch, seq):
+    from custom_cuda_kernals_b200.llama_block import LlamaBlock
+    w = workloads.block_weights(cfg)
+    x = workloads.block_input(batch, seq, cfg["hidden"])
+    kw = dict(n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"], eps=cfg["eps"], theta=cfg["theta"])
+    with torch.no_grad():
+        want = ops.llama_block(x, w, **kw).float()
+        truth = ops.llama_block(x.float(), {k: v.float() for k, v in w.items()}, **kw)
+        wd = {k: v.to(DEV) for k, v in w.items()}
+        block = LlamaBlock(wd, cfg["n_heads"], cfg["n_kv_heads"], cfg["eps"], cfg["theta"], max_seq_len=seq)
+        got_dev = block(x.to(DEV))
+        eager_dev = _gpu_eager_block(x.to(DEV), wd, cfg["n_heads"], cfg["n_kv_heads"], cfg["eps"], cfg["theta"])
+    assert got_dev.shape == x.shape and got_dev.dtype == torch.bfloat16
+    got = got_dev.cpu().float()
+    rms = lambda t: float(t.pow(2).mean().sqrt())
+    assert rms(got - truth) <= 1.25 * rms(want - truth)
+    outside = lambda a, b: float(((a - b).abs() > 2e-2 + 1e-2 * b.abs()).float().mean())
+    assert outside(got, want) <= 0.05
+    assert outside(got, eager_dev.cpu().float()) <= 2e-3
+    assert device_status_clean(got_dev)
+
+
+def test_block_llama3_8b_shapes_short_sequences():
+    """Benchmark config 4's architecture at batch 2 x seq 192 (the CPU oracle costs ~0.9 GFLOP per token)."""
+    _check(dict(workloads.LLAMA3_8B), 2, 192)
+
+
+def test_block_small_config_ragged_tokens():
+    """hidden 512, 8 q / 2 kv heads, FFN 1408, 3 x 77 tokens: partial GEMM tiles everywhere."""
+    cfg = dict(workloads.LLAMA3_8B, hidden=512, ffn=1408, n_heads=8, n_kv_heads=2, head_dim=64)
+    _check(cfg, 3, 77)
+
+
+def test_block_is_deterministic_and_batch_independent():
+    from custom_cuda_kernals_b200.llama_block import LlamaBlock
+    cfg = dict(workloads.LLAMA3_8B, hidden=1024, ffn=2816, n_heads=8, n_kv_heads=2, head_dim=128)
+    wd = {k: v.to(DEV) for k, v in workloads.block_weights(cfg).items()}
+    block = LlamaBlock(wd, 8, 2, cfg["eps"], cfg["theta"], max_seq_len=256)
+    x = workloads.block_input(4, 256, 1024).to(DEV)
+    with torch.no_grad():
+        full = block(x)
+        assert torch.equal(full, block(x))
+        # sequences are independent: a rank that holds only sequences 2..3 gets the same rows
+        part = block(x[2:4].contiguous())
+    assert torch.equal(part, full[2:4])
