@@ -258,3 +258,60 @@ extern "C" int32_t launch_lce_finalize(const float* stats, const int64_t* target
         stats, targets, n, static_cast<int>(n_shards), ignore_index, loss_rows, reduce_out);
     return cudaGetLastError();
 }
+
+// ------------------------------------------------------------------ variant that allocates nothing
+// Some hosts cannot hand this library a workspace: an inference server whose
+// memory pool already owns every byte of device memory, or a latency-critical
+// loop that must not call cudaMalloc (it synchronises the whole device).  For
+// them the per-split partial statistics live in this fixed array instead, which
+// every GPU that loads the library holds until the process exits.
+namespace {
+constexpr int64_t kNoAllocScratchBytes = 6ll << 20;   // 6 MiB: e.g. 8192 rows x 64 splits
+static __device__ __align__(256) float g_lce_noalloc_scratch[kNoAllocScratchBytes / sizeof(float)];
+
+// In host code the array's name only stands for the symbol; its device address has
+// to be asked for, once per device, with that device current.
+float* noalloc_scratch_ptr(cudaError_t* err) {
+    static float* ptr[64] = {};
+    int dev = 0;
+    *err = cudaGetDevice(&dev);
+    if (*err != cudaSuccess) return nullptr;
+    if (dev < 0 || dev >= 64) {
+        *err = cudaErrorInvalidDevice;
+        return nullptr;
+    }
+    if (!ptr[dev]) {
+        void* p = nullptr;
+        *err = cudaGetSymbolAddress(&p, g_lce_noalloc_scratch);
+        if (*err != cudaSuccess) return nullptr;
+        ptr[dev] = static_cast<float*>(p);
+    }
+    return ptr[dev];
+}
+}  // namespace
+
+extern "C" int64_t cck_lce_noalloc_max_workspace_bytes(void) { return kNoAllocScratchBytes; }
+
+// Same computation and same result as launch_linear_cross_entropy_fwd, but the
+// workspace is the library's own fixed 6 MiB device array, so the call makes no
+// cudaMalloc / cudaFree and needs no workspace argument.
+//   * Problems whose workspace need, cck_lce_workspace_bytes(n, v_count), exceeds
+//     cck_lce_noalloc_max_workspace_bytes() are refused with cudaErrorInvalidValue
+//     before anything is launched.
+//   * The first call on a device looks up the array's device address
+//     (cudaGetSymbolAddress); make that first call outside any stream capture.
+//   * All calls on a device share the one array.  Nothing in it has to start at
+//     zero - every partial that is read has been written by the same call - but two
+//     calls that overlap on the GPU (different streams) race on it: serialise them.
+extern "C" int32_t launch_linear_cross_entropy_fwd_noalloc(const void* hidden, const void* weight,
+                                                           const int64_t* targets, int64_t v_start, int64_t n,
+                                                           int64_t h, int64_t v_count, float* row_stats,
+                                                           int32_t dtype, void* stream) {
+    if (n <= 0 || v_count <= 0 || h <= 0) return cudaSuccess;
+    if (cck_lce_workspace_bytes(n, v_count) > kNoAllocScratchBytes) return cudaErrorInvalidValue;
+    cudaError_t err = cudaSuccess;
+    float* scratch = noalloc_scratch_ptr(&err);
+    if (scratch == nullptr) return err;
+    return launch_linear_cross_entropy_fwd(hidden, weight, targets, v_start, n, h, v_count, row_stats, scratch,
+                                           kNoAllocScratchBytes, dtype, stream);
+}

@@ -99,6 +99,19 @@ int32_t launch_linear_cross_entropy_fwd(const void* hidden, const void* weight, 
 int64_t cck_lce_workspace_bytes(int64_t n, int64_t v_count);
 int64_t cck_lce_num_splits(int64_t n, int64_t v_count);
 
+/* No counterpart in the reference.  launch_linear_cross_entropy_fwd for callers that cannot
+ * provide (or allocate) a workspace - a server whose memory pool owns all device memory, a loop
+ * that must not call cudaMalloc: the workspace is a fixed 6 MiB device array inside the library,
+ * held by every GPU that loads it.  No allocation or free is made.  Returns
+ * cudaErrorInvalidValue, launching nothing, when cck_lce_workspace_bytes(n, v_count) exceeds
+ * cck_lce_noalloc_max_workspace_bytes().  The first call on a device looks up the array's
+ * address and should be made outside stream capture.  Calls share the array: calls that overlap
+ * on the GPU race and must be serialised by the caller. */
+int32_t launch_linear_cross_entropy_fwd_noalloc(const void* hidden, const void* weight, const int64_t* targets,
+                                                int64_t v_start, int64_t n, int64_t h, int64_t v_count,
+                                                float* row_stats, int32_t dtype, void* stream);
+int64_t cck_lce_noalloc_max_workspace_bytes(void);
+
 /* Merge row_stats of n_shards vocabulary slices (stats [n_shards][3][n]) into per-row losses:
  * loss_rows [n] (0 where targets == ignore_index; may be NULL) and reduce_out [2] =
  * { sum of losses, number of rows whose target is not ignore_index }. */
