@@ -385,7 +385,7 @@ def run_ours(args, rank, world, local):
     line["e2e"] = {"value": tokens * args.steps / e2e_secs, "unit": UNIT,
                    "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": out_host.numel() * 2 * world,
                    "ms_per_step": e2e_secs / args.steps * 1e3,
-                   "api": "LlamaBlock.forward_host(pinned x, pinned out): H2D, 11 library kernels + SDPA, D2H"}
+                   "api": "LlamaBlock.forward_host(pinned x, pinned out): H2D, 11 library kernels + SDPA per group of sequences, D2H; groups pipelined over 3 streams"}
     line["gpu_launches"] = LlamaBlock.LAUNCHES_PER_FORWARD * args.steps * world
     line["clocks"] = clocks.summary()
     line["parity"] = parity

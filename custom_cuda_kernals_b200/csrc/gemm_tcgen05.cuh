@@ -18,6 +18,8 @@
 // All waits are bounded; a time-out sets bit 0 of *status and the CTA leaves.
 #pragma once
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -48,15 +50,16 @@ struct TileWork {
 struct SchedGemm {
     struct Params { int m_tiles, n_tiles; };
     struct Iter {
-        int t, total, m_tiles;
-        __device__ explicit Iter(const Params& p) : t(blockIdx.x), total(p.m_tiles * p.n_tiles), m_tiles(p.m_tiles) {}
+        int t, step, total, m_tiles;
+        __device__ Iter(const Params& p, int worker, int workers)
+            : t(worker), step(workers), total(p.m_tiles * p.n_tiles), m_tiles(p.m_tiles) {}
         __device__ bool next(TileWork& w) {
             if (t >= total) return false;
             w.m_tile = t % m_tiles;
             w.n_tile = t / m_tiles;
             w.split = 0;
             w.first = w.last = true;
-            t += gridDim.x;
+            t += step;
             return true;
         }
     };
@@ -114,7 +117,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            typename Sched::Iter it(sp);
+            typename Sched::Iter it(sp, blockIdx.x, gridDim.x);
             TileWork w;
             while (ok && it.next(w)) {
                 const int m0 = w.m_tile * kBM, n0 = w.n_tile * kBN;
@@ -135,7 +138,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t phase = 0;
             int acc_iter = 0;
             bool ok = true;
-            typename Sched::Iter it(sp);
+            typename Sched::Iter it(sp, blockIdx.x, gridDim.x);
             TileWork w;
             while (ok && it.next(w)) {
                 const int buf = acc_iter & 1;
@@ -169,7 +172,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         float* my_scratch = scratch + (warp - 2) * kScratchFloatsPerWarp;
         typename Epi::Thread th;
         int acc_iter = 0;
-        typename Sched::Iter it(sp);
+        typename Sched::Iter it(sp, blockIdx.x, gridDim.x);
         TileWork w;
         while (it.next(w)) {
             const int buf = acc_iter & 1;
@@ -211,6 +214,186 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
 }
 
+// ------------------------------------------------------------------ CTA-pair variant
+// Two CTAs on the SMs of one TPC (a cluster of 2) share one 256 x 256 output tile:
+// CTA r loads rows [128r, 128r+128) of the A tile and rows [128r, 128r+128) of the B
+// tile (32 KB per stage instead of 48 KB, so the ring is 6 stages deep), one thread of
+// the leader CTA (rank 0) issues tcgen05.mma.cta_group::2 with M = 256, and each CTA's
+// tensor memory receives its own 128 accumulator rows - which the CTA's epilogue warps
+// drain exactly as in the single-CTA kernel (its tile is m_tile = 2 * pair_tile + r).
+// Per MMA each SM reads 4 KB of A and 4 KB of B from its shared memory instead of
+// 4 + 8 KB: the operand traffic that limits the single-CTA kernel is cut by a third.
+// Cross-CTA signalling: both CTAs' TMA loads count their bytes on the leader's `full`
+// barrier; the leader's commits arrive on both CTAs' `empty` and `tmem full` barriers;
+// the peer's epilogue warps arrive on the leader's `tmem empty` barrier.  No load is
+// multicast; the only remote accesses are barrier arrivals and the MMA itself.
+constexpr int kPairStages = 6;
+constexpr int kPairBBytes = 128 * kRowBytes;                    // this CTA's half of B: 16 KiB
+constexpr int kPairStageBytes = kABytes + kPairBBytes;          // 32 KiB
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256 + kEpiWarps * kScratchFloatsPerWarp * 4;
+
+template <bool kFp8, class Sched, class Epi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const typename Sched::Params sp, const typename Epi::Params ep, int k_blocks, uint32_t idesc,
+                 unsigned int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - raw);
+    const uint32_t bar0 = base + kPairStages * kPairStageBytes;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kPairStages + s); };
+    auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * kPairStages + b); };
+    auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * kPairStages + 2 + b); };
+    uint8_t* misc = gen + kPairStages * kPairStageBytes + 8 * (2 * kPairStages + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
+    float* scratch = reinterpret_cast<float*>(gen + kPairStages * kPairStageBytes + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();          // 0 = leader
+    const bool leader = rank == 0;
+    const int pair_id = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    constexpr int kElemsPerSlab = kFp8 ? 128 : 64;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            ptx::mbar_init(full_bar(s), 1);                 // used in the leader only
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(tfull_bar(b), 1);
+            ptx::mbar_init(tempty_bar(b), 2 * kEpiWarps);   // used in the leader only: both CTAs' epilogues
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {                                        // the same warp in both CTAs
+        ptx::tmem_alloc_pair(ptx::smem_addr(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_arrive();                                  // barriers of both CTAs initialised before any remote arrival
+    ptx::cluster_wait();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            typename Sched::Iter it(sp, pair_id, pairs);
+            TileWork w;
+            while (ok && it.next(w)) {
+                const int m0 = (w.m_tile * 2 + static_cast<int>(rank)) * kBM;
+                const int n0 = w.n_tile * kBN + static_cast<int>(rank) * 128;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
+                    if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * kPairStageBytes);
+                    const uint32_t a_dst = base + stage * kPairStageBytes;
+                    ptx::tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * kElemsPerSlab, m0);
+                    ptx::tma_load_2d_pair(a_dst + kABytes, &tmap_b, leader_full, kb * kElemsPerSlab, n0);
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader only)
+        if (leader && lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc_iter = 0;
+            bool ok = true;
+            typename Sched::Iter it(sp, pair_id, pairs);
+            TileWork w;
+            while (ok && it.next(w)) {
+                const int buf = acc_iter & 1;
+                const uint32_t acc_phase = (acc_iter >> 1) & 1;
+                if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag)) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t d = tmem_base + buf * kBN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_src = base + stage * kPairStageBytes;
+                    const uint64_t da = ptx::smem_desc_k_sw128(a_src);
+                    const uint64_t db = ptx::smem_desc_k_sw128(a_src + kABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
+                        if (kFp8) ptx::mma_f8_pair(d, da + 2 * k, db + 2 * k, idesc, acc);
+                        else      ptx::mma_f16_pair(d, da + 2 * k, db + 2 * k, idesc, acc);
+                    }
+                    ptx::mma_commit_pair(ptx::map_to_cta(empty_bar(stage), 0));   // stage free in both CTAs
+                    ptx::mma_commit_pair(ptx::map_to_cta(empty_bar(stage), 1));
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) {
+                    ptx::mma_commit_pair(ptx::map_to_cta(tfull_bar(buf), 0));     // accumulators complete in both CTAs
+                    ptx::mma_commit_pair(ptx::map_to_cta(tfull_bar(buf), 1));
+                }
+                ++acc_iter;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        float* my_scratch = scratch + (warp - 2) * kScratchFloatsPerWarp;
+        typename Epi::Thread th;
+        int acc_iter = 0;
+        typename Sched::Iter it(sp, pair_id, pairs);
+        TileWork w;
+        while (it.next(w)) {
+            w.m_tile = w.m_tile * 2 + static_cast<int>(rank);
+            const int buf = acc_iter & 1;
+            const uint32_t acc_phase = (acc_iter >> 1) & 1;
+            __syncwarp();
+            Epi::tile_begin(ep, th, w, my_scratch, lane, row_in_tile);
+            __syncwarp();
+            const bool got = ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
+#pragma unroll 1
+            for (int c = 0; c < kBN / 32; ++c) {
+                float acc[32];
+                ptx::tmem_ld32(t0 + c * 32, acc);
+                Epi::chunk(ep, th, w, row_in_tile, c * 32, acc, my_scratch);
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(buf), 0));
+            Epi::tile_end(ep, th, w, row_in_tile);
+            ++acc_iter;
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        const unsigned long long t0 = ptx::globaltimer();
+        while (ptx::globaltimer() - t0 < 200000ull) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicOr(status, 1u);
+        __syncthreads();
+    }
+    // neither CTA may leave (or free tensor memory) while the other can still reach into it
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -243,6 +426,15 @@ inline cudaError_t make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int elem_
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// CCK_GEMM_SINGLE_CTA=1 in the environment keeps every GEMM on the single-CTA kernel.
+inline bool pair_kernels_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("CCK_GEMM_SINGLE_CTA");
+        return !(v && v[0] == '1');
+    }();
+    return on;
+}
+
 inline int sm_count() {
     static int n = [] {
         int dev = 0, v = 0;
@@ -271,6 +463,53 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const typename 
     const int slab = kFp8 ? 128 : 64;
     const int k_blocks = static_cast<int>((k_elems + slab - 1) / slab);
     kern<<<ctas, kThreads, kSmemBytes, s>>>(ta, tb, sp, ep, k_blocks, idesc, st);
+    return cudaGetLastError();
+}
+
+// Number of CTA pairs that can be resident at once (at most one pair per TPC).
+template <bool kFp8, class Sched, class Epi>
+int max_pairs() {
+    static int cached = 0;
+    if (cached > 0) return cached;
+    auto kern = gemm_pair_kernel<kFp8, Sched, Epi>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters <= 0) {
+        (void)cudaGetLastError();
+        cudaLaunchAttribute attr;                 // some runtimes want the cluster shape spelled out
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters <= 0) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+    }
+    cached = clusters;
+    return cached;
+}
+
+// `pair_tiles` = number of 256-row x 256-column tiles (or units) to spread over the pairs.
+template <bool kFp8, class Sched, class Epi>
+cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const typename Sched::Params& sp,
+                        const typename Epi::Params& ep, int64_t k_elems, uint32_t idesc, int64_t pair_tiles,
+                        cudaStream_t s) {
+    const int cap = max_pairs<kFp8, Sched, Epi>();
+    if (cap <= 0) return cudaErrorLaunchOutOfResources;
+    unsigned int* st = status_word();
+    if (!st) return cudaErrorMemoryAllocation;
+    const int pairs = static_cast<int>(pair_tiles < cap ? pair_tiles : cap);
+    const int slab = kFp8 ? 128 : 64;
+    const int k_blocks = static_cast<int>((k_elems + slab - 1) / slab);
+    gemm_pair_kernel<kFp8, Sched, Epi><<<2 * pairs, kThreads, kPairSmemBytes, s>>>(ta, tb, sp, ep, k_blocks, idesc, st);
     return cudaGetLastError();
 }
 

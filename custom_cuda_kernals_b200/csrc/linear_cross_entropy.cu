@@ -43,13 +43,13 @@ struct SchedLce {
     struct Params { int m_tiles, n_tiles, splits; };
     struct Iter {
         Params p;
-        int unit, units, nt, nt_end, nt_begin, split, m_tile;
-        __device__ explicit Iter(const Params& q)
-            : p(q), unit(static_cast<int>(blockIdx.x) - static_cast<int>(gridDim.x)), units(q.m_tiles * q.splits),
+        int unit, step, units, nt, nt_end, nt_begin, split, m_tile;
+        __device__ Iter(const Params& q, int worker, int workers)
+            : p(q), unit(worker - workers), step(workers), units(q.m_tiles * q.splits),
               nt(0), nt_end(0), nt_begin(0), split(0), m_tile(0) {}
         __device__ bool next(TileWork& w) {
             while (nt >= nt_end) {
-                unit += gridDim.x;
+                unit += step;
                 if (unit >= units) return false;
                 split = unit / p.m_tiles;
                 m_tile = unit - split * p.m_tiles;
@@ -205,11 +205,31 @@ inline int choose_splits(int m_tiles, int n_tiles, int ctas) {
 }  // namespace tc
 }  // namespace cck
 
+namespace cck {
+namespace tc {
+// How one launch is laid out: CTA pairs (256-row units) when the problem has at least two
+// row tiles and pairs can be scheduled, else single CTAs (128-row units).
+struct LcePlan {
+    bool pair;
+    int m_units, n_tiles, splits, workers;
+};
+inline LcePlan lce_plan(int64_t n, int64_t v_count) {
+    LcePlan p;
+    const int m_tiles = static_cast<int>(ceil_div64(n, kBM));
+    p.n_tiles = static_cast<int>(ceil_div64(v_count, kBN));
+    const int pairs = (m_tiles >= 2 && pair_kernels_enabled()) ? max_pairs<false, SchedLce, EpiLce>() : 0;
+    p.pair = pairs > 0;
+    p.m_units = p.pair ? (m_tiles + 1) / 2 : m_tiles;
+    p.workers = p.pair ? pairs : sm_count();
+    p.splits = choose_splits(p.m_units, p.n_tiles, p.workers);
+    return p;
+}
+}  // namespace tc
+}  // namespace cck
+
 extern "C" int64_t cck_lce_num_splits(int64_t n, int64_t v_count) {
-    using namespace cck;
     if (n <= 0 || v_count <= 0) return 1;
-    return tc::choose_splits(static_cast<int>(ceil_div64(n, tc::kBM)), static_cast<int>(ceil_div64(v_count, tc::kBN)),
-                             tc::sm_count());
+    return cck::tc::lce_plan(n, v_count).splits;
 }
 
 extern "C" int64_t cck_lce_workspace_bytes(int64_t n, int64_t v_count) {
@@ -228,26 +248,29 @@ extern "C" int32_t launch_linear_cross_entropy_fwd(const void* hidden, const voi
     if (h % 8 != 0 || !aligned16(hidden) || !aligned16(weight) || n >= (1LL << 31) || v_count >= (1LL << 31) ||
         h >= (1LL << 31))
         return cudaErrorInvalidValue;
-    if (workspace == nullptr || workspace_bytes < cck_lce_workspace_bytes(n, v_count)) return cudaErrorInvalidValue;
+    const LcePlan plan = lce_plan(n, v_count);
+    if (workspace == nullptr || workspace_bytes < static_cast<int64_t>(plan.splits) * 3 * n * 4) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool is_bf16 = dtype == kBF16;
     const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap ta, tb;
     cudaError_t e = make_tmap(&ta, dt, 2, hidden, n, h, kBM);
     if (e != cudaSuccess) return e;
-    e = make_tmap(&tb, dt, 2, weight, v_count, h, kBN);
+    e = make_tmap(&tb, dt, 2, weight, v_count, h, plan.pair ? 128 : kBN);
     if (e != cudaSuccess) return e;
-    const int m_tiles = static_cast<int>(ceil_div64(n, kBM)), n_tiles = static_cast<int>(ceil_div64(v_count, kBN));
-    const int splits = static_cast<int>(cck_lce_num_splits(n, v_count));
-    SchedLce::Params sp{m_tiles, n_tiles, splits};
+    SchedLce::Params sp{plan.m_units, plan.n_tiles, plan.splits};
     EpiLce::Params ep{targets, static_cast<float*>(workspace), n, v_count, v_start};
-    const int64_t units = static_cast<int64_t>(m_tiles) * splits;
-    const int ctas = static_cast<int>(units < sm_count() ? units : sm_count());
+    const int64_t units = static_cast<int64_t>(plan.m_units) * plan.splits;
     const uint32_t fmt = is_bf16 ? 1u : 0u;
-    e = launch<false, SchedLce, EpiLce>(ta, tb, sp, ep, h, ptx::instr_desc(fmt, fmt, kBM, kBN), ctas, s);
+    if (plan.pair) {
+        e = launch_pair<false, SchedLce, EpiLce>(ta, tb, sp, ep, h, ptx::instr_desc(fmt, fmt, 2 * kBM, kBN), units, s);
+    } else {
+        const int ctas = static_cast<int>(units < plan.workers ? units : plan.workers);
+        e = launch<false, SchedLce, EpiLce>(ta, tb, sp, ep, h, ptx::instr_desc(fmt, fmt, kBM, kBN), ctas, s);
+    }
     if (e != cudaSuccess) return e;
     lce_merge_kernel<<<static_cast<unsigned>(ceil_div64(n, 256)), 256, 0, s>>>(
-        static_cast<const float*>(workspace), splits, n, row_stats);
+        static_cast<const float*>(workspace), plan.splits, n, row_stats);
     return cudaGetLastError();
 }
 

@@ -133,17 +133,24 @@ cudaError_t gemm_tc(const void* x, const void* w, const void* bias, void* y, int
                     cudaStream_t s) {
     constexpr bool is_bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
     const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const int m_tiles = static_cast<int>(ceil_div64(m, kBM)), n_tiles = static_cast<int>(ceil_div64(n, kBN));
+    typename EpiBias<T>::Params ep{static_cast<const T*>(bias), static_cast<T*>(y), m, n,
+                                   (n % 8 == 0 && aligned16(y)) ? 1 : 0};
+    const uint32_t fmt = is_bf16 ? 1u : 0u;
+    const bool pair = m_tiles >= 2 && pair_kernels_enabled() && max_pairs<false, SchedGemm, EpiBias<T>>() > 0;
     CUtensorMap ta, tb;
     cudaError_t e = make_tmap(&ta, dt, 2, x, m, k, kBM);
     if (e != cudaSuccess) return e;
-    e = make_tmap(&tb, dt, 2, w, n, k, kBN);
+    e = make_tmap(&tb, dt, 2, w, n, k, pair ? 128 : kBN);     // a CTA of a pair loads half of the B tile
     if (e != cudaSuccess) return e;
-    SchedGemm::Params sp{static_cast<int>(ceil_div64(m, kBM)), static_cast<int>(ceil_div64(n, kBN))};
-    typename EpiBias<T>::Params ep{static_cast<const T*>(bias), static_cast<T*>(y), m, n,
-                                   (n % 8 == 0 && aligned16(y)) ? 1 : 0};
+    if (pair) {
+        SchedGemm::Params sp{(m_tiles + 1) / 2, n_tiles};
+        return launch_pair<false, SchedGemm, EpiBias<T>>(ta, tb, sp, ep, k, ptx::instr_desc(fmt, fmt, 2 * kBM, kBN),
+                                                         static_cast<int64_t>(sp.m_tiles) * sp.n_tiles, s);
+    }
+    SchedGemm::Params sp{m_tiles, n_tiles};
     const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
     const int ctas = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-    const uint32_t fmt = is_bf16 ? 1u : 0u;
     return launch<false, SchedGemm, EpiBias<T>>(ta, tb, sp, ep, k, ptx::instr_desc(fmt, fmt, kBM, kBN), ctas, s);
 }
 
@@ -182,27 +189,40 @@ extern "C" int32_t launch_matmul_add_bias_fp8_fwd(const uint8_t* a_codes, const 
         m >= (1LL << 31) || n >= (1LL << 31) || k >= (1LL << 31))
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int m_tiles = static_cast<int>(ceil_div64(m, kBM)), n_tiles = static_cast<int>(ceil_div64(n, kBN));
+    const int vec_ok = (n % 8 == 0 && aligned16(y)) ? 1 : 0;
+    if (out_dtype != kBF16 && out_dtype != kF16) return cudaErrorInvalidValue;
+    const bool bf = out_dtype == kBF16;
+    const bool pair = m_tiles >= 2 && pair_kernels_enabled() &&
+                      (bf ? max_pairs<true, SchedGemm, EpiScaledBias<__nv_bfloat16>>()
+                          : max_pairs<true, SchedGemm, EpiScaledBias<__half>>()) > 0;
     CUtensorMap ta, tb;
     cudaError_t e = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_codes, m, k, kBM);
     if (e != cudaSuccess) return e;
-    e = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_codes, n, k, kBN);
+    e = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_codes, n, k, pair ? 128 : kBN);
     if (e != cudaSuccess) return e;
-    SchedGemm::Params sp{static_cast<int>(ceil_div64(m, kBM)), static_cast<int>(ceil_div64(n, kBN))};
+    SchedGemm::Params sp{pair ? (m_tiles + 1) / 2 : m_tiles, n_tiles};
     const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
     const int ctas = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-    const uint32_t idesc = ptx::instr_desc(0u, 0u, kBM, kBN);   // e4m3 x e4m3
-    const int vec_ok = (n % 8 == 0 && aligned16(y)) ? 1 : 0;
-    if (out_dtype == kBF16) {
+    const uint32_t idesc = ptx::instr_desc(0u, 0u, pair ? 2 * kBM : kBM, kBN);   // e4m3 x e4m3
+    if (bf) {
         EpiScaledBias<__nv_bfloat16>::Params ep{a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias),
                                                 static_cast<__nv_bfloat16*>(y), m, n, vec_ok};
-        return launch<true, SchedGemm, EpiScaledBias<__nv_bfloat16>>(ta, tb, sp, ep, k, idesc, ctas, s);
+        return pair ? launch_pair<true, SchedGemm, EpiScaledBias<__nv_bfloat16>>(ta, tb, sp, ep, k, idesc, tiles, s)
+                    : launch<true, SchedGemm, EpiScaledBias<__nv_bfloat16>>(ta, tb, sp, ep, k, idesc, ctas, s);
     }
-    if (out_dtype == kF16) {
-        EpiScaledBias<__half>::Params ep{a_scale, w_scale, static_cast<const __half*>(bias),
-                                         static_cast<__half*>(y), m, n, vec_ok};
-        return launch<true, SchedGemm, EpiScaledBias<__half>>(ta, tb, sp, ep, k, idesc, ctas, s);
-    }
-    return cudaErrorInvalidValue;
+    EpiScaledBias<__half>::Params ep{a_scale, w_scale, static_cast<const __half*>(bias), static_cast<__half*>(y), m, n,
+                                     vec_ok};
+    return pair ? launch_pair<true, SchedGemm, EpiScaledBias<__half>>(ta, tb, sp, ep, k, idesc, tiles, s)
+                : launch<true, SchedGemm, EpiScaledBias<__half>>(ta, tb, sp, ep, k, idesc, ctas, s);
+}
+
+// Number of CTA pairs the bf16 GEMM can keep resident on the current device (0: the pair
+// kernel is unavailable or disabled and every GEMM runs on the single-CTA kernel).
+extern "C" int32_t cck_gemm_pair_capacity(void) {
+    using namespace cck::tc;
+    if (!pair_kernels_enabled()) return 0;
+    return max_pairs<false, SchedGemm, EpiBias<__nv_bfloat16>>();
 }
 
 // Returns the tensor-core kernels' error word of the current device and clears

@@ -129,15 +129,38 @@ class LlamaBlock:
 
     __call__ = forward
 
-    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunks: int | None = None) -> torch.Tensor:
         """Host-buffer entry point: ``x_host`` / ``out_host`` are pinned CPU tensors
-        ``[B, S, hidden]``; the input is copied to the device, the block runs, and the
-        result is copied back, all on the current stream.  Returns ``out_host`` after
-        synchronising that stream."""
+        ``[B, S, hidden]``.  The batch is cut into ``chunks`` groups of whole sequences
+        (default: up to 4) that flow through three streams - copy-in, compute (the current
+        stream) and copy-out - so the PCIe transfers of one group overlap the kernels of
+        another.  Returns ``out_host`` once every group has landed in it."""
         dev = self.w["q_proj"].device
-        xd = x_host.to(dev, non_blocking=True)
-        out_host.copy_(self.forward(xd), non_blocking=True)
-        torch.cuda.current_stream(dev).synchronize()
+        b = x_host.shape[0]
+        n = max(1, min(b, chunks if chunks is not None else 4))
+        if not hasattr(self, "_copy_in"):
+            self._copy_in, self._copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        compute = torch.cuda.current_stream(dev)
+        bounds = [(b * i // n, b * (i + 1) // n) for i in range(n)]
+        self._copy_in.wait_stream(compute)
+        staged = []
+        with torch.cuda.stream(self._copy_in):
+            for b0, b1 in bounds:
+                xd = x_host[b0:b1].to(dev, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self._copy_in)
+                staged.append((xd, ev))
+        for (b0, b1), (xd, ev) in zip(bounds, staged):
+            compute.wait_event(ev)
+            xd.record_stream(compute)
+            y = self.forward(xd)
+            done = torch.cuda.Event()
+            done.record(compute)
+            self._copy_out.wait_event(done)
+            y.record_stream(self._copy_out)
+            with torch.cuda.stream(self._copy_out):
+                out_host[b0:b1].copy_(y, non_blocking=True)
+        self._copy_out.synchronize()
         return out_host
 
     def gemm_flops(self, tokens: int) -> int:

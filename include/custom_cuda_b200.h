@@ -118,6 +118,11 @@ int64_t cck_lce_noalloc_max_workspace_bytes(void);
 int32_t launch_lce_finalize(const float* stats, const int64_t* targets, int64_t n, int64_t n_shards,
                             int64_t ignore_index, float* loss_rows, float* reduce_out, void* stream);
 
+/* Number of two-CTA pairs the tensor-core GEMM keeps resident on the current device; 0 means
+ * the pair kernel is unavailable (or disabled with CCK_GEMM_SINGLE_CTA=1) and the single-CTA
+ * kernel is used. */
+int32_t cck_gemm_pair_capacity(void);
+
 /* Reads and clears the error word of the tensor-core kernels on the current device (bit 0: a
  * bounded wait inside a kernel ran out and the kernel gave up).  Synchronises the device. */
 int32_t cck_take_device_status(uint32_t* out);

@@ -83,3 +83,11 @@ def test_block_is_deterministic_and_batch_independent():
         # sequences are independent: a rank that holds only sequences 2..3 gets the same rows
         part = block(x[2:4].contiguous())
     assert torch.equal(part, full[2:4])
+    # the host-buffer entry point (pinned in, pinned out, groups pipelined over three streams)
+    x_host = x.cpu().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    with torch.no_grad():
+        for chunks in (None, 1, 3):
+            out_host.zero_()
+            block.forward_host(x_host, out_host, chunks=chunks)
+            assert torch.equal(out_host, full.cpu())

@@ -81,3 +81,11 @@ def test_fp8_token_and_tensor_through_ctypes(lib):
     assert rc == 0
     want_codes, want_scale = ops.fp8_quant(x, "e5m2", "tensor")
     assert torch.equal(codes.cpu(), want_codes.view(torch.uint8)) and s1.item() == want_scale.item()
+
+
+def test_pair_kernel_is_available_on_this_gpu(lib):
+    """The two-CTA (cta_group::2) GEMM is the default tensor-core path: at least 64 CTA pairs
+    fit a B200 (148 SMs = 74 TPCs)."""
+    lib.cck_gemm_pair_capacity.restype = ctypes.c_int32
+    torch.zeros(1, device=DEV)
+    assert lib.cck_gemm_pair_capacity() >= 64
