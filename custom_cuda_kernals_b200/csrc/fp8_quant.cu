@@ -276,8 +276,15 @@ fp8_amax_kernel(const T* __restrict__ x, int32_t* __restrict__ amax_bits, int64_
     int64_t done = 0;
     if (vec_ok) {
         const int64_t n_vec = total / kPer;
-        for (int64_t i = tid; i < n_vec; i += stride)
-            m = fmaxf(m, Chunk<T>::amax(ld_cached(x + i * kPer)));   // default policy: the cast pass re-reads it from L2
+        int64_t i = tid;
+        for (; i + 3 * stride < n_vec; i += 4 * stride) {           // four loads in flight per thread
+            Vec16 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = ld_cached(x + (i + j * stride) * kPer);   // default policy: the cast pass re-reads from L2
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m = fmaxf(m, Chunk<T>::amax(v[j]));
+        }
+        for (; i < n_vec; i += stride) m = fmaxf(m, Chunk<T>::amax(ld_cached(x + i * kPer)));
         done = n_vec * kPer;
     }
     for (int64_t i = done + tid; i < total; i += stride) m = fmaxf(m, fabsf(Store<T>::load1(x + i)));
@@ -299,7 +306,15 @@ fp8_cast_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, float* __r
     int64_t done = 0;
     if (vec_ok) {
         const int64_t n_vec = total / kPer;
-        for (int64_t i = tid; i < n_vec; i += stride)
+        int64_t i = tid;
+        for (; i + 3 * stride < n_vec; i += 4 * stride) {
+            Vec16 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = ld_stream(x + (i + j * stride) * kPer);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) Chunk<T>::template quantise_store<E5M2>(v[j], div, codes + (i + j * stride) * kPer);
+        }
+        for (; i < n_vec; i += stride)
             Chunk<T>::template quantise_store<E5M2>(ld_stream(x + i * kPer), div, codes + i * kPer);
         done = n_vec * kPer;
     }

@@ -46,17 +46,39 @@ struct TileWork {
     bool first, last;   // first / last tile of a unit (a unit = tiles sharing epilogue row state)
 };
 
-// ---- scheduler: plain GEMM, m fastest so that concurrently running CTAs share B panels
+// Row units (128-row tiles, or 256-row tiles of a CTA pair) are walked in groups of `group`
+// units: inside a group the row unit varies fastest, then the column tile.  The workers that
+// run at the same time therefore touch `group` A panels and workers/group B panels - a roughly
+// square patch whose operands stay in the 126 MB L2 - instead of every A panel of the matrix.
+__host__ __device__ inline void grouped_unit(int t, int m_units, int other, int group, int& m, int& o) {
+    const int span = group * other;
+    const int g = t / span;
+    const int r = t - g * span;
+    const int left = m_units - g * group;
+    const int gm = left < group ? left : group;
+    o = r / gm;
+    m = g * group + (r - o * gm);
+}
+// Units per group so that one group's A panels take about 48 MB of L2 (4..32 units).
+inline int raster_group(int64_t rows_per_unit, int64_t k_elems, int elem_bytes, int m_units) {
+    const int64_t panel = rows_per_unit * k_elems * elem_bytes;
+    int64_t g = panel > 0 ? (48ll << 20) / panel : 32;
+    if (g < 4) g = 4;
+    if (g > 32) g = 32;
+    return static_cast<int>(g < m_units ? g : m_units);
+}
+
+// ---- scheduler: plain GEMM
 struct SchedGemm {
-    struct Params { int m_tiles, n_tiles; };
+    struct Params { int m_tiles, n_tiles, group; };
     struct Iter {
-        int t, step, total, m_tiles;
-        __device__ Iter(const Params& p, int worker, int workers)
-            : t(worker), step(workers), total(p.m_tiles * p.n_tiles), m_tiles(p.m_tiles) {}
+        int t, step, total;
+        Params p;
+        __device__ Iter(const Params& q, int worker, int workers)
+            : t(worker), step(workers), total(q.m_tiles * q.n_tiles), p(q) {}
         __device__ bool next(TileWork& w) {
             if (t >= total) return false;
-            w.m_tile = t % m_tiles;
-            w.n_tile = t / m_tiles;
+            grouped_unit(t, p.m_tiles, p.n_tiles, p.group, w.m_tile, w.n_tile);
             w.split = 0;
             w.first = w.last = true;
             t += step;

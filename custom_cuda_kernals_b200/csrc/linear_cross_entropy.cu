@@ -12,9 +12,10 @@
 // reference rounds them to bf16 first).
 //
 // Work decomposition: the vocabulary tiles are cut into `splits` contiguous
-// ranges; a unit = (split, 128-row tile); units are dealt round-robin to the
-// persistent CTAs in split-major order so that CTAs running at the same time
-// read the same weight rows (L2 reuse).  Each unit writes one partial triple per
+// ranges; a unit = (row tile, split); units are dealt round-robin to the persistent
+// CTAs (or CTA pairs) in groups of row tiles (grouped_unit in gemm_tcgen05.cuh) so
+// that the workers running at the same time share a few hidden-state panels and a
+// few weight ranges that fit the L2 together.  Each unit writes one partial triple per
 // row into the caller's workspace [splits][3][N]; lce_merge_kernel reduces them
 // to row_stats [3][N] for this vocabulary slice.  A vocabulary-sharded run
 // all-gathers row_stats across ranks and calls launch_lce_finalize on the stack.
@@ -40,7 +41,7 @@ __host__ __device__ inline int split_begin(int split, int splits, int n_tiles) {
 }
 
 struct SchedLce {
-    struct Params { int m_tiles, n_tiles, splits; };
+    struct Params { int m_tiles, n_tiles, splits, group; };
     struct Iter {
         Params p;
         int unit, step, units, nt, nt_end, nt_begin, split, m_tile;
@@ -51,8 +52,7 @@ struct SchedLce {
             while (nt >= nt_end) {
                 unit += step;
                 if (unit >= units) return false;
-                split = unit / p.m_tiles;
-                m_tile = unit - split * p.m_tiles;
+                grouped_unit(unit, p.m_tiles, p.splits, p.group, m_tile, split);
                 nt_begin = nt = split_begin(split, p.splits, p.n_tiles);
                 nt_end = split_begin(split + 1, p.splits, p.n_tiles);
             }
@@ -258,7 +258,8 @@ extern "C" int32_t launch_linear_cross_entropy_fwd(const void* hidden, const voi
     if (e != cudaSuccess) return e;
     e = make_tmap(&tb, dt, 2, weight, v_count, h, plan.pair ? 128 : kBN);
     if (e != cudaSuccess) return e;
-    SchedLce::Params sp{plan.m_units, plan.n_tiles, plan.splits};
+    SchedLce::Params sp{plan.m_units, plan.n_tiles, plan.splits,
+                        raster_group(plan.pair ? 2 * kBM : kBM, h, 2, plan.m_units)};
     EpiLce::Params ep{targets, static_cast<float*>(workspace), n, v_count, v_start};
     const int64_t units = static_cast<int64_t>(plan.m_units) * plan.splits;
     const uint32_t fmt = is_bf16 ? 1u : 0u;

@@ -144,11 +144,12 @@ cudaError_t gemm_tc(const void* x, const void* w, const void* bias, void* y, int
     e = make_tmap(&tb, dt, 2, w, n, k, pair ? 128 : kBN);     // a CTA of a pair loads half of the B tile
     if (e != cudaSuccess) return e;
     if (pair) {
-        SchedGemm::Params sp{(m_tiles + 1) / 2, n_tiles};
+        const int m_pairs = (m_tiles + 1) / 2;
+        SchedGemm::Params sp{m_pairs, n_tiles, raster_group(2 * kBM, k, 2, m_pairs)};
         return launch_pair<false, SchedGemm, EpiBias<T>>(ta, tb, sp, ep, k, ptx::instr_desc(fmt, fmt, 2 * kBM, kBN),
                                                          static_cast<int64_t>(sp.m_tiles) * sp.n_tiles, s);
     }
-    SchedGemm::Params sp{m_tiles, n_tiles};
+    SchedGemm::Params sp{m_tiles, n_tiles, raster_group(kBM, k, 2, m_tiles)};
     const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
     const int ctas = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     return launch<false, SchedGemm, EpiBias<T>>(ta, tb, sp, ep, k, ptx::instr_desc(fmt, fmt, kBM, kBN), ctas, s);
@@ -201,7 +202,8 @@ extern "C" int32_t launch_matmul_add_bias_fp8_fwd(const uint8_t* a_codes, const 
     if (e != cudaSuccess) return e;
     e = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_codes, n, k, pair ? 128 : kBN);
     if (e != cudaSuccess) return e;
-    SchedGemm::Params sp{pair ? (m_tiles + 1) / 2 : m_tiles, n_tiles};
+    const int m_units = pair ? (m_tiles + 1) / 2 : m_tiles;
+    SchedGemm::Params sp{m_units, n_tiles, raster_group(pair ? 2 * kBM : kBM, k, 1, m_units)};
     const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
     const int ctas = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     const uint32_t idesc = ptx::instr_desc(0u, 0u, pair ? 2 * kBM : kBM, kBN);   // e4m3 x e4m3

@@ -1,0 +1,72 @@
+"""GPU, >= 2 devices: one process per GPU over NCCL - the vocabulary-parallel cross entropy
+(its single all-gather) and the sequence-sharded decoder block give the single-GPU result.
+Skipped on a single-GPU machine; the same host logic runs on CPU in tests/test_dist_cpu.py."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as td
+
+    from custom_cuda_kernals_b200 import dist
+    from custom_cuda_kernals_b200.kernels.linear_cross_entropy import linear_cross_entropy
+    from custom_cuda_kernals_b200.kernels.matmul_add_bias import matmul_add_bias
+    from custom_cuda_kernals_b200.llama_block import LlamaBlock
+    from oracle import workloads
+    dist.init_from_env(timeout_s=120)
+    dev = torch.device("cuda", rank)
+    # --- vocabulary-parallel cross entropy: every rank holds whole 128-row tiles of W
+    h, w, t = workloads.lce_bf16(tokens=512, hidden=1024, vocab=20000 + 57)
+    h, w, t = h.to(dev), w.to(dev), t.to(dev)
+    v0, v1 = dist.vocab_range(w.shape[0], rank, world)
+    loss = dist.vocab_parallel_linear_cross_entropy(h, w[v0:v1].contiguous(), t, v0)
+    rows = dist.vocab_parallel_linear_cross_entropy(h, w[v0:v1].contiguous(), t, v0, reduction="none")
+    single = linear_cross_entropy(h, w, t)
+    single_rows = linear_cross_entropy(h, w, t, reduction="none")
+    # --- GEMM column shards written into one output
+    a, wt, b = workloads.gemm_bf16(m=512, k=1024, n=2048)
+    a, wt, b = a.to(dev), wt.to(dev), b.to(dev)
+    n0, n1 = dist.column_range(wt.shape[0], rank, world)
+    y_part = matmul_add_bias(a, wt[n0:n1].contiguous(), b[n0:n1].contiguous())
+    y_full = matmul_add_bias(a, wt, b)
+    # --- decoder block, sequences sharded
+    cfg = dict(workloads.LLAMA3_8B, hidden=1024, ffn=2816, n_heads=8, n_kv_heads=2, head_dim=128)
+    wd = {k: v.to(dev) for k, v in workloads.block_weights(cfg).items()}
+    block = LlamaBlock(wd, 8, 2, cfg["eps"], cfg["theta"], max_seq_len=128)
+    x = workloads.block_input(4, 128, 1024).to(dev)
+    b0, b1 = dist.sequence_range(4, rank, world)
+    with torch.no_grad():
+        part = block(x[b0:b1].contiguous())
+        full = block(x)
+    torch.cuda.synchronize()
+    torch.save({"loss": loss.cpu(), "single": single.cpu(), "rows_equal": bool(torch.allclose(rows, single_rows, rtol=1e-6, atol=1e-6)),
+                "gemm_equal": bool(torch.equal(y_part, y_full[:, n0:n1])),
+                "block_equal": bool(torch.equal(part, full[b0:b1]))}, os.path.join(out_dir, f"r{rank}.pt"))
+    td.barrier()
+    td.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_two_ranks_match_single_gpu(tmp_path):
+    world = 2
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    outs = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
+    for o in outs:
+        torch.testing.assert_close(o["loss"], o["single"], rtol=1e-6, atol=1e-6)
+        assert o["rows_equal"] and o["gemm_equal"] and o["block_equal"]
+    assert torch.equal(outs[0]["loss"], outs[1]["loss"])
