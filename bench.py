@@ -17,7 +17,8 @@ block path.  Rank 0 prints ONE JSON line:
                         timed steps, against the measured cuBLAS bf16 peak
   ops                   each fused op alone at the configuration sizes (HBM GB/s or
                         TFLOP/s, fraction of the measured peak), row / column / vocab
-                        sharded over the ranks
+                        sharded over the ranks; the bandwidth ops are timed as one CUDA
+                        graph of back-to-back launches over rotating inputs
   cpu_baseline          (N=1) the CPU oracle of the same block on a bounded sample
   clocks                SM clock and throttle reasons sampled during the timed region
 
@@ -134,13 +135,30 @@ def device_weights(dev, seed=1006):
             "gate_proj": lin(ffn, hid), "up_proj": lin(ffn, hid), "down_proj": lin(hid, ffn)}
 
 
-def timed_loop(fn, arg_sets, iters, warm=3):
-    """Average device time per call of fn over rotating argument sets (CUDA events on the
-    current stream, back-to-back launches)."""
+def timed_loop(fn, arg_sets, iters, warm=3, graph=False):
+    """Average device time per call of fn over rotating argument sets: CUDA events on the
+    current stream around `iters` back-to-back launches.  With graph=True the launches are
+    captured into one CUDA graph and the replay is timed, which takes the Python and
+    allocator overhead of each call (10-15 us, more than some of these kernels run) off the
+    device timeline."""
     for i in range(warm):
         fn(*arg_sets[i % len(arg_sets)])
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(*arg_sets[i % len(arg_sets)])
+        g.replay()                      # one untimed replay
+        torch.cuda.synchronize()
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        secs = a.elapsed_time(b) * 1e-3 / iters
+        del g
+        return secs
     a.record()
     for i in range(iters):
         fn(*arg_sets[i % len(arg_sets)])
@@ -182,14 +200,14 @@ def bench_ops(dev, rank, world, peaks, src):
     rows = r1 - r0
     sets = [(rn(rows, 4096, dtype=torch.float32), rn(rows, 4096, dtype=torch.float32),
              1 + 0.1 * rn(4096, dtype=torch.float32), 1e-5) for _ in range(max(6, 6 * world))]
-    record("rmsnorm_residual_fp32", "hbm", rows * 4096 * 4 * 4, timed_loop(rmsnorm_residual, sets, 120),
+    record("rmsnorm_residual_fp32", "hbm", rows * 4096 * 4 * 4, timed_loop(rmsnorm_residual, sets, 120, graph=True),
            f"rows {rows} of 2048")
     del sets
     # config 2a: swiglu bf16 [8192, 14336]
     r0, r1 = dist.row_range(8192, rank, world)
     rows = r1 - r0
     sets = [(rn(rows, 14336), rn(rows, 14336)) for _ in range(2 if world == 1 else 3)]
-    record("swiglu_bf16", "hbm", rows * 14336 * 2 * 3, timed_loop(swiglu, sets, 30), f"rows {rows} of 8192")
+    record("swiglu_bf16", "hbm", rows * 14336 * 2 * 3, timed_loop(swiglu, sets, 30, graph=True), f"rows {rows} of 8192")
     del sets
     # config 2b: rope bf16 q [4,2048,32,128], k [4,2048,8,128]; sequences sharded, then positions
     if world <= 4:
@@ -202,7 +220,7 @@ def bench_ops(dev, rank, world, peaks, src):
     cos, sin = rope_tables(2048, 128, 500000.0, dev)
     cos, sin = cos[s0:s1].contiguous(), sin[s0:s1].contiguous()
     sets = [(rn(b, s1 - s0, 32, 128), rn(b, s1 - s0, 8, 128), cos, sin) for _ in range(6)]
-    record("rope_bf16", "hbm", b * (s1 - s0) * 40 * 128 * 2 * 2, timed_loop(rope, sets, 120),
+    record("rope_bf16", "hbm", b * (s1 - s0) * 40 * 128 * 2 * 2, timed_loop(rope, sets, 120, graph=True),
            f"batch {b} x positions {s0}..{s1}")
     del sets
     # config 2c: per-token fp8 quant bf16 [8192, 4096] with 0.1 % outliers x50
@@ -213,9 +231,9 @@ def bench_ops(dev, rank, world, peaks, src):
         x = torch.randn(rows, 4096, device=dev, generator=g)
         hot = torch.rand(rows, 4096, device=dev, generator=g) < 1e-3
         sets.append((torch.where(hot, x * 50, x).to(bf), "e4m3", "token"))
-    record("fp8_quant_token_bf16", "hbm", rows * 4096 * 3, timed_loop(fp8_quant, sets, 120), f"rows {rows} of 8192")
+    record("fp8_quant_token_bf16", "hbm", rows * 4096 * 3, timed_loop(fp8_quant, sets, 120, graph=True), f"rows {rows} of 8192")
     record("fp8_quant_block_bf16", "hbm", rows * 4096 * 3,
-           timed_loop(fp8_quant, [(s[0], "e4m3", "block") for s in sets], 120), f"rows {rows} of 8192")
+           timed_loop(fp8_quant, [(s[0], "e4m3", "block") for s in sets], 120, graph=True), f"rows {rows} of 8192")
     # config 3: matmul_add_bias bf16 8192 x 4096 x 14336, output columns sharded
     n0, n1 = dist.column_range(14336, rank, world)
     a, w, bias = rn(8192, 4096), rn(n1 - n0, 4096, scale=0.02), rn(n1 - n0, scale=0.02)

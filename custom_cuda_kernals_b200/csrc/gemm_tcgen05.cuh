@@ -14,7 +14,9 @@
 //                       thread owns one output row) while the MMA warp already
 //                       fills the other accumulator.
 // Tiles come from a scheduler policy, the epilogue from an epilogue policy.
-// No cluster launch and no multicast: every CTA fetches its own tiles.
+// gemm_kernel is that single-CTA form; gemm_pair_kernel further down runs the same
+// roles on a pair of CTAs that share a 256 x 256 tile (cta_group::2) and is the
+// default.  Every CTA fetches its own operand tiles; no load is shared across CTAs.
 // All waits are bounded; a time-out sets bit 0 of *status and the CTA leaves.
 #pragma once
 
