@@ -195,6 +195,26 @@ def bench_ops(dev, rank, world, peaks, src):
                      "frac": round(ach / peak, 4), "us_per_launch": round(seconds * 1e6, 2),
                      "peak_source": src, "shard": note}
 
+    cpu_on = world == 1 and rank == 0
+
+    def cpu(name, work, fn, sample):
+        """The oracle's CPU op chain on a bounded sample of the same inputs (all host cores)."""
+        if not cpu_on:
+            return
+        from oracle import ops as oracle_ops  # noqa: F401  (the fn closures use it)
+        torch.set_num_threads(os.cpu_count() or 1)
+        fn()
+        t0 = time.perf_counter()
+        fn()
+        fn()
+        dt = (time.perf_counter() - t0) / 2
+        scale = 1e9 if out[name]["bound"] == "hbm" else 1e12
+        out[name]["cpu_baseline"] = {"value": round(work / dt / scale, 3), "unit": out[name]["unit"],
+                                     "cores": torch.get_num_threads(), "kind": "port", "sample": sample,
+                                     "seconds": round(dt, 4)}
+
+    from oracle import ops as O
+
     # config 1: rmsnorm+residual fp32 [2048, 4096], rows sharded
     r0, r1 = dist.row_range(2048, rank, world)
     rows = r1 - r0
@@ -202,12 +222,18 @@ def bench_ops(dev, rank, world, peaks, src):
              1 + 0.1 * rn(4096, dtype=torch.float32), 1e-5) for _ in range(max(6, 6 * world))]
     record("rmsnorm_residual_fp32", "hbm", rows * 4096 * 4 * 4, timed_loop(rmsnorm_residual, sets, 120, graph=True),
            f"rows {rows} of 2048")
+    if cpu_on:
+        cx, cr, cw = (t.cpu() for t in sets[0][:3])
+        cpu("rmsnorm_residual_fp32", rows * 4096 * 16, lambda: O.rmsnorm_residual(cx, cr, cw, 1e-5), "all 2048 rows")
     del sets
     # config 2a: swiglu bf16 [8192, 14336]
     r0, r1 = dist.row_range(8192, rank, world)
     rows = r1 - r0
     sets = [(rn(rows, 14336), rn(rows, 14336)) for _ in range(2 if world == 1 else 3)]
     record("swiglu_bf16", "hbm", rows * 14336 * 2 * 3, timed_loop(swiglu, sets, 30, graph=True), f"rows {rows} of 8192")
+    if cpu_on:
+        cg, cu = sets[0][0][:2048].cpu(), sets[0][1][:2048].cpu()
+        cpu("swiglu_bf16", 2048 * 14336 * 6, lambda: O.swiglu(cg, cu), "2048 of 8192 rows")
     del sets
     # config 2b: rope bf16 q [4,2048,32,128], k [4,2048,8,128]; sequences sharded, then positions
     if world <= 4:
@@ -222,6 +248,9 @@ def bench_ops(dev, rank, world, peaks, src):
     sets = [(rn(b, s1 - s0, 32, 128), rn(b, s1 - s0, 8, 128), cos, sin) for _ in range(6)]
     record("rope_bf16", "hbm", b * (s1 - s0) * 40 * 128 * 2 * 2, timed_loop(rope, sets, 120, graph=True),
            f"batch {b} x positions {s0}..{s1}")
+    if cpu_on:
+        cq, ck, cc, cs = (t.cpu() for t in sets[0])
+        cpu("rope_bf16", b * (s1 - s0) * 40 * 128 * 4, lambda: O.rope(cq, ck, cc, cs), "all of config 2b")
     del sets
     # config 2c: per-token fp8 quant bf16 [8192, 4096] with 0.1 % outliers x50
     r0, r1 = dist.row_range(8192, rank, world)
@@ -234,16 +263,28 @@ def bench_ops(dev, rank, world, peaks, src):
     record("fp8_quant_token_bf16", "hbm", rows * 4096 * 3, timed_loop(fp8_quant, sets, 120, graph=True), f"rows {rows} of 8192")
     record("fp8_quant_block_bf16", "hbm", rows * 4096 * 3,
            timed_loop(fp8_quant, [(s[0], "e4m3", "block") for s in sets], 120, graph=True), f"rows {rows} of 8192")
+    if cpu_on:
+        cx8 = sets[0][0].cpu()
+        cpu("fp8_quant_token_bf16", rows * 4096 * 3, lambda: O.fp8_quant(cx8, "e4m3", "token"), "all 8192 rows")
+        cpu("fp8_quant_block_bf16", rows * 4096 * 3, lambda: O.fp8_quant(cx8, "e4m3", "block"), "all 8192 rows")
     # config 3: matmul_add_bias bf16 8192 x 4096 x 14336, output columns sharded
     n0, n1 = dist.column_range(14336, rank, world)
     a, w, bias = rn(8192, 4096), rn(n1 - n0, 4096, scale=0.02), rn(n1 - n0, scale=0.02)
     record("matmul_add_bias_bf16", "tensor", 2 * 8192 * 4096 * (n1 - n0),
            timed_loop(matmul_add_bias, [(a, w, bias)], 20), f"columns {n1 - n0} of 14336")
+    if cpu_on:
+        ca, cwt, cb = a[:1024].cpu(), w.cpu(), bias.cpu()
+        cpu("matmul_add_bias_bf16", 2 * 1024 * 4096 * (n1 - n0), lambda: O.matmul_add_bias(ca, cwt, cb),
+            "1024 of 8192 rows")
     a8, a_s = fp8_quant(sets[0][0], "e4m3", "token") if rows == 8192 else fp8_quant(a, "e4m3", "token")
     w8, w_s = fp8_quant(w, "e4m3", "token")
     record("matmul_add_bias_fp8", "tensor", 2 * 8192 * 4096 * (n1 - n0),
            timed_loop(matmul_add_bias_fp8, [(a8, a_s, w8, w_s, bias)], 20), f"columns {n1 - n0} of 14336")
     out["matmul_add_bias_fp8"]["note"] = "fraction is against the bf16 dense peak"
+    if cpu_on:
+        c8 = (a8[:256].cpu(), a_s[:256].cpu(), w8.cpu(), w_s.cpu(), bias.cpu())
+        cpu("matmul_add_bias_fp8", 2 * 256 * 4096 * (n1 - n0), lambda: O.matmul_add_bias_fp8(*c8),
+            "256 of 8192 rows (dequantise, fp32 matmul)")
     del sets, a, w, a8, w8
     # config 5: linear cross entropy 16384 x 4096 x 128256, vocabulary sharded + one all-gather
     v0, v1 = dist.vocab_range(128256, rank, world)
@@ -258,6 +299,10 @@ def bench_ops(dev, rank, world, peaks, src):
 
     record("linear_cross_entropy_bf16", "tensor", 2 * 16384 * 4096 * (v1 - v0),
            timed_loop(lce, [(h, wv, t)], 4 if world == 1 else 8, warm=2), f"vocab rows {v1 - v0} of 128256")
+    if cpu_on:
+        ch, cwv, ct = h[:256].cpu(), wv.cpu(), t[:256].cpu()
+        cpu("linear_cross_entropy_bf16", 2 * 256 * 4096 * (v1 - v0), lambda: O.linear_cross_entropy(ch, cwv, ct),
+            "256 of 16384 rows (eager: full logits, then cross entropy)")
     return out
 
 
@@ -389,22 +434,25 @@ def run_ours(args, rank, world, local):
 
     tokens = BATCH * SEQ
     totals = timer.totals()
-    gemm_ms = dist.max_over_ranks(totals["gemm"]["ms"], dev)
+    gemm_kinds = [k for k in totals if k.startswith("gemm")]          # plain, + swiglu, + residual epilogues
+    gemm_calls = sum(totals[k]["calls"] for k in gemm_kinds)
+    gemm_ms = dist.max_over_ranks(sum(totals[k]["ms"] for k in gemm_kinds), dev)
     gemm_flops = block.gemm_flops(nb * SEQ) * args.steps               # per rank
     ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
     peak = peaks["bf16_tflops_sustained"]
     line = base_line(args, world, tokens * args.steps / secs, secs / args.steps * 1e3)
-    line["roofline"] = {"kernel": "gemm_kernel<bf16> (matmul_add_bias, 7 launches per step)", "bound": "tensor",
+    line["roofline"] = {"kernel": f"gemm_pair_kernel<bf16> (tcgen05 GEMM, {gemm_calls // args.steps} launches per step: "
+                                  "q/k/v/o projections, gate-up + SwiGLU, down + residual)", "bound": "tensor",
                         "achieved": round(ach, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
                         "traffic": NCU_TRAFFIC_BYTES["gemm"], "peak_source": f"{src} (cuBLAS bf16, sustained)",
-                        "flops_per_launch_avg": gemm_flops // (7 * args.steps),
-                        "us_per_launch_avg": round(gemm_ms * 1e3 / totals["gemm"]["calls"], 1), "per_gpu": True}
+                        "flops_per_launch_avg": gemm_flops // gemm_calls,
+                        "us_per_launch_avg": round(gemm_ms * 1e3 / gemm_calls, 1), "per_gpu": True}
     line["step_breakdown_ms"] = {k: round(v["ms"] / args.steps, 4) for k, v in sorted(totals.items())}
     line["e2e"] = {"value": tokens * args.steps / e2e_secs, "unit": UNIT,
                    "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": out_host.numel() * 2 * world,
                    "ms_per_step": e2e_secs / args.steps * 1e3,
-                   "api": "LlamaBlock.forward_host(pinned x, pinned out): H2D, 11 library kernels + SDPA per group of sequences, D2H; groups pipelined over 3 streams"}
-    line["gpu_launches"] = LlamaBlock.LAUNCHES_PER_FORWARD * args.steps * world
+                   "api": "LlamaBlock.forward_host(pinned x, pinned out): H2D, 9 library kernels + SDPA per group of sequences, D2H; groups pipelined over 3 streams"}
+    line["gpu_launches"] = block.launches_per_forward * args.steps * world
     line["clocks"] = clocks.summary()
     line["parity"] = parity
     if not args.skip_ops:

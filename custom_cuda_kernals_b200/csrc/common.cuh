@@ -141,6 +141,20 @@ __device__ __forceinline__ float cta_reduce(float v, float* slots) {
     return r;
 }
 
+// ---------------------------------------------------------------- SwiGLU element
+// g * sigmoid(g) = g / (1 + 2^(-g*log2 e)); ex2.approx and the approximate divide are each
+// good to ~2 ulp, far inside the 1e-4 / 1e-2 tolerances.
+__device__ __forceinline__ float silu_f32(float g) {
+    const float e = exp2f(-g * 1.4426950408889634f);
+    return __fdividef(g, 1.0f + e);
+}
+// silu in fp32, rounded to the storage type, times `up`, rounded by the caller's store
+// (the order of roundings of baselines/swiglu.py:109-112).
+template <typename T>
+__device__ __forceinline__ float glu1(float g, float u) {
+    return Store<T>::round(silu_f32(g)) * u;
+}
+
 __host__ __device__ constexpr int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

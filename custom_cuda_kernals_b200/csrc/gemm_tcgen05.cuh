@@ -21,6 +21,7 @@
 #pragma once
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -88,6 +89,34 @@ struct SchedGemm {
         }
     };
 };
+
+// Reads one finished 128 x 256 accumulator (this thread's row) out of tensor memory and hands
+// it to the epilogue policy, 32 columns at a time.  A policy with kPairedHalves pairs column j
+// of the tile's first half with column j of its second half (gate / up of a fused SwiGLU GEMM)
+// and gets both 32-column pieces at once.
+template <class Epi, class = void> struct PairedHalves { static constexpr bool value = false; };
+template <class Epi> struct PairedHalves<Epi, std::enable_if_t<Epi::kPairedHalves>> { static constexpr bool value = true; };
+
+template <class Epi>
+__device__ __forceinline__ void drain_tile(const typename Epi::Params& ep, typename Epi::Thread& th, const TileWork& w,
+                                           int row_in_tile, uint32_t t0, float* scratch) {
+    if constexpr (PairedHalves<Epi>::value) {
+#pragma unroll 1
+        for (int c = 0; c < kBN / 64; ++c) {
+            float lo[32], hi[32];
+            ptx::tmem_ld32(t0 + c * 32, lo);
+            ptx::tmem_ld32(t0 + kBN / 2 + c * 32, hi);
+            Epi::chunk2(ep, th, w, row_in_tile, c * 32, lo, hi, scratch);
+        }
+    } else {
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+            float acc[32];
+            ptx::tmem_ld32(t0 + c * 32, acc);
+            Epi::chunk(ep, th, w, row_in_tile, c * 32, acc, scratch);
+        }
+    }
+}
 
 // ---- kernel
 template <bool kFp8, class Sched, class Epi>
@@ -208,12 +237,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (!__all_sync(0xffffffffu, got)) break;
             ptx::tc_fence_after_sync();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
-#pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
-                float acc[32];
-                ptx::tmem_ld32(t0 + c * 32, acc);
-                Epi::chunk(ep, th, w, row_in_tile, c * 32, acc, my_scratch);
-            }
+            drain_tile<Epi>(ep, th, w, row_in_tile, t0, my_scratch);
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
@@ -386,12 +410,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (!__all_sync(0xffffffffu, got)) break;
             ptx::tc_fence_after_sync();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
-#pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
-                float acc[32];
-                ptx::tmem_ld32(t0 + c * 32, acc);
-                Epi::chunk(ep, th, w, row_in_tile, c * 32, acc, my_scratch);
-            }
+            drain_tile<Epi>(ep, th, w, row_in_tile, t0, my_scratch);
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(buf), 0));

@@ -6,8 +6,8 @@
 // in the epilogue and one rounding to the storage type (gemm_tcgen05.cuh).
 // An FP8 entry point (e4m3 operands, per-token and per-channel scales folded
 // into the epilogue) has no counterpart in the reference.
-// fp32 inputs and shapes TMA cannot address (K not a multiple of 8 elements,
-// fewer rows than one box) use the CUDA-core kernel in gemm_simt.cuh.
+// fp32 inputs, shapes TMA cannot address (K not a multiple of 8 elements) and
+// problems below ~4 MFLOP use the CUDA-core kernel in gemm_simt.cuh.
 //
 // Tensor-bound: 2*M*N*K flops per launch.
 #include <type_traits>
@@ -124,7 +124,10 @@ struct EpiScaledBias {
 
 template <typename T>
 bool tc_applicable(const void* x, const void* w, int64_t m, int64_t k, int64_t n) {
-    return k % 8 == 0 && k >= 64 && m >= kBM && n >= kBN && aligned16(x) && aligned16(w) &&
+    // rows must be 16-byte multiples for TMA; partial and even undersized tiles are fine (TMA
+    // zero-fills outside the matrix, the epilogue masks), but below ~4 MFLOP the CUDA-core
+    // kernel is as fast and skips building two tensor maps
+    return k % 8 == 0 && aligned16(x) && aligned16(w) && 2 * m * n * k >= (1LL << 22) &&
            m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31);
 }
 

@@ -1,0 +1,185 @@
+// GEMMs of the decoder block with the neighbouring elementwise op folded into the
+// epilogue (no counterpart in the reference, which runs these as separate kernels:
+// examples/llama_block.py:168-172 computes gate_proj, up_proj, swiglu, down_proj and
+// the residual add one after the other).
+//
+//   matmul_swiglu:             y[M,F]  = silu(x @ Wg^T) * (x @ Wu^T)
+//   matmul_add_bias_residual:  y[M,N]  = x @ W^T + bias + residual
+//
+// Both reuse the tcgen05 mainloop of gemm_tcgen05.cuh.  For the SwiGLU form the gate
+// and up weights are interleaved in blocks of 128 output features (rows [256j, 256j+128)
+// of the fused weight are gate rows [128j, 128j+128), the next 128 rows the matching up
+// rows), so one 256-column accumulator tile holds gate columns in its first half and the
+// matching up columns in its second half; in the CTA-pair kernel CTA 0 loads the gate
+// half and CTA 1 the up half.  The epilogue rounds exactly where the unfused chain
+// rounds (GEMM output to the storage type, silu to the storage type, product to the
+// storage type; GEMM output to the storage type before the residual add), so the fused
+// results equal the unfused ones bit for bit.
+//
+// Tensor-bound; what the fusion removes is HBM traffic: 2*M*F*sizeof(T) written and
+// read again for gate/up, M*N*sizeof(T) written and read again for the residual add.
+#include <type_traits>
+
+#include "gemm_tcgen05.cuh"
+
+namespace cck {
+namespace tc {
+
+template <typename T>
+__device__ __forceinline__ void store32(T* out, const float (&v)[32], int64_t col, int64_t n, int vec_ok) {
+    if (vec_ok && col + 32 <= n) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            Vec16 o;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o.w[i] = Store<T>::pack2(v[8 * q + 2 * i], v[8 * q + 2 * i + 1]);
+            st_stream(out + 8 * q, o);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col + j < n) Store<T>::store1(out + j, v[j]);
+    }
+}
+
+// ---- epilogue: y = silu(gate) * up, gate = first half of the tile, up = second half
+template <typename T>
+struct EpiSwiGLU {
+    static constexpr bool kPairedHalves = true;
+    struct Params {
+        T* y;
+        int64_t m, f;      // y is [m, f]
+        int vec_ok;
+    };
+    struct Thread {};
+    __device__ static __forceinline__ void tile_begin(const Params&, Thread&, const TileWork&, float*, int, int) {}
+    __device__ static __forceinline__ void chunk2(const Params& p, Thread&, const TileWork& w, int row_in_tile, int c0,
+                                                  float (&gate)[32], float (&up)[32], const float*) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        const int64_t col = static_cast<int64_t>(w.n_tile) * (kBN / 2) + c0;
+        if (row >= p.m || col >= p.f) return;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) gate[j] = glu1<T>(Store<T>::round(gate[j]), Store<T>::round(up[j]));
+        store32<T>(p.y + row * p.f + col, gate, col, p.f, p.vec_ok);
+    }
+    __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
+};
+
+// ---- epilogue: y = round(acc + bias) + residual
+template <typename T>
+struct EpiBiasResidual {
+    struct Params {
+        const T* bias;       // [n] or null
+        const T* residual;   // [m, n]
+        T* y;
+        int64_t m, n;
+        int vec_ok;
+    };
+    struct Thread {};
+    __device__ static __forceinline__ void tile_begin(const Params& p, Thread&, const TileWork& w, float* scratch,
+                                                      int lane, int) {
+        const int64_t n0 = static_cast<int64_t>(w.n_tile) * kBN;
+#pragma unroll
+        for (int i = 0; i < kBN / 32; ++i) {
+            const int64_t col = n0 + lane + 32 * i;
+            scratch[lane + 32 * i] = (p.bias != nullptr && col < p.n) ? Store<T>::load1(p.bias + col) : 0.0f;
+        }
+    }
+    __device__ static __forceinline__ void chunk(const Params& p, Thread&, const TileWork& w, int row_in_tile, int c0,
+                                                 float (&acc)[32], const float* scratch) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        const int64_t col = static_cast<int64_t>(w.n_tile) * kBN + c0;
+        if (row >= p.m || col >= p.n) return;
+        const T* res = p.residual + row * p.n + col;
+        if (p.vec_ok && col + 32 <= p.n) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float r[8];
+                unpack<T>(ld_stream(res + 8 * q), r);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[8 * q + i] = Store<T>::round(acc[8 * q + i] + scratch[c0 + 8 * q + i]) + r[i];
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col + j < p.n) acc[j] = Store<T>::round(acc[j] + scratch[c0 + j]) + Store<T>::load1(res + j);
+        }
+        store32<T>(p.y + row * p.n + col, acc, col, p.n, p.vec_ok);
+    }
+    __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
+};
+
+inline bool tc_shape_ok(const void* a, const void* b, int64_t m, int64_t k, int64_t n) {
+    return k % 8 == 0 && k >= 8 && aligned16(a) && aligned16(b) && m < (1LL << 31) && n < (1LL << 31) &&
+           k < (1LL << 31);
+}
+
+template <typename T, class Epi>
+cudaError_t run_fused(const void* x, const void* w, int64_t m, int64_t k, int64_t n_rows_of_w,
+                      const typename Epi::Params& ep, cudaStream_t s) {
+    constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+    const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const int m_tiles = static_cast<int>(ceil_div64(m, kBM)), n_tiles = static_cast<int>(ceil_div64(n_rows_of_w, kBN));
+    const uint32_t fmt = is_bf16 ? 1u : 0u;
+    const bool pair = m_tiles >= 2 && pair_kernels_enabled() && max_pairs<false, SchedGemm, Epi>() > 0;
+    CUtensorMap ta, tb;
+    cudaError_t e = make_tmap(&ta, dt, 2, x, m, k, kBM);
+    if (e != cudaSuccess) return e;
+    e = make_tmap(&tb, dt, 2, w, n_rows_of_w, k, pair ? 128 : kBN);
+    if (e != cudaSuccess) return e;
+    if (pair) {
+        const int m_pairs = (m_tiles + 1) / 2;
+        SchedGemm::Params sp{m_pairs, n_tiles, raster_group(2 * kBM, k, 2, m_pairs)};
+        return launch_pair<false, SchedGemm, Epi>(ta, tb, sp, ep, k, ptx::instr_desc(fmt, fmt, 2 * kBM, kBN),
+                                                  static_cast<int64_t>(m_pairs) * n_tiles, s);
+    }
+    SchedGemm::Params sp{m_tiles, n_tiles, raster_group(kBM, k, 2, m_tiles)};
+    const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
+    const int ctas = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    return launch<false, SchedGemm, Epi>(ta, tb, sp, ep, k, ptx::instr_desc(fmt, fmt, kBM, kBN), ctas, s);
+}
+
+}  // namespace tc
+}  // namespace cck
+
+extern "C" int32_t launch_matmul_swiglu_fwd(const void* x, const void* w_gate_up, void* y, int64_t m, int64_t k,
+                                            int64_t f, int32_t dtype, void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (m <= 0 || k <= 0 || f <= 0) return cudaSuccess;
+    if (f % 128 != 0 || !tc_shape_ok(x, w_gate_up, m, k, 2 * f)) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int vec_ok = (f % 8 == 0 && aligned16(y)) ? 1 : 0;
+    if (dtype == kBF16) {
+        EpiSwiGLU<__nv_bfloat16>::Params ep{static_cast<__nv_bfloat16*>(y), m, f, vec_ok};
+        return run_fused<__nv_bfloat16, EpiSwiGLU<__nv_bfloat16>>(x, w_gate_up, m, k, 2 * f, ep, s);
+    }
+    if (dtype == kF16) {
+        EpiSwiGLU<__half>::Params ep{static_cast<__half*>(y), m, f, vec_ok};
+        return run_fused<__half, EpiSwiGLU<__half>>(x, w_gate_up, m, k, 2 * f, ep, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+extern "C" int32_t launch_matmul_add_bias_residual_fwd(const void* x, const void* weight, const void* bias,
+                                                       const void* residual, void* y, int64_t m, int64_t k,
+                                                       int64_t n, int32_t dtype, void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (m <= 0 || k <= 0 || n <= 0) return cudaSuccess;
+    if (residual == nullptr || !tc_shape_ok(x, weight, m, k, n)) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int vec_ok = (n % 8 == 0 && aligned16(y) && aligned16(residual)) ? 1 : 0;
+    if (dtype == kBF16) {
+        EpiBiasResidual<__nv_bfloat16>::Params ep{static_cast<const __nv_bfloat16*>(bias),
+                                                  static_cast<const __nv_bfloat16*>(residual),
+                                                  static_cast<__nv_bfloat16*>(y), m, n, vec_ok};
+        return run_fused<__nv_bfloat16, EpiBiasResidual<__nv_bfloat16>>(x, weight, m, k, n, ep, s);
+    }
+    if (dtype == kF16) {
+        EpiBiasResidual<__half>::Params ep{static_cast<const __half*>(bias), static_cast<const __half*>(residual),
+                                           static_cast<__half*>(y), m, n, vec_ok};
+        return run_fused<__half, EpiBiasResidual<__half>>(x, weight, m, k, n, ep, s);
+    }
+    return cudaErrorInvalidValue;
+}

@@ -321,6 +321,58 @@ void matmul_add_bias_fp8_fwd(const at::Tensor& a, const at::Tensor& a_scale, con
                                                 l.stream));
 }
 
+// fused epilogues (no counterpart in the reference)
+void matmul_swiglu_fwd(const at::Tensor& x, const at::Tensor& w_gate_up, const at::Tensor& y) {
+    const int32_t dt = tag_of("x", x);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "' for the fused path; expected float16 or bfloat16");
+    expect_same_dtype("w_gate_up", tag_of("w_gate_up", w_gate_up), dt);
+    expect_same_dtype("y", tag_of("y", y), dt);
+    if (x.dim() != 2 || w_gate_up.dim() != 2)
+        value_error("shape mismatch: x and w_gate_up must be 2-D; got x=" + shape_str(x) + ", w_gate_up=" + shape_str(w_gate_up));
+    const int64_t m = x.size(0), k = x.size(1), f2 = w_gate_up.size(0);
+    if (w_gate_up.size(1) != k)
+        value_error("shape mismatch: w_gate_up's in_features (" + std::to_string(w_gate_up.size(1)) +
+                    ") must match x's last dim (" + std::to_string(k) + ")");
+    if (f2 % 256 != 0) value_error("shape mismatch: w_gate_up must have a multiple of 256 rows (128-feature gate/up blocks)");
+    if (k % 8 != 0) value_error("shape mismatch: the fused path needs K to be a multiple of 8");
+    const int64_t f = f2 / 2;
+    if (y.dim() != 2 || y.size(0) != m || y.size(1) != f)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " + std::to_string(f) + "]");
+    Launch l(x, {&w_gate_up, &y});
+    check_launch("launch_matmul_swiglu_fwd",
+                 launch_matmul_swiglu_fwd(x.data_ptr(), w_gate_up.data_ptr(), y.data_ptr(), m, k, f, dt, l.stream));
+}
+
+void matmul_add_bias_residual_fwd(const at::Tensor& x, const at::Tensor& weight, const c10::optional<at::Tensor>& bias,
+                                  const at::Tensor& residual, const at::Tensor& y) {
+    const int32_t dt = tag_of("x", x);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "' for the fused path; expected float16 or bfloat16");
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_same_dtype("residual", tag_of("residual", residual), dt);
+    expect_same_dtype("y", tag_of("y", y), dt);
+    const bool has_bias = bias.has_value() && bias->defined();
+    if (has_bias) expect_same_dtype("bias", tag_of("bias", *bias), dt);
+    if (x.dim() != 2 || weight.dim() != 2)
+        value_error("shape mismatch: x and weight must be 2-D; got x=" + shape_str(x) + ", weight=" + shape_str(weight));
+    const int64_t m = x.size(0), k = x.size(1), n = weight.size(0);
+    if (weight.size(1) != k)
+        value_error("shape mismatch: weight's in_features (" + std::to_string(weight.size(1)) +
+                    ") must match x's last dim (" + std::to_string(k) + ")");
+    if (k % 8 != 0) value_error("shape mismatch: the fused path needs K to be a multiple of 8");
+    for (const at::Tensor* t : {&residual, &y})
+        if (t->dim() != 2 || t->size(0) != m || t->size(1) != n)
+            value_error("shape mismatch: residual and y must be [" + std::to_string(m) + ", " + std::to_string(n) + "]");
+    if (has_bias && (bias->dim() != 1 || bias->size(0) != n))
+        value_error("shape mismatch: bias shape " + shape_str(*bias) + " must be [" + std::to_string(n) + "]");
+    at::Tensor none;
+    Launch l(x, {&weight, &residual, &y, has_bias ? &*bias : &none});
+    check_launch("launch_matmul_add_bias_residual_fwd",
+                 launch_matmul_add_bias_residual_fwd(x.data_ptr(), weight.data_ptr(), has_bias ? bias->data_ptr() : nullptr,
+                                                     residual.data_ptr(), y.data_ptr(), m, k, n, dt, l.stream));
+}
+
 // ------------------------------------------------------------------ src/kernels/linear_cross_entropy.rs:44-133
 void linear_ce_chunk_update(const at::Tensor& logits_chunk, const at::Tensor& targets, int64_t v_start,
                             const at::Tensor& running_max, const at::Tensor& running_sum,
@@ -442,6 +494,9 @@ PYBIND11_MODULE(_native, m) {
           py::arg("fp8_format"));
     m.def("matmul_add_bias_fp8_fwd", &matmul_add_bias_fp8_fwd, py::arg("a_fp8"), py::arg("a_scale"), py::arg("w_fp8"),
           py::arg("w_scale"), py::arg("bias").none(true), py::arg("y"));
+    m.def("matmul_swiglu_fwd", &matmul_swiglu_fwd, py::arg("x"), py::arg("w_gate_up"), py::arg("y"));
+    m.def("matmul_add_bias_residual_fwd", &matmul_add_bias_residual_fwd, py::arg("x"), py::arg("weight"),
+          py::arg("bias").none(true), py::arg("residual"), py::arg("y"));
     m.def("linear_cross_entropy_fwd", &linear_cross_entropy_fwd, py::arg("hidden"), py::arg("weight"),
           py::arg("targets"), py::arg("v_start"), py::arg("row_stats"), py::arg("workspace"));
     m.def("lce_workspace_bytes", &lce_workspace_bytes, py::arg("like"), py::arg("n"), py::arg("v_count"));

@@ -18,18 +18,6 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
-__device__ __forceinline__ float silu_f32(float g) {
-    // g * sigmoid(g) = g / (1 + 2^(-g*log2 e)); ex2.approx and the approximate
-    // divide are each good to ~2 ulp, far inside the 1e-4 / 1e-2 tolerances.
-    const float e = exp2f(-g * 1.4426950408889634f);
-    return __fdividef(g, 1.0f + e);
-}
-
-template <typename T>
-__device__ __forceinline__ float glu1(float g, float u) {
-    return Store<T>::round(silu_f32(g)) * u;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ y,

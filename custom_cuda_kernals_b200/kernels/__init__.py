@@ -3,4 +3,4 @@
 so ``kernels.rope`` is the module, as in the reference).
 """
 
-from . import fp8_quant, linear_cross_entropy, matmul_add_bias, rmsnorm_residual, rope, swiglu  # noqa: F401
+from . import fp8_quant, fused, linear_cross_entropy, matmul_add_bias, rmsnorm_residual, rope, swiglu  # noqa: F401

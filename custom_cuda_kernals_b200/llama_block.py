@@ -9,8 +9,11 @@ RoPE, SwiGLU FFN, with the same op order
 
 The reference swaps in its three bandwidth-bound kernels and leaves every
 projection to ``nn.Linear`` (cuBLAS); here the seven projections also run on this
-library's tcgen05 GEMM (``matmul_add_bias`` with no bias).  The attention core
-stays ``torch.nn.functional.scaled_dot_product_attention`` as in the reference.
+library's tcgen05 GEMM (``matmul_add_bias`` with no bias), and by default two of
+them carry the neighbouring elementwise op in their epilogue - gate/up + SwiGLU in
+one GEMM, down_proj + the final residual add in another - with results identical to
+the unfused chain (``fused=False`` runs that chain).  The attention core stays
+``torch.nn.functional.scaled_dot_product_attention`` as in the reference.
 Forward only, no autograd.
 """
 
@@ -21,6 +24,7 @@ from typing import Callable
 import torch
 import torch.nn.functional as F
 
+from .kernels.fused import GATE_UP_BLOCK, interleave_gate_up, matmul_add_bias_residual, matmul_swiglu
 from .kernels.matmul_add_bias import matmul_add_bias
 from .kernels.rmsnorm_residual import rmsnorm_residual
 from .kernels.rope import rope
@@ -78,11 +82,8 @@ class LlamaBlock:
     """One decoder block; ``weights`` maps PARAM_NAMES to CUDA tensors
     (projections as ``[out_features, in_features]``, the nn.Linear layout)."""
 
-    #: kernels of this library launched per forward call (2 norms, 7 GEMMs, rope, swiglu)
-    LAUNCHES_PER_FORWARD = 11
-
     def __init__(self, weights: dict[str, torch.Tensor], n_heads: int = 32, n_kv_heads: int = 8,
-                 eps: float = 1e-5, theta: float = 500000.0, max_seq_len: int = 2048):
+                 eps: float = 1e-5, theta: float = 500000.0, max_seq_len: int = 2048, fused: bool = True):
         missing = [n for n in PARAM_NAMES if n not in weights]
         if missing:
             raise ValueError(f"missing block parameters: {missing}")
@@ -96,6 +97,16 @@ class LlamaBlock:
         self.eps = eps
         dev = self.w["q_proj"].device
         self.cos, self.sin = rope_tables(max_seq_len, self.head_dim, theta, dev)
+        ffn, dt = self.w["gate_proj"].shape[0], self.w["gate_proj"].dtype
+        self.fused = bool(fused and ffn % GATE_UP_BLOCK == 0 and self.hidden % 8 == 0 and ffn % 8 == 0
+                          and dt in (torch.float16, torch.bfloat16))
+        if self.fused:      # one-time re-layout; the separate gate/up weights are not kept
+            self.w_gate_up = interleave_gate_up(self.w["gate_proj"], self.w["up_proj"])
+            self.ffn = ffn
+            del self.w["gate_proj"], self.w["up_proj"]
+        #: kernels of this library launched per forward call: 2 norms, rope, q/k/v/o GEMMs and
+        #: either gate + up + swiglu + down (unfused) or gate-up-swiglu + down-residual (fused)
+        self.launches_per_forward = 9 if self.fused else 11
 
     def forward(self, x: torch.Tensor, timer: OpTimer | None = None, pos_offset: int = 0) -> torch.Tensor:
         """x ``[B, S, hidden]`` -> ``[B, S, hidden]``.  ``pos_offset`` is the position of
@@ -120,11 +131,15 @@ class LlamaBlock:
         att = t.run("copy", lambda a: a.transpose(1, 2).contiguous().view(b * s, hid), att)
         att = t.run("gemm", matmul_add_bias, att, w["o_proj"])
         h2, res2 = t.run("rmsnorm", rmsnorm_residual, att, res, w["post_attention_layernorm_weight"], self.eps)
-        gate = t.run("gemm", matmul_add_bias, h2, w["gate_proj"])
-        up = t.run("gemm", matmul_add_bias, h2, w["up_proj"])
-        act = t.run("swiglu", swiglu, gate, up)
-        mlp = t.run("gemm", matmul_add_bias, act, w["down_proj"])
-        out = t.run("add", torch.add, mlp, res2)
+        if self.fused:
+            act = t.run("gemm_swiglu", matmul_swiglu, h2, self.w_gate_up)
+            out = t.run("gemm_residual", matmul_add_bias_residual, act, w["down_proj"], None, res2)
+        else:
+            gate = t.run("gemm", matmul_add_bias, h2, w["gate_proj"])
+            up = t.run("gemm", matmul_add_bias, h2, w["up_proj"])
+            act = t.run("swiglu", swiglu, gate, up)
+            mlp = t.run("gemm", matmul_add_bias, act, w["down_proj"])
+            out = t.run("add", torch.add, mlp, res2)
         return out.view(b, s, hid)
 
     __call__ = forward
@@ -165,5 +180,6 @@ class LlamaBlock:
 
     def gemm_flops(self, tokens: int) -> int:
         """2*M*K*N summed over the seven projections for ``tokens`` rows."""
-        return sum(2 * tokens * self.w[n].shape[0] * self.w[n].shape[1]
-                   for n in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"))
+        shapes = [self.w[n].shape for n in ("q_proj", "k_proj", "v_proj", "o_proj", "down_proj")]
+        shapes += [self.w_gate_up.shape] if self.fused else [self.w["gate_proj"].shape, self.w["up_proj"].shape]
+        return sum(2 * tokens * o * i for o, i in shapes)

@@ -118,6 +118,22 @@ int64_t cck_lce_noalloc_max_workspace_bytes(void);
 int32_t launch_lce_finalize(const float* stats, const int64_t* targets, int64_t n, int64_t n_shards,
                             int64_t ignore_index, float* loss_rows, float* reduce_out, void* stream);
 
+/* Fused gate/up projection + SwiGLU: y[m, f] = silu(x @ Wg^T) * (x @ Wu^T).  w_gate_up is
+ * [2f, k]: for every block j of 128 output features, rows [256j, 256j+128) hold rows
+ * [128j, 128j+128) of Wg and rows [256j+128, 256j+256) the same rows of Wu.  Rounds where the
+ * unfused chain rounds (launch_matmul_add_bias_fwd twice, then launch_swiglu_fwd), so the result
+ * is identical.  dtype CCK_BF16 or CCK_F16; f % 128 == 0, k % 8 == 0, 16-byte aligned operands;
+ * otherwise cudaErrorInvalidValue. */
+int32_t launch_matmul_swiglu_fwd(const void* x, const void* w_gate_up, void* y, int64_t m, int64_t k,
+                                 int64_t f, int32_t dtype, void* stream);
+
+/* y = x @ weight^T + bias + residual (residual [m, n], bias [n] or NULL), identical to
+ * launch_matmul_add_bias_fwd followed by an elementwise add in the storage type.  dtype CCK_BF16
+ * or CCK_F16; k % 8 == 0, 16-byte aligned x and weight; otherwise cudaErrorInvalidValue. */
+int32_t launch_matmul_add_bias_residual_fwd(const void* x, const void* weight, const void* bias,
+                                            const void* residual, void* y, int64_t m, int64_t k, int64_t n,
+                                            int32_t dtype, void* stream);
+
 /* Number of two-CTA pairs the tensor-core GEMM keeps resident on the current device; 0 means
  * the pair kernel is unavailable (or disabled with CCK_GEMM_SINGLE_CTA=1) and the single-CTA
  * kernel is used. */

@@ -47,8 +47,13 @@ def _check(cfg, batch, seq):
         want = ops.llama_block(x, w, **kw).float()
         truth = ops.llama_block(x.float(), {k: v.float() for k, v in w.items()}, **kw)
         wd = {k: v.to(DEV) for k, v in w.items()}
-        block = LlamaBlock(wd, cfg["n_heads"], cfg["n_kv_heads"], cfg["eps"], cfg["theta"], max_seq_len=seq)
+        block = LlamaBlock(dict(wd), cfg["n_heads"], cfg["n_kv_heads"], cfg["eps"], cfg["theta"], max_seq_len=seq)
         got_dev = block(x.to(DEV))
+        # the fused epilogues (gate-up + SwiGLU, down + residual) change nothing, bit for bit
+        unfused = LlamaBlock(dict(wd), cfg["n_heads"], cfg["n_kv_heads"], cfg["eps"], cfg["theta"], max_seq_len=seq,
+                             fused=False)
+        assert block.fused == (cfg["ffn"] % 128 == 0) and not unfused.fused
+        assert torch.equal(got_dev, unfused(x.to(DEV)))
         eager_dev = _gpu_eager_block(x.to(DEV), wd, cfg["n_heads"], cfg["n_kv_heads"], cfg["eps"], cfg["theta"])
     assert got_dev.shape == x.shape and got_dev.dtype == torch.bfloat16
     got = got_dev.cpu().float()

@@ -96,3 +96,57 @@ def test_fp8_gemm_matches_oracle(shape):
     rel = (y.cpu().double() - full).norm() / full.norm()
     assert rel < 0.08, rel
     assert device_status_clean(y)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 1024, 1408), (130, 72, 384), (4096, 4096, 14336)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fused_gate_up_swiglu_equals_unfused_chain(shape, dtype):
+    """One GEMM over the interleaved gate/up weight with the SwiGLU in its epilogue gives, bit
+    for bit, what matmul_add_bias x 2 followed by swiglu gives (same roundings in the same
+    places), and so inherits their parity with the oracle."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    from custom_cuda.kernels.swiglu import swiglu
+    from custom_cuda_kernals_b200.kernels.fused import interleave_gate_up, matmul_swiglu
+    m, k, f = shape
+    g = torch.Generator().manual_seed(f + m)
+    x = torch.randn(m, k, generator=g).to(dtype).to(DEV)
+    wg = (0.05 * torch.randn(f, k, generator=g)).to(dtype).to(DEV)
+    wu = (0.05 * torch.randn(f, k, generator=g)).to(dtype).to(DEV)
+    fused = matmul_swiglu(x, interleave_gate_up(wg, wu))
+    chain = swiglu(matmul_add_bias(x, wg), matmul_add_bias(x, wu))
+    assert torch.equal(fused, chain)
+    if m * k * f <= 1 << 31:
+        want = ops.swiglu(ops.matmul_add_bias(x.cpu(), wg.cpu()), ops.matmul_add_bias(x.cpu(), wu.cpu()))
+        check(fused, want, dtype, ops.TOLERANCE_GEMM)
+    assert device_status_clean(fused)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 1408, 1024), (131, 72, 777), (4096, 14336, 4096)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_fused_residual_add_equals_unfused_chain(shape, with_bias):
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    from custom_cuda_kernals_b200.kernels.fused import matmul_add_bias_residual
+    m, k, n = shape
+    g = torch.Generator().manual_seed(n + m)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (0.05 * torch.randn(n, k, generator=g)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(torch.bfloat16).to(DEV) if with_bias else None
+    r = torch.randn(m, n, generator=g).to(torch.bfloat16).to(DEV)
+    fused = matmul_add_bias_residual(x, w, b, r)
+    assert torch.equal(fused, matmul_add_bias(x, w, b) + r)
+    assert device_status_clean(fused)
+
+
+def test_fused_ops_reject_what_they_cannot_run():
+    from custom_cuda_kernals_b200.kernels.fused import interleave_gate_up, matmul_add_bias_residual, matmul_swiglu
+    x = torch.randn(16, 64, device=DEV)
+    with pytest.raises(ValueError):
+        matmul_swiglu(x, torch.randn(256, 64, device=DEV))                 # float32
+    with pytest.raises(ValueError):
+        interleave_gate_up(torch.randn(100, 64), torch.randn(100, 64))     # F not a multiple of 128
+    xb = x.to(torch.bfloat16)
+    with pytest.raises(ValueError):
+        matmul_swiglu(xb, torch.randn(128, 64, device=DEV).to(torch.bfloat16))   # rows not a multiple of 256
+    with pytest.raises(ValueError):
+        matmul_add_bias_residual(xb, torch.randn(32, 64, device=DEV).to(torch.bfloat16), None,
+                                 torch.randn(16, 31, device=DEV).to(torch.bfloat16))
