@@ -48,9 +48,23 @@ UNIT = "tokens/s"
 BATCH, SEQ = 8, 2048
 CFG = dict(hidden=4096, ffn=14336, n_heads=32, n_kv_heads=8, head_dim=128, eps=1e-5, theta=500000.0)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
-# ncu capture summarised under profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = {"gemm": None}
+# DRAM traffic of the dominant kernel: ncu measured dram__bytes_read.sum + dram__bytes_write.sum =
+# 157.4 MB per launch of gemm_pair_kernel on the 4096 x 4096 x 8192 case (A + W + y = 167.8 MB of
+# algorithmic bytes; profiles/gemm_pair_kernel_bf16_4096x4096x8192.md).  The step's GEMM launches
+# are too large to replay under ncu, so their traffic is that ratio times their own A + W (+
+# residual) + y bytes - the kernel reads and writes each operand once whatever the size.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 157.4 / 167.8
+
+
+# Everything except the final JSON line goes to stderr - including what native libraries print
+# to file descriptor 1 (NCCL's version banner): fd 1 is pointed at stderr for the whole run and
+# the JSON line is written to a saved copy of the original stdout.
+_REAL_STDOUT = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit(line: dict):
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
 
 
 def log(*a):
@@ -312,18 +326,18 @@ def cpu_block_step(x, w):
         return ops.llama_block(x, w, CFG["n_heads"], CFG["n_kv_heads"], CFG["eps"], CFG["theta"])
 
 
-def cpu_sample_tokens_per_s(w_cpu, steps, warm, seed=7):
-    """The oracle block on batch 1 x seq 2048 (1/8 of one step's tokens) on all host cores."""
+def cpu_sample_tokens_per_s(w_cpu, steps, warm, batch=1, seed=7):
+    """The oracle block on `batch` x seq 2048 (batch/8 of one step's tokens) on all host cores."""
     torch.set_num_threads(os.cpu_count() or 1)
     g = torch.Generator().manual_seed(seed)
-    x = (0.02 * torch.randn(1, SEQ, CFG["hidden"], generator=g)).to(torch.bfloat16)
+    x = (0.02 * torch.randn(batch, SEQ, CFG["hidden"], generator=g)).to(torch.bfloat16)
     for _ in range(warm):
         cpu_block_step(x, w_cpu)
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_block_step(x, w_cpu)
     dt = (time.perf_counter() - t0) / steps
-    return SEQ / dt, dt
+    return batch * SEQ / dt, dt
 
 
 def cpu_weights(seed=1006):
@@ -347,15 +361,15 @@ def run_reference(args, rank, world):
         return
     steps, warm = max(1, args.steps), max(0, args.warmup)
     w = cpu_weights()
-    tps, dt = cpu_sample_tokens_per_s(w, steps, warm)
+    tps, dt = cpu_sample_tokens_per_s(w, steps, warm, batch=2)
     line = base_line(args, world, tps, dt * 1e3)
     line.update({"impl": "reference", "scaling": "strong",
                  "cpu_baseline": {"value": tps, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                                  "sample": f"oracle block (eager baselines' op chain) on batch 1 x seq {SEQ}, "
-                                            f"{steps} timed step(s) after {warm} warm-up; tokens/s = {SEQ} / step time"},
+                                  "sample": f"oracle block (eager baselines' op chain) on batch 2 x seq {SEQ} (1/4 of a "
+                                            f"step), {steps} timed step(s) after {warm} warm-up; tokens/s = {2 * SEQ} / step time"},
                  "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                  })
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # --------------------------------------------------------------------------- our arm
@@ -410,12 +424,23 @@ def run_ours(args, rank, world, local):
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
             for _ in range(args.steps):
-                block(x_dev, timer=timer)
+                block(x_dev)
             ev1.record()
             torch.cuda.synchronize()
             if world > 1:
                 torch.distributed.barrier()
             secs = dist.max_over_ranks(ev0.elapsed_time(ev1) * 1e-3, dev)
+
+            # the same K steps once more with an event pair around every op: per-kernel durations
+            # for the roofline and the breakdown (kept out of `value`: at 8 ranks a step is short
+            # enough for the 26 extra event records per step to show)
+            if world > 1:
+                torch.distributed.barrier()
+            for _ in range(args.steps):
+                block(x_dev, timer=timer)
+            torch.cuda.synchronize()
+            if world > 1:
+                torch.distributed.barrier()
 
             # end to end: pinned host input in, output back out, every step
             for _ in range(2):
@@ -441,17 +466,26 @@ def run_ours(args, rank, world, local):
     ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
     peak = peaks["bf16_tflops_sustained"]
     line = base_line(args, world, tokens * args.steps / secs, secs / args.steps * 1e3)
+    m_rank, el = nb * SEQ, 2
+    hid, ffn, kvw = CFG["hidden"], CFG["ffn"], CFG["n_kv_heads"] * CFG["head_dim"]
+    gemm_bytes = el * (m_rank * hid + (hid + 2 * kvw) * hid + m_rank * (hid + 2 * kvw)       # qkv projection
+                       + m_rank * hid + hid * hid + m_rank * hid                              # o projection
+                       + m_rank * hid + 2 * ffn * hid + m_rank * ffn                          # gate-up + SwiGLU
+                       + m_rank * ffn + hid * ffn + 2 * m_rank * hid)                         # down + residual
     line["roofline"] = {"kernel": f"gemm_pair_kernel<bf16> (tcgen05 GEMM, {gemm_calls // args.steps} launches per step: "
-                                  "q/k/v/o projections, gate-up + SwiGLU, down + residual)", "bound": "tensor",
+                                  "qkv and o projections, gate-up + SwiGLU, down + residual)", "bound": "tensor",
                         "achieved": round(ach, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
-                        "traffic": NCU_TRAFFIC_BYTES["gemm"], "peak_source": f"{src} (cuBLAS bf16, sustained)",
+                        "traffic": int(NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * gemm_bytes / 4),
+                        "traffic_note": "bytes per launch (average of the step's 4 GEMM launches), scaled from an ncu "
+                                        "capture of a smaller case by algorithmic bytes",
+                        "peak_source": f"{src} (cuBLAS bf16, sustained)",
                         "flops_per_launch_avg": gemm_flops // gemm_calls,
                         "us_per_launch_avg": round(gemm_ms * 1e3 / gemm_calls, 1), "per_gpu": True}
     line["step_breakdown_ms"] = {k: round(v["ms"] / args.steps, 4) for k, v in sorted(totals.items())}
     line["e2e"] = {"value": tokens * args.steps / e2e_secs, "unit": UNIT,
                    "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": out_host.numel() * 2 * world,
                    "ms_per_step": e2e_secs / args.steps * 1e3,
-                   "api": "LlamaBlock.forward_host(pinned x, pinned out): H2D, 9 library kernels + SDPA per group of sequences, D2H; groups pipelined over 3 streams"}
+                   "api": "LlamaBlock.forward_host(pinned x, pinned out): H2D, 7 library kernels + SDPA per group of sequences, D2H; groups pipelined over 3 streams"}
     line["gpu_launches"] = block.launches_per_forward * args.steps * world
     line["clocks"] = clocks.summary()
     line["parity"] = parity
@@ -459,12 +493,12 @@ def run_ours(args, rank, world, local):
         line["ops"] = bench_ops(dev, rank, world, peaks, src)
     if rank == 0 and world == 1:
         w_cpu = {k: v.cpu() for k, v in weights.items()}
-        tps, dt = cpu_sample_tokens_per_s(w_cpu, 2, 1)
+        tps, dt = cpu_sample_tokens_per_s(w_cpu, 4, 1, batch=BATCH)
         line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                                "sample": f"CPU oracle block on batch 1 x seq {SEQ} (1/8 of a step), 2 timed steps "
+                                "sample": f"CPU oracle block on the full step (batch {BATCH} x seq {SEQ}), 4 timed steps "
                                           f"of {dt:.2f} s after 1 warm-up"}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
 
 
 PROFILE_CASES = ("gemm", "gemm_fp8", "lce", "swiglu", "rmsnorm", "rope", "fp8_token", "fp8_block")

@@ -15,7 +15,8 @@
 //     FMA residual corrections (struct ExactDiv), two elements per packed fp32x2
 //     instruction - 2.5 issue slots per element instead of a full division.  This file must not be compiled with
 //     --use_fast_math.
-//   * The row / tile is held in registers between the amax pass and the cast,
+//   * The row / tile is held in registers (token; small block problems) or in shared
+//     memory filled by one TMA tile load (block) between the amax pass and the cast,
 //     so HBM is read once.  Every load is one 16-byte vector per lane with
 //     consecutive lanes on consecutive vectors (a warp reads 512 contiguous
 //     bytes per instruction); the codes of one vector (8 for 16-bit inputs,
@@ -25,6 +26,8 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "ptx.cuh"
+#include "tma_host.cuh"
 
 namespace cck {
 namespace {
@@ -243,6 +246,56 @@ fp8_block_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, float* __
         if (live[j]) Chunk<T>::template quantise_store<E5M2>(v[j], div, codes + off[j]);
 }
 
+// Same tile, staged by TMA: one thread issues a single 2-D tile load of the whole 128x128 tile
+// (32 KB for 16-bit inputs, 64 KB for fp32) into shared memory, so a 128-thread CTA keeps a
+// full tile in flight and 3-6 CTAs per SM keep 190 KB in flight without spending registers on
+// it; the tile is then read from shared memory twice (amax pass, cast pass) with 16-byte
+// conflict-free accesses.  TMA zero-fills the part of an edge tile that lies outside the
+// matrix, which cannot change a maximum of magnitudes.  The wait is bounded; if it runs out
+// the CTA sets bit 1 of the status word and writes nothing.
+constexpr int kTmaThreads = 128;
+template <typename T, bool E5M2>
+__global__ void __launch_bounds__(kTmaThreads)
+fp8_block_tma_kernel(const __grid_constant__ CUtensorMap map, uint8_t* __restrict__ codes,
+                     float* __restrict__ scale, int64_t m, int64_t n, unsigned int* status) {
+    constexpr int kPer = Store<T>::kPerVec;
+    constexpr int kVecPerRow = kTile / kPer;
+    constexpr int kVecs = kTile * kVecPerRow;               // 2048 or 4096 vectors per tile
+    extern __shared__ __align__(128) uint8_t tile[];
+    __shared__ __align__(8) uint64_t bar_storage;
+    __shared__ float slots[32];
+    __shared__ int abort_flag;
+    const uint32_t bar = ptx::smem_addr(&bar_storage);
+    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * kTile, c0 = static_cast<int64_t>(blockIdx.x) * kTile;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(bar, 1);
+        ptx::fence_barrier_init();
+        ptx::mbar_arrive_expect_tx(bar, kTile * kTile * static_cast<uint32_t>(sizeof(T)));
+        // c0 is a multiple of 128 elements: the copy starts on a 16-byte boundary
+        ptx::tma_load_2d(ptx::smem_addr(tile), &map, bar, static_cast<int32_t>(c0), static_cast<int32_t>(r0));
+    }
+    __syncthreads();
+    const bool ok = ptx::mbar_wait(bar, 0, &abort_flag);
+    if (!__syncthreads_and(ok)) {
+        if (threadIdx.x == 0) atomicOr(status, 2u);
+        return;
+    }
+    const Vec16* t16 = reinterpret_cast<const Vec16*>(tile);
+    float mx = 0.0f;
+#pragma unroll 4
+    for (int id = threadIdx.x; id < kVecs; id += kTmaThreads) mx = fmaxf(mx, Chunk<T>::amax(t16[id]));
+    const float sc = scale_of<E5M2>(cta_max_dyn(mx, slots));
+    if (threadIdx.x == 0) scale[static_cast<int64_t>(blockIdx.y) * gridDim.x + blockIdx.x] = sc;
+    const ExactDiv div = ExactDiv::make(sc);
+    const bool interior = r0 + kTile <= m && c0 + kTile <= n;
+#pragma unroll 2
+    for (int id = threadIdx.x; id < kVecs; id += kTmaThreads) {
+        const int64_t r = r0 + id / kVecPerRow, c = c0 + (id % kVecPerRow) * kPer;
+        if (interior || (r < m && c < n)) Chunk<T>::template quantise_store<E5M2>(t16[id], div, codes + r * n + c);
+    }
+}
+
 template <typename T, bool E5M2>
 __global__ void __launch_bounds__(256)
 fp8_block_generic_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, float* __restrict__ scale,
@@ -349,7 +402,37 @@ cudaError_t run_block(const void* x, uint8_t* codes, float* scale, int64_t m, in
     if (gy > 65535 || gx > 0x7fffffffLL) return cudaErrorInvalidValue;
     const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
     const T* xp = static_cast<const T*>(x);
-    if (n % Store<T>::kPerVec == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(codes) % 8) == 0)
+    const bool vec_ok = n % Store<T>::kPerVec == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(codes) % 8) == 0;
+    // TMA needs 16-byte aligned rows; tiny matrices are not worth a tensor map
+    if (vec_ok && (n * sizeof(T)) % 16 == 0 && m * n >= (1 << 16) && m < (1LL << 31) && n < (1LL << 31) &&
+        tc::encode_fn() != nullptr) {
+        constexpr bool is32 = sizeof(T) == 4;
+        const CUtensorMapDataType dt = is32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                            : (std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                              : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+        CUtensorMap map;
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(n) * sizeof(T)};
+        const cuuint32_t box[2] = {kTile, kTile};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult r = tc::encode_fn()(&map, dt, 2, const_cast<T*>(xp), dims, strides, box, estr,
+                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        unsigned int* st = tc::status_word();
+        if (r == CUDA_SUCCESS && st != nullptr) {
+            constexpr int kSmem = kTile * kTile * static_cast<int>(sizeof(T));
+            auto kern = fp8_block_tma_kernel<T, E5M2>;
+            static bool configured = false;
+            if (!configured) {
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+                if (e != cudaSuccess) return e;
+                configured = true;
+            }
+            kern<<<grid, kTmaThreads, kSmem, s>>>(map, codes, scale, m, n, st);
+            return cudaGetLastError();
+        }
+    }
+    if (vec_ok)
         fp8_block_kernel<T, E5M2><<<grid, kBlockThreads, 0, s>>>(xp, codes, scale, m, n);
     else
         fp8_block_generic_kernel<T, E5M2><<<grid, 256, 0, s>>>(xp, codes, scale, m, n);

@@ -25,6 +25,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tma_host.cuh"
 
 namespace cck {
 namespace tc {
@@ -438,22 +439,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-inline EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
 // Row-major [rows, cols] matrix of `elem_bytes`-wide elements; box = 128 bytes x box_rows, 128-byte swizzle.
 inline cudaError_t make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr,
                              int64_t rows, int64_t cols, int box_rows) {
@@ -487,9 +472,6 @@ inline int sm_count() {
     }();
     return n;
 }
-
-// Device word that collects wait time-outs of the tensor-core kernels (bit 0).
-unsigned int* status_word();
 
 template <bool kFp8, class Sched, class Epi>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const typename Sched::Params& sp,

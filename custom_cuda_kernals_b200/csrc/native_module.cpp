@@ -193,6 +193,50 @@ void rope_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& cos, c
                                  k_out.data_ptr(), batch, seq, hq, k.size(2), d, dt, l.stream));
 }
 
+// rope on strided q/k views (no counterpart in the reference): q [B,S,Hq,D] and k [B,S,Hkv,D] may be
+// views whose tokens are a fixed number of elements apart (heads of a token contiguous)
+int64_t token_stride_of(const char* name, const at::Tensor& t) {
+    if (!t.is_cuda())
+        value_error(std::string("argument '") + name + "' must be a CUDA tensor, got device type '" +
+                    c10::DeviceTypeName(t.device().type(), true) + "'");
+    if (t.dim() != 4) value_error(std::string("shape mismatch: ") + name + " must be 4-D [batch, seq_len, heads, head_dim], got " + shape_str(t));
+    const int64_t s = t.size(1), h = t.size(2), d = t.size(3);
+    const int64_t ts = t.stride(1);
+    const bool ok = t.stride(3) == 1 && (h == 1 || t.stride(2) == d) && (t.size(0) == 1 || t.stride(0) == s * ts) && ts >= h * d;
+    if (!ok) value_error(std::string("argument '") + name + "' must have contiguous heads per token and evenly spaced tokens");
+    return ts;
+}
+
+void rope_strided_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& cos, const at::Tensor& sin,
+                      const at::Tensor& q_out, const at::Tensor& k_out) {
+    const int64_t qs = token_stride_of("q", q), ks = token_stride_of("k", k);
+    int32_t dt;
+    switch (q.scalar_type()) {
+        case at::kFloat: dt = CCK_F32; break;
+        case at::kHalf: dt = CCK_F16; break;
+        case at::kBFloat16: dt = CCK_BF16; break;
+        default: value_error(std::string("unsupported dtype '") + c10::toString(q.scalar_type()) + "'; expected float32, float16, or bfloat16");
+    }
+    if (k.scalar_type() != q.scalar_type()) value_error("dtype mismatch: 'k' must match 'q'");
+    expect_same_dtype("q_out", tag_of("q_out", q_out), dt);
+    expect_same_dtype("k_out", tag_of("k_out", k_out), dt);
+    expect_f32("cos", tag_of("cos", cos), " (RoPE tables are always fp32)");
+    expect_f32("sin", tag_of("sin", sin), " (RoPE tables are always fp32)");
+    if (q_out.sizes() != q.sizes()) value_error("shape mismatch: q_out must match q's shape");
+    if (k_out.sizes() != k.sizes()) value_error("shape mismatch: k_out must match k's shape");
+    const int64_t batch = q.size(0), seq = q.size(1), hq = q.size(2), d = q.size(3);
+    if (k.size(0) != batch || k.size(1) != seq || k.size(3) != d)
+        value_error("shape mismatch: q and k must share batch/seq_len/head_dim; got q=" + shape_str(q) + ", k=" + shape_str(k));
+    if (d % 2 != 0) value_error("shape mismatch: head_dim must be even, got " + std::to_string(d));
+    if (cos.dim() != 2 || sin.dim() != 2 || cos.size(0) != seq || cos.size(1) != d / 2 || sin.size(0) != seq ||
+        sin.size(1) != d / 2)
+        value_error("shape mismatch: cos/sin must have shape [" + std::to_string(seq) + ", " + std::to_string(d / 2) + "]");
+    Launch l(q, {&k, &cos, &sin, &q_out, &k_out});
+    check_launch("launch_rope_strided_fwd",
+                 launch_rope_strided_fwd(q.data_ptr(), k.data_ptr(), cos.data_ptr(), sin.data_ptr(), q_out.data_ptr(),
+                                         k_out.data_ptr(), batch, seq, hq, k.size(2), d, qs, ks, dt, l.stream));
+}
+
 // ------------------------------------------------------------------ src/kernels/fp8_quant.rs:62-210 (+ token)
 struct Fp8Args {
     int32_t dt, fmt;
@@ -494,6 +538,8 @@ PYBIND11_MODULE(_native, m) {
           py::arg("fp8_format"));
     m.def("matmul_add_bias_fp8_fwd", &matmul_add_bias_fp8_fwd, py::arg("a_fp8"), py::arg("a_scale"), py::arg("w_fp8"),
           py::arg("w_scale"), py::arg("bias").none(true), py::arg("y"));
+    m.def("rope_strided_fwd", &rope_strided_fwd, py::arg("q"), py::arg("k"), py::arg("cos"), py::arg("sin"),
+          py::arg("q_out"), py::arg("k_out"));
     m.def("matmul_swiglu_fwd", &matmul_swiglu_fwd, py::arg("x"), py::arg("w_gate_up"), py::arg("y"));
     m.def("matmul_add_bias_residual_fwd", &matmul_add_bias_residual_fwd, py::arg("x"), py::arg("weight"),
           py::arg("bias").none(true), py::arg("residual"), py::arg("y"));

@@ -38,7 +38,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 rope_kernel(const T* __restrict__ q, const T* __restrict__ k, const float* __restrict__ cos_t,
             const float* __restrict__ sin_t, T* __restrict__ q_out, T* __restrict__ k_out,
-            int batch, int seq_len, int hq, int hkv, int head_dim) {
+            int batch, int seq_len, int hq, int hkv, int head_dim, int64_t q_tok_stride, int64_t k_tok_stride) {
     constexpr int kPer = Store<T>::kPerVec;
     const int half = head_dim >> 1;
     const int hv = half / kPer;                 // 16-byte vectors per half row
@@ -69,15 +69,18 @@ rope_kernel(const T* __restrict__ q, const T* __restrict__ k, const float* __res
         const int heads = is_q ? hq : hkv;
         const int hh = is_q ? h : h - hq;
 
+        const int64_t in_stride = is_q ? q_tok_stride : k_tok_stride;   // elements between tokens of the input
         Vec16 lo[kBatchPerCta], hi[kBatchPerCta];
         int64_t off[kBatchPerCta];
 #pragma unroll
         for (int bb = 0; bb < kBatchPerCta; ++bb) {
             const int b = b0 + bb;
-            off[bb] = ((static_cast<int64_t>(b) * seq_len + s_idx) * heads + hh) * head_dim + j * kPer;
+            const int64_t tok = static_cast<int64_t>(b) * seq_len + s_idx;
+            off[bb] = (tok * heads + hh) * head_dim + j * kPer;           // outputs are contiguous
             if (b < batch) {
-                lo[bb] = ld_stream(src + off[bb]);
-                hi[bb] = ld_stream(src + off[bb] + half);
+                const int64_t in = tok * in_stride + hh * head_dim + j * kPer;
+                lo[bb] = ld_stream(src + in);
+                hi[bb] = ld_stream(src + in + half);
             }
         }
 #pragma unroll
@@ -92,7 +95,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 rope_scalar_kernel(const T* __restrict__ q, const T* __restrict__ k, const float* __restrict__ cos_t,
                    const float* __restrict__ sin_t, T* __restrict__ q_out, T* __restrict__ k_out,
-                   int64_t tokens, int seq_len, int hq, int hkv, int head_dim) {
+                   int64_t tokens, int seq_len, int hq, int hkv, int head_dim, int64_t q_tok_stride,
+                   int64_t k_tok_stride) {
     const int half = head_dim >> 1;
     const int64_t per_token = static_cast<int64_t>(hq + hkv) * half;
     const int64_t total = tokens * per_token;
@@ -107,8 +111,10 @@ rope_scalar_kernel(const T* __restrict__ q, const T* __restrict__ k, const float
         const bool is_q = h < hq;
         const T* src = is_q ? q : k;
         T* dst = is_q ? q_out : k_out;
-        const int64_t o = (tok * (is_q ? hq : hkv) + (is_q ? h : h - hq)) * head_dim + i;
-        const float a = Store<T>::load1(src + o), b = Store<T>::load1(src + o + half);
+        const int hh = is_q ? h : h - hq;
+        const int64_t o = (tok * (is_q ? hq : hkv) + hh) * head_dim + i;
+        const int64_t in = tok * (is_q ? q_tok_stride : k_tok_stride) + static_cast<int64_t>(hh) * head_dim + i;
+        const float a = Store<T>::load1(src + in), b = Store<T>::load1(src + in + half);
         Store<T>::store1(dst + o, a * c - b * sn);
         Store<T>::store1(dst + o + half, b * c + a * sn);
     }
@@ -116,10 +122,11 @@ rope_scalar_kernel(const T* __restrict__ q, const T* __restrict__ k, const float
 
 template <typename T>
 cudaError_t run(const void* q, const void* k, const void* cos_t, const void* sin_t, void* q_out, void* k_out,
-                int64_t batch, int64_t seq_len, int64_t hq, int64_t hkv, int64_t head_dim, cudaStream_t stream) {
+                int64_t batch, int64_t seq_len, int64_t hq, int64_t hkv, int64_t head_dim, int64_t q_tok_stride,
+                int64_t k_tok_stride, cudaStream_t stream) {
     constexpr int kPer = Store<T>::kPerVec;
     const int64_t half = head_dim / 2;
-    const bool vec_ok = (half % kPer == 0) && aligned16(q) && aligned16(k) && aligned16(cos_t) &&
+    const bool vec_ok = (half % kPer == 0) && q_tok_stride % kPer == 0 && k_tok_stride % kPer == 0 && aligned16(q) && aligned16(k) && aligned16(cos_t) &&
                         aligned16(sin_t) && aligned16(q_out) && aligned16(k_out) &&
                         seq_len <= 0x7fffffffLL && ceil_div64(batch, kBatchPerCta) <= 65535;
     const float* cp = static_cast<const float*>(cos_t);
@@ -132,7 +139,7 @@ cudaError_t run(const void* q, const void* k, const void* cos_t, const void* sin
         rope_kernel<T><<<grid, threads, 0, stream>>>(
             static_cast<const T*>(q), static_cast<const T*>(k), cp, sp, static_cast<T*>(q_out),
             static_cast<T*>(k_out), static_cast<int>(batch), static_cast<int>(seq_len),
-            static_cast<int>(hq), static_cast<int>(hkv), static_cast<int>(head_dim));
+            static_cast<int>(hq), static_cast<int>(hkv), static_cast<int>(head_dim), q_tok_stride, k_tok_stride);
     } else {
         const int64_t total = batch * seq_len * (hq + hkv) * half;
         int64_t ctas = ceil_div64(total, 256);
@@ -141,7 +148,7 @@ cudaError_t run(const void* q, const void* k, const void* cos_t, const void* sin
         rope_scalar_kernel<T><<<static_cast<unsigned>(ctas), 256, 0, stream>>>(
             static_cast<const T*>(q), static_cast<const T*>(k), cp, sp, static_cast<T*>(q_out),
             static_cast<T*>(k_out), batch * seq_len, static_cast<int>(seq_len), static_cast<int>(hq),
-            static_cast<int>(hkv), static_cast<int>(head_dim));
+            static_cast<int>(hkv), static_cast<int>(head_dim), q_tok_stride, k_tok_stride);
     }
     return cudaGetLastError();
 }
@@ -149,24 +156,46 @@ cudaError_t run(const void* q, const void* k, const void* cos_t, const void* sin
 }  // namespace
 }  // namespace cck
 
+namespace {
+int32_t rope_dispatch(const void* q, const void* k, const void* cos_table, const void* sin_table, void* q_out,
+                      void* k_out, int64_t batch, int64_t seq_len, int64_t n_q_heads, int64_t n_kv_heads,
+                      int64_t head_dim, int64_t q_tok_stride, int64_t k_tok_stride, int32_t dtype, void* stream) {
+    if (batch <= 0 || seq_len <= 0 || head_dim <= 0 || (n_q_heads + n_kv_heads) <= 0) return cudaSuccess;
+    if (head_dim & 1) return cudaErrorInvalidValue;
+    if (q_tok_stride < n_q_heads * head_dim || k_tok_stride < n_kv_heads * head_dim) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case cck::kF32:
+            return cck::run<float>(q, k, cos_table, sin_table, q_out, k_out, batch, seq_len, n_q_heads, n_kv_heads,
+                                   head_dim, q_tok_stride, k_tok_stride, s);
+        case cck::kF16:
+            return cck::run<__half>(q, k, cos_table, sin_table, q_out, k_out, batch, seq_len, n_q_heads, n_kv_heads,
+                                    head_dim, q_tok_stride, k_tok_stride, s);
+        case cck::kBF16:
+            return cck::run<__nv_bfloat16>(q, k, cos_table, sin_table, q_out, k_out, batch, seq_len, n_q_heads,
+                                           n_kv_heads, head_dim, q_tok_stride, k_tok_stride, s);
+        default:
+            return cudaErrorInvalidValue;
+    }
+}
+}  // namespace
+
 extern "C" int32_t launch_rope_fwd(const void* q, const void* k, const void* cos_table, const void* sin_table,
                                    void* q_out, void* k_out, int64_t batch, int64_t seq_len,
                                    int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim, int32_t dtype,
                                    void* stream) {
-    if (batch <= 0 || seq_len <= 0 || head_dim <= 0 || (n_q_heads + n_kv_heads) <= 0) return cudaSuccess;
-    if (head_dim & 1) return cudaErrorInvalidValue;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    switch (dtype) {
-        case cck::kF32:
-            return cck::run<float>(q, k, cos_table, sin_table, q_out, k_out, batch, seq_len, n_q_heads,
-                                   n_kv_heads, head_dim, s);
-        case cck::kF16:
-            return cck::run<__half>(q, k, cos_table, sin_table, q_out, k_out, batch, seq_len, n_q_heads,
-                                    n_kv_heads, head_dim, s);
-        case cck::kBF16:
-            return cck::run<__nv_bfloat16>(q, k, cos_table, sin_table, q_out, k_out, batch, seq_len,
-                                           n_q_heads, n_kv_heads, head_dim, s);
-        default:
-            return cudaErrorInvalidValue;
-    }
+    return rope_dispatch(q, k, cos_table, sin_table, q_out, k_out, batch, seq_len, n_q_heads, n_kv_heads, head_dim,
+                         n_q_heads * head_dim, n_kv_heads * head_dim, dtype, stream);
+}
+
+// Same rotation for inputs whose tokens are not packed: consecutive tokens of q (of k) are
+// q_token_stride (k_token_stride) elements apart, e.g. q and k are column ranges of one fused
+// QKV projection output.  Within a token the heads are contiguous; the outputs are contiguous.
+extern "C" int32_t launch_rope_strided_fwd(const void* q, const void* k, const void* cos_table,
+                                           const void* sin_table, void* q_out, void* k_out, int64_t batch,
+                                           int64_t seq_len, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
+                                           int64_t q_token_stride, int64_t k_token_stride, int32_t dtype,
+                                           void* stream) {
+    return rope_dispatch(q, k, cos_table, sin_table, q_out, k_out, batch, seq_len, n_q_heads, n_kv_heads, head_dim,
+                         q_token_stride, k_token_stride, dtype, stream);
 }

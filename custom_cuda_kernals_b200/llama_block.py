@@ -11,7 +11,8 @@ The reference swaps in its three bandwidth-bound kernels and leaves every
 projection to ``nn.Linear`` (cuBLAS); here the seven projections also run on this
 library's tcgen05 GEMM (``matmul_add_bias`` with no bias), and by default two of
 them carry the neighbouring elementwise op in their epilogue - gate/up + SwiGLU in
-one GEMM, down_proj + the final residual add in another - with results identical to
+one GEMM, down_proj + the final residual add in another - and q, k, v come from one
+projection whose q / k column ranges RoPE reads in place; results are identical to
 the unfused chain (``fused=False`` runs that chain).  The attention core stays
 ``torch.nn.functional.scaled_dot_product_attention`` as in the reference.
 Forward only, no autograd.
@@ -27,7 +28,7 @@ import torch.nn.functional as F
 from .kernels.fused import GATE_UP_BLOCK, interleave_gate_up, matmul_add_bias_residual, matmul_swiglu
 from .kernels.matmul_add_bias import matmul_add_bias
 from .kernels.rmsnorm_residual import rmsnorm_residual
-from .kernels.rope import rope
+from .kernels.rope import rope, rope_strided
 from .kernels.swiglu import swiglu
 
 __all__ = ["LlamaBlock", "rope_tables", "OpTimer", "PARAM_NAMES"]
@@ -95,18 +96,23 @@ class LlamaBlock:
         self.n_heads, self.n_kv_heads = n_heads, n_kv_heads
         self.head_dim = self.w["q_proj"].shape[0] // n_heads
         self.eps = eps
-        dev = self.w["q_proj"].device
+        dev = self.device = self.w["q_proj"].device
         self.cos, self.sin = rope_tables(max_seq_len, self.head_dim, theta, dev)
         ffn, dt = self.w["gate_proj"].shape[0], self.w["gate_proj"].dtype
         self.fused = bool(fused and ffn % GATE_UP_BLOCK == 0 and self.hidden % 8 == 0 and ffn % 8 == 0
                           and dt in (torch.float16, torch.bfloat16))
-        if self.fused:      # one-time re-layout; the separate gate/up weights are not kept
+        if self.fused:      # one-time re-layout; the separate q/k/v and gate/up weights are not kept
             self.w_gate_up = interleave_gate_up(self.w["gate_proj"], self.w["up_proj"])
+            self.w_qkv = torch.cat([self.w["q_proj"], self.w["k_proj"], self.w["v_proj"]], dim=0).contiguous()
+            self.q_cols = self.w["q_proj"].shape[0]
+            self.kv_cols = self.w["k_proj"].shape[0]
             self.ffn = ffn
-            del self.w["gate_proj"], self.w["up_proj"]
-        #: kernels of this library launched per forward call: 2 norms, rope, q/k/v/o GEMMs and
-        #: either gate + up + swiglu + down (unfused) or gate-up-swiglu + down-residual (fused)
-        self.launches_per_forward = 9 if self.fused else 11
+            for name in ("gate_proj", "up_proj", "q_proj", "k_proj", "v_proj"):
+                del self.w[name]
+        #: kernels of this library launched per forward call: 2 norms, rope, and either
+        #: q + k + v + o + gate + up + swiglu + down (unfused: 11 in all) or
+        #: qkv + o + gate-up-swiglu + down-residual (fused: 7 in all)
+        self.launches_per_forward = 7 if self.fused else 11
 
     def forward(self, x: torch.Tensor, timer: OpTimer | None = None, pos_offset: int = 0) -> torch.Tensor:
         """x ``[B, S, hidden]`` -> ``[B, S, hidden]``.  ``pos_offset`` is the position of
@@ -122,10 +128,19 @@ class LlamaBlock:
         x2 = x.view(b * s, hid)
         zero = t.run("fill", torch.zeros_like, x2)
         h, res = t.run("rmsnorm", rmsnorm_residual, x2, zero, w["input_layernorm_weight"], self.eps)
-        q = t.run("gemm", matmul_add_bias, h, w["q_proj"]).view(b, s, self.n_heads, self.head_dim)
-        k = t.run("gemm", matmul_add_bias, h, w["k_proj"]).view(b, s, self.n_kv_heads, self.head_dim)
-        v = t.run("gemm", matmul_add_bias, h, w["v_proj"]).view(b, s, self.n_kv_heads, self.head_dim)
-        q, k = t.run("rope", rope, q, k, self.cos[pos_offset:pos_offset + s], self.sin[pos_offset:pos_offset + s])
+        cos, sin = self.cos[pos_offset:pos_offset + s], self.sin[pos_offset:pos_offset + s]
+        if self.fused:       # one projection for q, k and v; rope reads its q / k column ranges in place
+            qkv = t.run("gemm", matmul_add_bias, h, self.w_qkv).view(b, s, -1)
+            qc, kc = self.q_cols, self.kv_cols
+            q = qkv[..., :qc].unflatten(-1, (self.n_heads, self.head_dim))
+            k = qkv[..., qc:qc + kc].unflatten(-1, (self.n_kv_heads, self.head_dim))
+            v = qkv[..., qc + kc:].unflatten(-1, (self.n_kv_heads, self.head_dim))
+            q, k = t.run("rope", rope_strided, q, k, cos, sin)
+        else:
+            q = t.run("gemm", matmul_add_bias, h, w["q_proj"]).view(b, s, self.n_heads, self.head_dim)
+            k = t.run("gemm", matmul_add_bias, h, w["k_proj"]).view(b, s, self.n_kv_heads, self.head_dim)
+            v = t.run("gemm", matmul_add_bias, h, w["v_proj"]).view(b, s, self.n_kv_heads, self.head_dim)
+            q, k = t.run("rope", rope, q, k, cos, sin)
         att = t.run("sdpa", F.scaled_dot_product_attention, q.transpose(1, 2), k.transpose(1, 2),
                     v.transpose(1, 2), is_causal=True, enable_gqa=self.n_heads != self.n_kv_heads)
         att = t.run("copy", lambda a: a.transpose(1, 2).contiguous().view(b * s, hid), att)
@@ -150,7 +165,7 @@ class LlamaBlock:
         (default: up to 4) that flow through three streams - copy-in, compute (the current
         stream) and copy-out - so the PCIe transfers of one group overlap the kernels of
         another.  Returns ``out_host`` once every group has landed in it."""
-        dev = self.w["q_proj"].device
+        dev = self.device
         b = x_host.shape[0]
         n = max(1, min(b, chunks if chunks is not None else 4))
         if not hasattr(self, "_copy_in"):
@@ -180,6 +195,7 @@ class LlamaBlock:
 
     def gemm_flops(self, tokens: int) -> int:
         """2*M*K*N summed over the seven projections for ``tokens`` rows."""
-        shapes = [self.w[n].shape for n in ("q_proj", "k_proj", "v_proj", "o_proj", "down_proj")]
-        shapes += [self.w_gate_up.shape] if self.fused else [self.w["gate_proj"].shape, self.w["up_proj"].shape]
+        shapes = [self.w[n].shape for n in ("o_proj", "down_proj")]
+        shapes += ([self.w_gate_up.shape, self.w_qkv.shape] if self.fused else
+                   [self.w[n].shape for n in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj")])
         return sum(2 * tokens * o * i for o, i in shapes)

@@ -118,6 +118,15 @@ int64_t cck_lce_noalloc_max_workspace_bytes(void);
 int32_t launch_lce_finalize(const float* stats, const int64_t* targets, int64_t n, int64_t n_shards,
                             int64_t ignore_index, float* loss_rows, float* reduce_out, void* stream);
 
+/* launch_rope_fwd for inputs whose tokens are not packed: consecutive tokens of q (k) are
+ * q_token_stride (k_token_stride) elements apart - e.g. q and k are column ranges of one fused
+ * QKV projection output [tokens, (Hq + 2 Hkv) * D].  Heads of one token are contiguous; q_out and
+ * k_out are contiguous [batch, seq_len, heads, head_dim]. */
+int32_t launch_rope_strided_fwd(const void* q, const void* k, const void* cos_table, const void* sin_table,
+                                void* q_out, void* k_out, int64_t batch, int64_t seq_len, int64_t n_q_heads,
+                                int64_t n_kv_heads, int64_t head_dim, int64_t q_token_stride,
+                                int64_t k_token_stride, int32_t dtype, void* stream);
+
 /* Fused gate/up projection + SwiGLU: y[m, f] = silu(x @ Wg^T) * (x @ Wu^T).  w_gate_up is
  * [2f, k]: for every block j of 128 output features, rows [256j, 256j+128) hold rows
  * [128j, 128j+128) of Wg and rows [256j+128, 256j+256) the same rows of Wu.  Rounds where the

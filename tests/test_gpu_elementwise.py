@@ -151,3 +151,25 @@ def test_rope_config2b_full_size_and_position_slices():
     s0, s1 = 512, 1024
     q_part, k_part = rope(qd[:, s0:s1].contiguous(), kd[:, s0:s1].contiguous(), cd[s0:s1], sd[s0:s1])
     assert torch.equal(q_part, q_out[:, s0:s1]) and torch.equal(k_part, k_out[:, s0:s1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dims", [(2, 33, 8, 2, 64), (1, 128, 32, 8, 128), (3, 5, 3, 1, 6)])
+def test_rope_strided_views_equal_packed_inputs(dims, dtype):
+    """q and k as column ranges of one fused QKV buffer [tokens, (Hq + 2 Hkv) * D] give exactly
+    what packed copies give (vector path and, for head_dim 6, the scalar path)."""
+    from custom_cuda.kernels.rope import rope, rope_strided
+    b, s, hq, hkv, d = dims
+    g = torch.Generator().manual_seed(sum(dims))
+    qkv = torch.randn(b, s, (hq + 2 * hkv) * d, generator=g).to(dtype).to(DEV)
+    q = qkv[..., :hq * d].unflatten(-1, (hq, d))
+    k = qkv[..., hq * d:(hq + hkv) * d].unflatten(-1, (hkv, d))
+    cos, sin = (t.to(DEV) for t in ops.rope_tables(s, d, 500000.0))
+    q1, k1 = rope_strided(q, k, cos, sin)
+    q2, k2 = rope(q.contiguous(), k.contiguous(), cos, sin)
+    assert q1.is_contiguous() and torch.equal(q1, q2) and torch.equal(k1, k2)
+    q_ref, k_ref = ops.rope(q.cpu().contiguous(), k.cpu().contiguous(), cos.cpu(), sin.cpu())
+    check(q1, q_ref, dtype)
+    check(k1, k_ref, dtype)
+    with pytest.raises(ValueError):
+        rope_strided(q.transpose(1, 2), k.transpose(1, 2), cos, sin)     # heads no longer contiguous per token
