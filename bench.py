@@ -181,6 +181,27 @@ def timed_loop(fn, arg_sets, iters, warm=3, graph=False):
     return a.elapsed_time(b) * 1e-3 / iters
 
 
+def wrapper_call_stats(fn, arg_sets, flush, iters=100):
+    """The reference's own harness (benchmarks/rmsnorm_residual_bench.py:124-153): flush the L2,
+    synchronise, then time ONE call of the Python wrapper with CUDA events - host overhead of the
+    call included.  Returns median and inter-quartile range in microseconds."""
+    times = []
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(iters):
+        flush.fill_(1.0)
+        torch.cuda.synchronize()
+        a.record()
+        fn(*arg_sets[i % len(arg_sets)])
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    times.sort()
+    return {"median_us": round(statistics.median(times), 2),
+            "iqr_us": round(times[int(0.75 * iters)] - times[int(0.25 * iters)], 2),
+            "method": "reference harness: 512 MB L2 flush + synchronize before each of 100 single calls, "
+                      "CUDA events around the Python wrapper call"}
+
+
 def bench_ops(dev, rank, world, peaks, src):
     """Each fused op alone at the configuration sizes, sharded over the ranks; inputs rotate
     through sets whose total size exceeds the 126 MB L2."""
@@ -210,6 +231,11 @@ def bench_ops(dev, rank, world, peaks, src):
                      "peak_source": src, "shard": note}
 
     cpu_on = world == 1 and rank == 0
+    flush = torch.empty(128 << 20, dtype=torch.float32, device=dev) if world == 1 else None   # 512 MB
+
+    def wrapper(name, fn, arg_sets):
+        if flush is not None:
+            out[name]["wrapper_call"] = wrapper_call_stats(fn, arg_sets, flush)
 
     def cpu(name, work, fn, sample):
         """The oracle's CPU op chain on a bounded sample of the same inputs (all host cores)."""
@@ -236,6 +262,7 @@ def bench_ops(dev, rank, world, peaks, src):
              1 + 0.1 * rn(4096, dtype=torch.float32), 1e-5) for _ in range(max(6, 6 * world))]
     record("rmsnorm_residual_fp32", "hbm", rows * 4096 * 4 * 4, timed_loop(rmsnorm_residual, sets, 120, graph=True),
            f"rows {rows} of 2048")
+    wrapper("rmsnorm_residual_fp32", rmsnorm_residual, sets)
     if cpu_on:
         cx, cr, cw = (t.cpu() for t in sets[0][:3])
         cpu("rmsnorm_residual_fp32", rows * 4096 * 16, lambda: O.rmsnorm_residual(cx, cr, cw, 1e-5), "all 2048 rows")
@@ -245,6 +272,7 @@ def bench_ops(dev, rank, world, peaks, src):
     rows = r1 - r0
     sets = [(rn(rows, 14336), rn(rows, 14336)) for _ in range(2 if world == 1 else 3)]
     record("swiglu_bf16", "hbm", rows * 14336 * 2 * 3, timed_loop(swiglu, sets, 30, graph=True), f"rows {rows} of 8192")
+    wrapper("swiglu_bf16", swiglu, sets)
     if cpu_on:
         cg, cu = sets[0][0][:2048].cpu(), sets[0][1][:2048].cpu()
         cpu("swiglu_bf16", 2048 * 14336 * 6, lambda: O.swiglu(cg, cu), "2048 of 8192 rows")
@@ -262,6 +290,7 @@ def bench_ops(dev, rank, world, peaks, src):
     sets = [(rn(b, s1 - s0, 32, 128), rn(b, s1 - s0, 8, 128), cos, sin) for _ in range(6)]
     record("rope_bf16", "hbm", b * (s1 - s0) * 40 * 128 * 2 * 2, timed_loop(rope, sets, 120, graph=True),
            f"batch {b} x positions {s0}..{s1}")
+    wrapper("rope_bf16", rope, sets)
     if cpu_on:
         cq, ck, cc, cs = (t.cpu() for t in sets[0])
         cpu("rope_bf16", b * (s1 - s0) * 40 * 128 * 4, lambda: O.rope(cq, ck, cc, cs), "all of config 2b")
@@ -277,6 +306,8 @@ def bench_ops(dev, rank, world, peaks, src):
     record("fp8_quant_token_bf16", "hbm", rows * 4096 * 3, timed_loop(fp8_quant, sets, 120, graph=True), f"rows {rows} of 8192")
     record("fp8_quant_block_bf16", "hbm", rows * 4096 * 3,
            timed_loop(fp8_quant, [(s[0], "e4m3", "block") for s in sets], 120, graph=True), f"rows {rows} of 8192")
+    wrapper("fp8_quant_token_bf16", fp8_quant, sets)
+    wrapper("fp8_quant_block_bf16", fp8_quant, [(s[0], "e4m3", "block") for s in sets])
     if cpu_on:
         cx8 = sets[0][0].cpu()
         cpu("fp8_quant_token_bf16", rows * 4096 * 3, lambda: O.fp8_quant(cx8, "e4m3", "token"), "all 8192 rows")

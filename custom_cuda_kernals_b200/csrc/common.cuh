@@ -53,7 +53,6 @@ template <typename T> struct Store;
 template <> struct Store<float> {
     static constexpr int kPerVec = 4;
     __device__ static __forceinline__ float get(const Vec16& v, int i) { return __uint_as_float(v.w[i]); }
-    __device__ static __forceinline__ void put(Vec16& v, int i, float f) { v.w[i] = __float_as_uint(f); }
     __device__ static __forceinline__ float load1(const float* p) { return *p; }
     __device__ static __forceinline__ void store1(float* p, float f) { *p = f; }
     // value after one rounding to the storage type
@@ -66,7 +65,6 @@ template <> struct Store<__nv_bfloat16> {
         const uint32_t w = v.w[i >> 1];
         return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
     }
-    // put() is only used through put2 below
     __device__ static __forceinline__ float load1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
     __device__ static __forceinline__ void store1(__nv_bfloat16* p, float f) { *p = __float2bfloat16_rn(f); }
     __device__ static __forceinline__ float round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }

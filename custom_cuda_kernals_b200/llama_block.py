@@ -115,10 +115,9 @@ class LlamaBlock:
         self.launches_per_forward = 7 if self.fused else 11
 
     def forward(self, x: torch.Tensor, timer: OpTimer | None = None, pos_offset: int = 0) -> torch.Tensor:
-        """x ``[B, S, hidden]`` -> ``[B, S, hidden]``.  ``pos_offset`` is the position of
-        ``x[:, 0]`` when the caller holds only a slice of each sequence's prefix-free chunk
-        (only meaningful for a single chunk starting at that offset: attention is causal
-        within the chunk)."""
+        """x ``[B, S, hidden]`` -> ``[B, S, hidden]``.  ``pos_offset`` shifts the RoPE positions:
+        ``x[:, i]`` is rotated as position ``pos_offset + i`` (attention stays causal within
+        the ``S`` tokens given)."""
         t = timer if timer is not None else _NoTimer
         w = self.w
         b, s, hid = x.shape

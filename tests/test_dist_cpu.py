@@ -78,6 +78,28 @@ def test_vocab_parallel_exchange_two_gloo_ranks(tmp_path):
     assert outs[0]["range"][1] == outs[1]["range"][0]
 
 
+def _rank_that_loses_its_peer(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_from_env(timeout_s=10)
+    if rank == 1:
+        return                      # leaves between steps, with no collective in flight, and never joins the next one
+    outcome = "completed"
+    try:
+        dist.gather_row_stats(torch.zeros(3, 16))
+    except Exception as e:          # the survivor must get an error, not hang
+        outcome = type(e).__name__
+    with open(os.path.join(out_dir, "r0.txt"), "w") as f:
+        f.write(outcome)
+
+
+def test_a_rank_that_never_joins_surfaces_as_an_error_on_the_survivor(tmp_path):
+    """Failure detection on the host: rank 1 exits before the statistics exchange; rank 0's
+    all-gather ends with an exception within the process-group timeout instead of waiting forever."""
+    mp.spawn(_rank_that_loses_its_peer, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "r0.txt").read_text() != "completed"
+
+
 def test_single_process_needs_no_group():
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
         os.environ.pop(k, None)
