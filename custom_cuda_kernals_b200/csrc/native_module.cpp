@@ -145,6 +145,25 @@ void rmsnorm_residual_fwd(const at::Tensor& x, const at::Tensor& residual, const
                                              l.stream));
 }
 
+// the norm alone (no counterpart in the reference)
+void rmsnorm_fwd(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& y, double eps) {
+    const int32_t dt = tag_of("x", x);
+    expect_float_input("x", dt);
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_same_dtype("y", tag_of("y", y), dt);
+    if (y.sizes() != x.sizes())
+        value_error("shape mismatch: x and y must share the same shape; got x=" + shape_str(x) + ", y=" + shape_str(y));
+    if (x.dim() < 1) value_error("shape mismatch: x must have at least 1 dimension");
+    const int64_t cols = x.size(-1);
+    if (weight.dim() != 1 || weight.size(0) != cols)
+        value_error("shape mismatch: weight shape " + shape_str(weight) + " must be [" + std::to_string(cols) +
+                    "] (x's last dimension)");
+    const int64_t rows = cols > 0 ? x.numel() / cols : 0;
+    Launch l(x, {&weight, &y});
+    check_launch("launch_rmsnorm_fwd", launch_rmsnorm_fwd(x.data_ptr(), weight.data_ptr(), y.data_ptr(), rows, cols,
+                                                          static_cast<float>(eps), dt, l.stream));
+}
+
 // ------------------------------------------------------------------ src/kernels/swiglu.rs:31-79
 void swiglu_fwd(const at::Tensor& gate, const at::Tensor& up, const at::Tensor& y) {
     const int32_t dt = tag_of("gate", gate);
@@ -522,6 +541,7 @@ PYBIND11_MODULE(_native, m) {
     m.doc() = "validation + FFI layer over libcustom_cuda_b200 (C ABI in include/custom_cuda_b200.h)";
     m.def("rmsnorm_residual_fwd", &rmsnorm_residual_fwd, py::arg("x"), py::arg("residual"), py::arg("weight"),
           py::arg("y"), py::arg("residual_out"), py::arg("eps"));
+    m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("weight"), py::arg("y"), py::arg("eps"));
     m.def("swiglu_fwd", &swiglu_fwd, py::arg("gate"), py::arg("up"), py::arg("y"));
     m.def("rope_fwd", &rope_fwd, py::arg("q"), py::arg("k"), py::arg("cos"), py::arg("sin"), py::arg("q_out"),
           py::arg("k_out"));

@@ -31,7 +31,9 @@ __device__ __forceinline__ float cta_sum_dyn(float v, float* slots) {
     return r;
 }
 
-template <typename T, int VPT>
+// kResidual = false is the plain RMSNorm used when the residual add has already been folded
+// into the producing GEMM: `res` and `res_out` are not touched (2 tensors of traffic, not 4).
+template <typename T, int VPT, bool kResidual>
 __global__ void __launch_bounds__(1024)
 rmsnorm_rowreg_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
                       T* __restrict__ y, T* __restrict__ res_out, int cols, int n_vec, float eps) {
@@ -50,7 +52,7 @@ rmsnorm_rowreg_kernel(const T* __restrict__ x, const T* __restrict__ res, const 
         const int i = threadIdx.x + j * blockDim.x;
         if (i < n_vec) {
             xv[j] = ld_stream(x16 + i);
-            rv[j] = ld_stream(r16 + i);
+            if constexpr (kResidual) rv[j] = ld_stream(r16 + i);
         }
     }
 
@@ -61,16 +63,21 @@ rmsnorm_rowreg_kernel(const T* __restrict__ x, const T* __restrict__ res, const 
     for (int j = 0; j < VPT; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < n_vec) {
-            float a[kPer], b[kPer];
-            unpack<T>(xv[j], a);
-            unpack<T>(rv[j], b);
+            float a[kPer];
+            if constexpr (kResidual) {
+                float b[kPer];
+                unpack<T>(xv[j], a);
+                unpack<T>(rv[j], b);
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) a[e] += b[e];
-            sv[j] = pack<T>(a);
+                for (int e = 0; e < kPer; ++e) a[e] += b[e];
+                sv[j] = pack<T>(a);
+                st_stream(o16 + i, sv[j]);
+            } else {
+                sv[j] = xv[j];
+            }
             unpack<T>(sv[j], a);
 #pragma unroll
             for (int e = 0; e < kPer; ++e) sq = fmaf(a[e], a[e], sq);
-            st_stream(o16 + i, sv[j]);
         }
     }
     const float total = cta_sum_dyn(sq, slots);
@@ -92,27 +99,31 @@ rmsnorm_rowreg_kernel(const T* __restrict__ x, const T* __restrict__ res, const 
 
 // Any column count / alignment: scalar accesses, the row sum is written to
 // residual_out in pass one and read back (by the thread that wrote it) in pass two.
-template <typename T>
+template <typename T, bool kResidual>
 __global__ void __launch_bounds__(256)
 rmsnorm_generic_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
                        T* __restrict__ y, T* res_out, int64_t cols, float eps) {
     __shared__ float slots[32];
     const int64_t off = static_cast<int64_t>(blockIdx.x) * cols;
+    const T* summed = kResidual ? res_out : x;          // pass two re-reads the row from here
     float sq = 0.0f;
     for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
-        const float s = Store<T>::round(Store<T>::load1(x + off + c) + Store<T>::load1(res + off + c));
-        Store<T>::store1(res_out + off + c, s);
+        float s = Store<T>::load1(x + off + c);
+        if constexpr (kResidual) {
+            s = Store<T>::round(s + Store<T>::load1(res + off + c));
+            Store<T>::store1(res_out + off + c, s);
+        }
         sq = fmaf(s, s, sq);
     }
     const float total = cta_sum_dyn(sq, slots);
     const float inv = 1.0f / sqrtf(total / static_cast<float>(cols) + eps);
     for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
-        const float s = Store<T>::load1(res_out + off + c);
+        const float s = Store<T>::load1(summed + off + c);
         Store<T>::store1(y + off + c, Store<T>::round(s * inv) * Store<T>::load1(w + c));
     }
 }
 
-template <typename T>
+template <typename T, bool kResidual>
 cudaError_t run(const void* x, const void* res, const void* w, void* y, void* res_out,
                 int64_t rows, int64_t cols, float eps, cudaStream_t stream) {
     constexpr int kPer = Store<T>::kPerVec;
@@ -123,21 +134,21 @@ cudaError_t run(const void* x, const void* res, const void* w, void* y, void* re
     T* op = static_cast<T*>(res_out);
     if (rows > 0x7fffffffLL) return cudaErrorInvalidValue;
     const unsigned grid = static_cast<unsigned>(rows);
-    const bool vec_ok = (cols % kPer == 0) && aligned16(x) && aligned16(res) && aligned16(w) &&
-                        aligned16(y) && aligned16(res_out);
+    const bool vec_ok = (cols % kPer == 0) && aligned16(x) && aligned16(w) && aligned16(y) &&
+                        (!kResidual || (aligned16(res) && aligned16(res_out)));
     const int64_t n_vec = cols / kPer;
     if (vec_ok && n_vec <= 8 * 1024) {
         const int vpt = n_vec <= 4 * 1024 ? 4 : 8;
         int threads = static_cast<int>(ceil_div64(ceil_div64(n_vec, vpt), 32) * 32);
         if (threads < 32) threads = 32;
         if (vpt == 4)
-            rmsnorm_rowreg_kernel<T, 4><<<grid, threads, 0, stream>>>(
+            rmsnorm_rowreg_kernel<T, 4, kResidual><<<grid, threads, 0, stream>>>(
                 xp, rp, wp, yp, op, static_cast<int>(cols), static_cast<int>(n_vec), eps);
         else
-            rmsnorm_rowreg_kernel<T, 8><<<grid, threads, 0, stream>>>(
+            rmsnorm_rowreg_kernel<T, 8, kResidual><<<grid, threads, 0, stream>>>(
                 xp, rp, wp, yp, op, static_cast<int>(cols), static_cast<int>(n_vec), eps);
     } else {
-        rmsnorm_generic_kernel<T><<<grid, 256, 0, stream>>>(xp, rp, wp, yp, op, cols, eps);
+        rmsnorm_generic_kernel<T, kResidual><<<grid, 256, 0, stream>>>(xp, rp, wp, yp, op, cols, eps);
     }
     return cudaGetLastError();
 }
@@ -151,9 +162,24 @@ extern "C" int32_t launch_rmsnorm_residual_fwd(const void* x, const void* residu
     if (rows <= 0 || cols <= 0) return cudaSuccess;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (dtype) {
-        case cck::kF32:  return cck::run<float>(x, residual, weight, y, residual_out, rows, cols, eps, s);
-        case cck::kF16:  return cck::run<__half>(x, residual, weight, y, residual_out, rows, cols, eps, s);
-        case cck::kBF16: return cck::run<__nv_bfloat16>(x, residual, weight, y, residual_out, rows, cols, eps, s);
+        case cck::kF32:  return cck::run<float, true>(x, residual, weight, y, residual_out, rows, cols, eps, s);
+        case cck::kF16:  return cck::run<__half, true>(x, residual, weight, y, residual_out, rows, cols, eps, s);
+        case cck::kBF16: return cck::run<__nv_bfloat16, true>(x, residual, weight, y, residual_out, rows, cols, eps, s);
+        default:         return cudaErrorInvalidValue;
+    }
+}
+
+// y = x * rsqrt(mean(x^2) + eps) * weight: the norm alone, for callers whose residual add already
+// happened in the producing GEMM's epilogue (no counterpart in the reference).  Same rounding as
+// launch_rmsnorm_residual_fwd with a zero residual, half the HBM traffic.
+extern "C" int32_t launch_rmsnorm_fwd(const void* x, const void* weight, void* y, int64_t rows, int64_t cols,
+                                      float eps, int32_t dtype, void* stream) {
+    if (rows <= 0 || cols <= 0) return cudaSuccess;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case cck::kF32:  return cck::run<float, false>(x, nullptr, weight, y, nullptr, rows, cols, eps, s);
+        case cck::kF16:  return cck::run<__half, false>(x, nullptr, weight, y, nullptr, rows, cols, eps, s);
+        case cck::kBF16: return cck::run<__nv_bfloat16, false>(x, nullptr, weight, y, nullptr, rows, cols, eps, s);
         default:         return cudaErrorInvalidValue;
     }
 }

@@ -11,7 +11,8 @@ The reference swaps in its three bandwidth-bound kernels and leaves every
 projection to ``nn.Linear`` (cuBLAS); here the seven projections also run on this
 library's tcgen05 GEMM (``matmul_add_bias`` with no bias), and by default two of
 them carry the neighbouring elementwise op in their epilogue - gate/up + SwiGLU in
-one GEMM, down_proj + the final residual add in another - and q, k, v come from one
+one GEMM, o_proj and down_proj + their residual adds in two more (so both norms read
+one tensor instead of two) - and q, k, v come from one
 projection whose q / k column ranges RoPE reads in place; results are identical to
 the unfused chain (``fused=False`` runs that chain).  The attention core stays
 ``torch.nn.functional.scaled_dot_product_attention`` as in the reference.
@@ -27,7 +28,7 @@ import torch.nn.functional as F
 
 from .kernels.fused import GATE_UP_BLOCK, interleave_gate_up, matmul_add_bias_residual, matmul_swiglu
 from .kernels.matmul_add_bias import matmul_add_bias
-from .kernels.rmsnorm_residual import rmsnorm_residual
+from .kernels.rmsnorm_residual import rmsnorm, rmsnorm_residual
 from .kernels.rope import rope, rope_strided
 from .kernels.swiglu import swiglu
 
@@ -125,8 +126,11 @@ class LlamaBlock:
             raise ValueError(f"sequence positions {pos_offset}..{pos_offset + s - 1} exceed the RoPE table "
                              f"({self.cos.shape[0]} rows)")
         x2 = x.view(b * s, hid)
-        zero = t.run("fill", torch.zeros_like, x2)
-        h, res = t.run("rmsnorm", rmsnorm_residual, x2, zero, w["input_layernorm_weight"], self.eps)
+        if self.fused:       # x + 0 is x: the norm alone, and x itself is the residual stream
+            h, res = t.run("rmsnorm", rmsnorm, x2, w["input_layernorm_weight"], self.eps), x2
+        else:
+            zero = t.run("fill", torch.zeros_like, x2)
+            h, res = t.run("rmsnorm", rmsnorm_residual, x2, zero, w["input_layernorm_weight"], self.eps)
         cos, sin = self.cos[pos_offset:pos_offset + s], self.sin[pos_offset:pos_offset + s]
         if self.fused:       # one projection for q, k and v; rope reads its q / k column ranges in place
             qkv = t.run("gemm", matmul_add_bias, h, self.w_qkv).view(b, s, -1)
@@ -143,8 +147,12 @@ class LlamaBlock:
         att = t.run("sdpa", F.scaled_dot_product_attention, q.transpose(1, 2), k.transpose(1, 2),
                     v.transpose(1, 2), is_causal=True, enable_gqa=self.n_heads != self.n_kv_heads)
         att = t.run("copy", lambda a: a.transpose(1, 2).contiguous().view(b * s, hid), att)
-        att = t.run("gemm", matmul_add_bias, att, w["o_proj"])
-        h2, res2 = t.run("rmsnorm", rmsnorm_residual, att, res, w["post_attention_layernorm_weight"], self.eps)
+        if self.fused:       # o_proj adds the residual in its epilogue; the norm reads that sum once
+            res2 = t.run("gemm_residual", matmul_add_bias_residual, att, w["o_proj"], None, res)
+            h2 = t.run("rmsnorm", rmsnorm, res2, w["post_attention_layernorm_weight"], self.eps)
+        else:
+            att = t.run("gemm", matmul_add_bias, att, w["o_proj"])
+            h2, res2 = t.run("rmsnorm", rmsnorm_residual, att, res, w["post_attention_layernorm_weight"], self.eps)
         if self.fused:
             act = t.run("gemm_swiglu", matmul_swiglu, h2, self.w_gate_up)
             out = t.run("gemm_residual", matmul_add_bias_residual, act, w["down_proj"], None, res2)

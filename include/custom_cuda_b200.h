@@ -118,6 +118,12 @@ int64_t cck_lce_noalloc_max_workspace_bytes(void);
 int32_t launch_lce_finalize(const float* stats, const int64_t* targets, int64_t n, int64_t n_shards,
                             int64_t ignore_index, float* loss_rows, float* reduce_out, void* stream);
 
+/* y = x * rsqrt(mean(x^2) + eps) * weight - the norm of launch_rmsnorm_residual_fwd alone, for
+ * callers whose residual add already happened in the producing GEMM's epilogue.  x, y [rows, cols];
+ * weight [cols]; one dtype.  Equals launch_rmsnorm_residual_fwd with a zero residual. */
+int32_t launch_rmsnorm_fwd(const void* x, const void* weight, void* y, int64_t rows, int64_t cols, float eps,
+                           int32_t dtype, void* stream);
+
 /* launch_rope_fwd for inputs whose tokens are not packed: consecutive tokens of q (k) are
  * q_token_stride (k_token_stride) elements apart - e.g. q and k are column ranges of one fused
  * QKV projection output [tokens, (Hq + 2 Hkv) * D].  Heads of one token are contiguous; q_out and

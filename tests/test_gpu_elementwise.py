@@ -173,3 +173,18 @@ def test_rope_strided_views_equal_packed_inputs(dims, dtype):
     check(k1, k_ref, dtype)
     with pytest.raises(ValueError):
         rope_strided(q.transpose(1, 2), k.transpose(1, 2), cos, sin)     # heads no longer contiguous per token
+
+
+@pytest.mark.parametrize("shape", [(5, 100), (64, 768), (300, 4096), (3, 20000), (2, 40000)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_rmsnorm_alone_equals_zero_residual(shape, dtype):
+    """The norm without the residual add gives exactly what rmsnorm_residual gives for a zero residual."""
+    from custom_cuda.kernels.rmsnorm_residual import rmsnorm, rmsnorm_residual
+    g = torch.Generator().manual_seed(shape[1])
+    x = torch.randn(shape, generator=g).to(dtype).to(DEV)
+    w = (1 + 0.1 * torch.randn(shape[1], generator=g)).to(dtype).to(DEV)
+    y = rmsnorm(x, w, 1e-5)
+    y_ref, ro = rmsnorm_residual(x, torch.zeros_like(x), w, 1e-5)
+    assert torch.equal(y, y_ref) and torch.equal(ro, x)
+    want, _ = ops.rmsnorm_residual(x.cpu(), torch.zeros_like(x).cpu(), w.cpu(), 1e-5)
+    check(y, want, dtype)

@@ -120,3 +120,28 @@ def test_lce_config5_shapes_sampled_rows():
     want_rows = ops.linear_cross_entropy_fp64(h[rows], w, t[rows], reduction="none")
     torch.testing.assert_close(per_row[rows].double(), want_rows, rtol=1e-4, atol=1e-5)
     assert device_status_clean(got)
+
+
+def test_lce_config5_full_size_properties():
+    """Benchmark config 5 at full size (16384 x 4096 x 128256, 5 % ignored): the mean equals the
+    masked mean of the per-row losses, eight vocabulary shards merge to the single-shot result,
+    and 64 sampled rows match the fp64 oracle to 1e-4."""
+    from custom_cuda.kernels.linear_cross_entropy import (lce_loss_from_stats, lce_row_stats,
+                                                          linear_cross_entropy)
+    from custom_cuda_kernals_b200 import dist
+    h, w, t = workloads.lce_bf16()
+    hd, wd, td = to_dev(h, w, t)
+    mean = linear_cross_entropy(hd, wd, td)
+    rows = linear_cross_entropy(hd, wd, td, reduction="none")
+    total = linear_cross_entropy(hd, wd, td, reduction="sum")
+    keep = td != -100
+    assert torch.all(rows[~keep] == 0)
+    torch.testing.assert_close(total, rows.double().sum().float(), rtol=1e-5, atol=0)
+    torch.testing.assert_close(mean, (rows.double().sum() / keep.sum()).float(), rtol=1e-5, atol=0)
+    stats = torch.stack([lce_row_stats(hd, wd[a:b], td, a)
+                         for a, b in (dist.vocab_range(w.shape[0], r, 8) for r in range(8))])
+    torch.testing.assert_close(lce_loss_from_stats(stats, td, -100, "mean"), mean, rtol=1e-6, atol=0)
+    pick = torch.arange(5, 16384, 256)
+    want = ops.linear_cross_entropy_fp64(h[pick], w, t[pick], reduction="none")
+    torch.testing.assert_close(rows[pick.to(DEV)].cpu().double(), want, rtol=1e-4, atol=1e-5)
+    assert device_status_clean(mean)
