@@ -233,6 +233,24 @@ def bench_ops(dev, rank, world, peaks, src):
     cpu_on = world == 1 and rank == 0
     flush = torch.empty(128 << 20, dtype=torch.float32, device=dev) if world == 1 else None   # 512 MB
 
+    # Beside each op (N=1): the reference project's own kernel, compiled unchanged for sm_100a
+    # (oracle/_ref, built by oracle/build_ref.py where a reference checkout exists), timed the
+    # same way on the same inputs.  A baseline leg like cpu_baseline: measured, never shipped.
+    ref = None
+    if cpu_on:
+        from oracle import ref_kernels
+        ref = ref_kernels if ref_kernels.available() else None
+
+    def reference_kernel(name, fn, arg_sets, work, iters, graph=True):
+        if ref is None:
+            return
+        secs = timed_loop(fn, arg_sets, iters, graph=graph)
+        scale = 1e9 if out[name]["bound"] == "hbm" else 1e12
+        out[name]["reference_kernel"] = {
+            "achieved": round(work / secs / scale, 2), "unit": out[name]["unit"], "us_per_launch": round(secs * 1e6, 2),
+            "speedup": round(secs / (out[name]["us_per_launch"] * 1e-6), 2),
+            "what": "the reference's own CUDA kernel recompiled for sm_100a (-O3 --use_fast_math), same inputs, same timing"}
+
     def wrapper(name, fn, arg_sets):
         if flush is not None:
             out[name]["wrapper_call"] = wrapper_call_stats(fn, arg_sets, flush)
@@ -263,6 +281,8 @@ def bench_ops(dev, rank, world, peaks, src):
     record("rmsnorm_residual_fp32", "hbm", rows * 4096 * 4 * 4, timed_loop(rmsnorm_residual, sets, 120, graph=True),
            f"rows {rows} of 2048")
     wrapper("rmsnorm_residual_fp32", rmsnorm_residual, sets)
+    if ref:
+        reference_kernel("rmsnorm_residual_fp32", ref.rmsnorm_residual, sets, rows * 4096 * 16, 120)
     if cpu_on:
         cx, cr, cw = (t.cpu() for t in sets[0][:3])
         cpu("rmsnorm_residual_fp32", rows * 4096 * 16, lambda: O.rmsnorm_residual(cx, cr, cw, 1e-5), "all 2048 rows")
@@ -273,6 +293,8 @@ def bench_ops(dev, rank, world, peaks, src):
     sets = [(rn(rows, 14336), rn(rows, 14336)) for _ in range(2 if world == 1 else 3)]
     record("swiglu_bf16", "hbm", rows * 14336 * 2 * 3, timed_loop(swiglu, sets, 30, graph=True), f"rows {rows} of 8192")
     wrapper("swiglu_bf16", swiglu, sets)
+    if ref:
+        reference_kernel("swiglu_bf16", ref.swiglu, sets, rows * 14336 * 6, 30)
     if cpu_on:
         cg, cu = sets[0][0][:2048].cpu(), sets[0][1][:2048].cpu()
         cpu("swiglu_bf16", 2048 * 14336 * 6, lambda: O.swiglu(cg, cu), "2048 of 8192 rows")
@@ -291,6 +313,8 @@ def bench_ops(dev, rank, world, peaks, src):
     record("rope_bf16", "hbm", b * (s1 - s0) * 40 * 128 * 2 * 2, timed_loop(rope, sets, 120, graph=True),
            f"batch {b} x positions {s0}..{s1}")
     wrapper("rope_bf16", rope, sets)
+    if ref:
+        reference_kernel("rope_bf16", ref.rope, sets, b * (s1 - s0) * 40 * 128 * 4, 120)
     if cpu_on:
         cq, ck, cc, cs = (t.cpu() for t in sets[0])
         cpu("rope_bf16", b * (s1 - s0) * 40 * 128 * 4, lambda: O.rope(cq, ck, cc, cs), "all of config 2b")
@@ -308,6 +332,9 @@ def bench_ops(dev, rank, world, peaks, src):
            timed_loop(fp8_quant, [(s[0], "e4m3", "block") for s in sets], 120, graph=True), f"rows {rows} of 8192")
     wrapper("fp8_quant_token_bf16", fp8_quant, sets)
     wrapper("fp8_quant_block_bf16", fp8_quant, [(s[0], "e4m3", "block") for s in sets])
+    if ref:      # the reference has no per-token mode; its block kernel is the comparator for ours
+        reference_kernel("fp8_quant_block_bf16", ref.fp8_quant, [(s[0], "e4m3", "block") for s in sets],
+                         rows * 4096 * 3, 120)
     if cpu_on:
         cx8 = sets[0][0].cpu()
         cpu("fp8_quant_token_bf16", rows * 4096 * 3, lambda: O.fp8_quant(cx8, "e4m3", "token"), "all 8192 rows")
@@ -317,6 +344,9 @@ def bench_ops(dev, rank, world, peaks, src):
     a, w, bias = rn(8192, 4096), rn(n1 - n0, 4096, scale=0.02), rn(n1 - n0, scale=0.02)
     record("matmul_add_bias_bf16", "tensor", 2 * 8192 * 4096 * (n1 - n0),
            timed_loop(matmul_add_bias, [(a, w, bias)], 20), f"columns {n1 - n0} of 14336")
+    if ref:      # the reference GEMM is a CUDA-core kernel: tens of milliseconds per launch, timed eagerly
+        reference_kernel("matmul_add_bias_bf16", ref.matmul_add_bias, [(a, w, bias)], 2 * 8192 * 4096 * (n1 - n0), 3,
+                         graph=False)
     if cpu_on:
         ca, cwt, cb = a[:1024].cpu(), w.cpu(), bias.cpu()
         cpu("matmul_add_bias_bf16", 2 * 1024 * 4096 * (n1 - n0), lambda: O.matmul_add_bias(ca, cwt, cb),
@@ -344,6 +374,12 @@ def bench_ops(dev, rank, world, peaks, src):
 
     record("linear_cross_entropy_bf16", "tensor", 2 * 16384 * 4096 * (v1 - v0),
            timed_loop(lce, [(h, wv, t)], 4 if world == 1 else 8, warm=2), f"vocab rows {v1 - v0} of 128256")
+    if ref:      # the reference path: 32 cuBLAS chunk GEMMs + its chunk-update kernel (logits chunks materialised)
+        reference_kernel("linear_cross_entropy_bf16", ref.linear_cross_entropy, [(h, wv, t)],
+                         2 * 16384 * 4096 * (v1 - v0), 3, graph=False)
+        out["linear_cross_entropy_bf16"]["reference_kernel"]["what"] = (
+            "the reference's wrapper loop: torch matmul (cuBLAS) per 4096-column chunk + its chunk-update kernel "
+            "recompiled for sm_100a")
     if cpu_on:
         ch, cwv, ct = h[:256].cpu(), wv.cpu(), t[:256].cpu()
         cpu("linear_cross_entropy_bf16", 2 * 256 * 4096 * (v1 - v0), lambda: O.linear_cross_entropy(ch, cwv, ct),
