@@ -125,6 +125,67 @@ struct EpiLce {
     }
 };
 
+// ---- backward helper: d(loss)/d(logits) for a block of rows, written in the storage type.
+//   dl[i, j] = (exp(l_ij - lse_i) - [j == target_i]) * grad_scale   (0 for ignored rows)
+// The logits tile is recomputed by the same mainloop and turned into its gradient in the
+// epilogue; the caller then forms d_hidden = dl @ W and d_weight += dl^T @ hidden with the GEMM.
+template <typename T>
+struct EpiDlogits {
+    struct Params {
+        const int64_t* targets;   // [n]
+        const float* lse;         // [n] log-sum-exp of each row's logits (from the forward statistics)
+        T* dl;                    // [n, v]
+        int64_t n, v;
+        int64_t ignore_index;
+        float grad_scale;
+        int vec_ok;
+    };
+    struct Thread {
+        float neg_lse2;           // -lse * log2(e)
+        float scale;              // grad_scale, or 0 for an ignored row
+        int64_t target;
+    };
+    __device__ static __forceinline__ void tile_begin(const Params& p, Thread& th, const TileWork& w, float*, int,
+                                                      int row_in_tile) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        th.target = -1;
+        th.scale = 0.0f;
+        th.neg_lse2 = 0.0f;
+        if (row < p.n) {
+            th.target = p.targets[row];
+            th.scale = th.target == p.ignore_index ? 0.0f : p.grad_scale;
+            th.neg_lse2 = -p.lse[row] * kLog2e;
+        }
+    }
+    __device__ static __forceinline__ void chunk(const Params& p, Thread& th, const TileWork& w, int row_in_tile, int c0,
+                                                 float (&acc)[32], const float*) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        const int64_t col = static_cast<int64_t>(w.n_tile) * kBN + c0;
+        if (row >= p.n || col >= p.v) return;
+        const int64_t t_off = th.target - col;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float prob = ex2_approx(fmaf(acc[j], kLog2e, th.neg_lse2));
+            acc[j] = (prob - (j == t_off ? 1.0f : 0.0f)) * th.scale;
+        }
+        T* out = p.dl + row * p.v + col;
+        if (p.vec_ok && col + 32 <= p.v) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                Vec16 o;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o.w[i] = Store<T>::pack2(acc[8 * q + 2 * i], acc[8 * q + 2 * i + 1]);
+                st_stream(out + 8 * q, o);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col + j < p.v) Store<T>::store1(out + j, acc[j]);
+        }
+    }
+    __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
+};
+
 // partials [splits][3][N] -> row_stats [3][N]
 __global__ void __launch_bounds__(256)
 lce_merge_kernel(const float* __restrict__ partials, int splits, int64_t n, float* __restrict__ row_stats) {
@@ -338,4 +399,46 @@ extern "C" int32_t launch_linear_cross_entropy_fwd_noalloc(const void* hidden, c
     if (scratch == nullptr) return err;
     return launch_linear_cross_entropy_fwd(hidden, weight, targets, v_start, n, h, v_count, row_stats, scratch,
                                            kNoAllocScratchBytes, dtype, stream);
+}
+
+// d(loss)/d(logits) of rows [0, n) against the whole vocabulary [0, v), in the storage type
+// (no counterpart in the reference, which is forward-only).  lse[i] = max_i + log(sumexp_i) from
+// the forward statistics; grad_scale = upstream gradient (x 1/valid_rows for a mean reduction).
+extern "C" int32_t launch_lce_dlogits_fwd(const void* hidden, const void* weight, const int64_t* targets,
+                                          const float* lse, int64_t n, int64_t h, int64_t v, int64_t ignore_index,
+                                          float grad_scale, void* dlogits, int32_t dtype, void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (n <= 0 || v <= 0 || h <= 0) return cudaSuccess;
+    if (dtype != kBF16 && dtype != kF16) return cudaErrorInvalidValue;
+    if (h % 8 != 0 || !aligned16(hidden) || !aligned16(weight) || n >= (1LL << 31) || v >= (1LL << 31) || h >= (1LL << 31))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int m_tiles = static_cast<int>(ceil_div64(n, kBM)), n_tiles = static_cast<int>(ceil_div64(v, kBN));
+    const int vec_ok = (v % 8 == 0 && aligned16(dlogits)) ? 1 : 0;
+    auto run = [&](auto tag) -> cudaError_t {
+        using T = decltype(tag);
+        using Epi = EpiDlogits<T>;
+        constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+        const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        const uint32_t fmt = is_bf16 ? 1u : 0u;
+        typename Epi::Params ep{targets, lse, static_cast<T*>(dlogits), n, v, ignore_index, grad_scale, vec_ok};
+        const bool pair = m_tiles >= 2 && pair_kernels_enabled() && max_pairs<false, SchedGemm, Epi>() > 0;
+        CUtensorMap ta, tb;
+        cudaError_t e = make_tmap(&ta, dt, 2, hidden, n, h, kBM);
+        if (e != cudaSuccess) return e;
+        e = make_tmap(&tb, dt, 2, weight, v, h, pair ? 128 : kBN);
+        if (e != cudaSuccess) return e;
+        if (pair) {
+            const int m_pairs = (m_tiles + 1) / 2;
+            SchedGemm::Params sp{m_pairs, n_tiles, raster_group(2 * kBM, h, 2, m_pairs)};
+            return launch_pair<false, SchedGemm, Epi>(ta, tb, sp, ep, h, ptx::instr_desc(fmt, fmt, 2 * kBM, kBN),
+                                                      static_cast<int64_t>(m_pairs) * n_tiles, s);
+        }
+        SchedGemm::Params sp{m_tiles, n_tiles, raster_group(kBM, h, 2, m_tiles)};
+        const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
+        return launch<false, SchedGemm, Epi>(ta, tb, sp, ep, h, ptx::instr_desc(fmt, fmt, kBM, kBN),
+                                             static_cast<int>(tiles < sm_count() ? tiles : sm_count()), s);
+    };
+    return dtype == kBF16 ? run(__nv_bfloat16{}) : run(__half{});
 }

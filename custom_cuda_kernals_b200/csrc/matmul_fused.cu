@@ -109,6 +109,40 @@ struct EpiBiasResidual {
     __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
 };
 
+// ---- epilogue: y_f32 += acc   (fp32 accumulation across calls, e.g. a weight gradient
+// summed over row blocks)
+struct EpiAccumF32 {
+    struct Params {
+        float* y;
+        int64_t m, n;
+    };
+    struct Thread {};
+    __device__ static __forceinline__ void tile_begin(const Params&, Thread&, const TileWork&, float*, int, int) {}
+    __device__ static __forceinline__ void chunk(const Params& p, Thread&, const TileWork& w, int row_in_tile, int c0,
+                                                 float (&acc)[32], const float*) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        const int64_t col = static_cast<int64_t>(w.n_tile) * kBN + c0;
+        if (row >= p.m || col >= p.n) return;
+        float* out = p.y + row * p.n + col;
+        if (p.n % 4 == 0 && col + 32 <= p.n) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                float4 v = *reinterpret_cast<const float4*>(out + 4 * q);
+                v.x += acc[4 * q];
+                v.y += acc[4 * q + 1];
+                v.z += acc[4 * q + 2];
+                v.w += acc[4 * q + 3];
+                *reinterpret_cast<float4*>(out + 4 * q) = v;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col + j < p.n) out[j] += acc[j];
+        }
+    }
+    __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
+};
+
 inline bool tc_shape_ok(const void* a, const void* b, int64_t m, int64_t k, int64_t n) {
     return k % 8 == 0 && k >= 8 && aligned16(a) && aligned16(b) && m < (1LL << 31) && n < (1LL << 31) &&
            k < (1LL << 31);
@@ -181,5 +215,20 @@ extern "C" int32_t launch_matmul_add_bias_residual_fwd(const void* x, const void
                                            static_cast<__half*>(y), m, n, vec_ok};
         return run_fused<__half, EpiBiasResidual<__half>>(x, weight, m, k, n, ep, s);
     }
+    return cudaErrorInvalidValue;
+}
+
+// y_f32[m, n] += x[m, k] @ weight[n, k]^T: 16-bit operands, fp32 output accumulated in place
+// across calls (no counterpart in the reference).  y must be 16-byte aligned.
+extern "C" int32_t launch_matmul_accumulate_f32_fwd(const void* x, const void* weight, float* y, int64_t m, int64_t k,
+                                                    int64_t n, int32_t dtype, void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (m <= 0 || k <= 0 || n <= 0) return cudaSuccess;
+    if (!tc_shape_ok(x, weight, m, k, n) || !aligned16(y)) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EpiAccumF32::Params ep{y, m, n};
+    if (dtype == kBF16) return run_fused<__nv_bfloat16, EpiAccumF32>(x, weight, m, k, n, ep, s);
+    if (dtype == kF16) return run_fused<__half, EpiAccumF32>(x, weight, m, k, n, ep, s);
     return cudaErrorInvalidValue;
 }

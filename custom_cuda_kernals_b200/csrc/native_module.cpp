@@ -500,6 +500,49 @@ void linear_cross_entropy_fwd(const at::Tensor& hidden, const at::Tensor& weight
                                                  ws_bytes, dt, l.stream));
 }
 
+// backward helpers (no counterpart in the reference)
+void lce_dlogits_fwd(const at::Tensor& hidden, const at::Tensor& weight, const at::Tensor& targets,
+                     const at::Tensor& lse, int64_t ignore_index, double grad_scale, const at::Tensor& dlogits) {
+    const int32_t dt = tag_of("hidden", hidden);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_same_dtype("dlogits", tag_of("dlogits", dlogits), dt);
+    expect_int("targets", targets, at::kLong, "int64");
+    expect_f32("lse", tag_of("lse", lse));
+    if (hidden.dim() != 2 || weight.dim() != 2 || weight.size(1) != hidden.size(1))
+        value_error("shape mismatch: hidden [N, H] and weight [V, H] expected; got hidden=" + shape_str(hidden) +
+                    ", weight=" + shape_str(weight));
+    const int64_t n = hidden.size(0), h = hidden.size(1), v = weight.size(0);
+    if (targets.numel() != n || lse.numel() != n) value_error("shape mismatch: targets and lse must have " + std::to_string(n) + " elements");
+    if (dlogits.dim() != 2 || dlogits.size(0) != n || dlogits.size(1) != v)
+        value_error("shape mismatch: dlogits shape " + shape_str(dlogits) + " must be [" + std::to_string(n) + ", " + std::to_string(v) + "]");
+    if (h % 8 != 0) value_error("shape mismatch: hidden dim must be a multiple of 8");
+    Launch l(hidden, {&weight, &targets, &lse, &dlogits});
+    check_launch("launch_lce_dlogits_fwd",
+                 launch_lce_dlogits_fwd(hidden.data_ptr(), weight.data_ptr(), static_cast<const int64_t*>(targets.data_ptr()),
+                                        static_cast<const float*>(lse.data_ptr()), n, h, v, ignore_index,
+                                        static_cast<float>(grad_scale), dlogits.data_ptr(), dt, l.stream));
+}
+
+void matmul_accumulate_f32_fwd(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& y) {
+    const int32_t dt = tag_of("x", x);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_f32("y", tag_of("y", y));
+    if (x.dim() != 2 || weight.dim() != 2 || weight.size(1) != x.size(1))
+        value_error("shape mismatch: x [M, K] and weight [N, K] expected; got x=" + shape_str(x) + ", weight=" + shape_str(weight));
+    const int64_t m = x.size(0), k = x.size(1), n = weight.size(0);
+    if (y.dim() != 2 || y.size(0) != m || y.size(1) != n)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " + std::to_string(n) + "]");
+    if (k % 8 != 0) value_error("shape mismatch: K must be a multiple of 8");
+    Launch l(x, {&weight, &y});
+    check_launch("launch_matmul_accumulate_f32_fwd",
+                 launch_matmul_accumulate_f32_fwd(x.data_ptr(), weight.data_ptr(), static_cast<float*>(y.data_ptr()), m, k,
+                                                  n, dt, l.stream));
+}
+
 int64_t lce_workspace_bytes(const at::Tensor& like, int64_t n, int64_t v) {
     c10::cuda::CUDAGuard guard(like.device());
     return cck_lce_workspace_bytes(n, v);
@@ -565,6 +608,9 @@ PYBIND11_MODULE(_native, m) {
           py::arg("bias").none(true), py::arg("residual"), py::arg("y"));
     m.def("linear_cross_entropy_fwd", &linear_cross_entropy_fwd, py::arg("hidden"), py::arg("weight"),
           py::arg("targets"), py::arg("v_start"), py::arg("row_stats"), py::arg("workspace"));
+    m.def("lce_dlogits_fwd", &lce_dlogits_fwd, py::arg("hidden"), py::arg("weight"), py::arg("targets"), py::arg("lse"),
+          py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"));
+    m.def("matmul_accumulate_f32_fwd", &matmul_accumulate_f32_fwd, py::arg("x"), py::arg("weight"), py::arg("y"));
     m.def("lce_workspace_bytes", &lce_workspace_bytes, py::arg("like"), py::arg("n"), py::arg("v_count"));
     m.def("lce_finalize", &lce_finalize, py::arg("stats"), py::arg("targets"), py::arg("ignore_index"),
           py::arg("loss_rows").none(true), py::arg("reduce_out"));

@@ -27,7 +27,8 @@ import torch
 import torch.distributed as dist
 
 __all__ = ["init_from_env", "row_range", "sequence_range", "column_range", "vocab_range",
-           "gather_row_stats", "vocab_parallel_linear_cross_entropy", "max_over_ranks"]
+           "gather_row_stats", "vocab_parallel_linear_cross_entropy",
+           "vocab_parallel_linear_cross_entropy_fwd_bwd", "max_over_ranks"]
 
 VOCAB_TILE = 128
 
@@ -112,6 +113,37 @@ def vocab_parallel_linear_cross_entropy(hidden: torch.Tensor, weight_shard: torc
         raise ValueError(f"reduction must be 'mean', 'sum', or 'none', got {reduction!r}")
     stats = lce_row_stats(hidden, weight_shard, targets, v_start)
     return lce_loss_from_stats(gather_row_stats(stats, group), targets, ignore_index, reduction)
+
+
+def vocab_parallel_linear_cross_entropy_fwd_bwd(hidden: torch.Tensor, weight_shard: torch.Tensor,
+                                                targets: torch.Tensor, v_start: int, ignore_index: int = -100,
+                                                reduction: str = "mean", rows_per_chunk: int = 4096,
+                                                scatter_rows: bool = False, group=None
+                                                ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Loss, ``d_hidden`` and this rank's ``d_weight`` rows for a vocabulary-sharded LM head.
+
+    Two collectives: the ``[3, N]`` all-gather of the forward, and one reduction of the
+    per-shard ``d_hidden`` contributions - an all-reduce, or with ``scatter_rows`` (``N``
+    divisible by the world size) a reduce-scatter that leaves each rank with its
+    ``row_range`` of ``d_hidden``.  ``d_weight`` needs no exchange: every rank owns its rows."""
+    from .kernels.linear_cross_entropy import (lce_grad_scale, lce_gradients, lce_loss_from_stats,
+                                               lce_lse_from_stats, lce_row_stats)
+    scale = lce_grad_scale(targets, ignore_index, reduction)
+    stats = gather_row_stats(lce_row_stats(hidden, weight_shard, targets, v_start), group)
+    loss = lce_loss_from_stats(stats, targets, ignore_index, reduction)
+    d_hidden, d_weight = lce_gradients(hidden, weight_shard, targets, lce_lse_from_stats(stats), scale, v_start,
+                                       ignore_index, rows_per_chunk)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        world = dist.get_world_size(group)
+        if scatter_rows:
+            if hidden.shape[0] % world:
+                raise ValueError(f"scatter_rows needs N ({hidden.shape[0]}) divisible by the world size ({world})")
+            mine = torch.empty(hidden.shape[0] // world, hidden.shape[1], dtype=d_hidden.dtype, device=d_hidden.device)
+            dist.reduce_scatter_tensor(mine, d_hidden, group=group)
+            d_hidden = mine
+        else:
+            dist.all_reduce(d_hidden, group=group)
+    return loss, d_hidden, d_weight
 
 
 def max_over_ranks(value: float, device=None) -> float:

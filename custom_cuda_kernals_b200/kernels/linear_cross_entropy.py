@@ -15,7 +15,8 @@ import torch
 
 from .. import _native
 
-__all__ = ["linear_cross_entropy", "lce_row_stats", "lce_loss_from_stats", "DEFAULT_CHUNK_SIZE"]
+__all__ = ["linear_cross_entropy", "lce_row_stats", "lce_loss_from_stats", "linear_cross_entropy_fwd_bwd", "lce_gradients", "lce_lse_from_stats", "lce_grad_scale",
+           "linear_cross_entropy_trainable", "DEFAULT_CHUNK_SIZE"]
 
 DEFAULT_CHUNK_SIZE = 4096
 IGNORE_INDEX = -100
@@ -92,3 +93,110 @@ def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, targets: to
         return empty.sum() if reduction == "sum" else empty.sum() / 0.0
     stats = lce_row_stats(hidden, weight, targets, 0, chunk_size)
     return lce_loss_from_stats(stats.unsqueeze(0), targets, ignore_index, reduction)
+
+
+def lce_lse_from_stats(stats: torch.Tensor) -> torch.Tensor:
+    """Row-wise log-sum-exp over the whole vocabulary from ``[shards, 3, N]`` statistics."""
+    m = stats[:, 0].amax(dim=0)
+    total = (stats[:, 1] * torch.exp(stats[:, 0] - m)).sum(dim=0)
+    return (m + torch.log(total)).contiguous()
+
+
+def _local_targets(targets: torch.Tensor, v_start: int, v: int, ignore_index: int) -> torch.Tensor:
+    """Targets as column indices of a vocabulary shard: ignored rows keep ``ignore_index``, rows
+    whose target lies in another shard get a value that matches no column."""
+    if v_start == 0:
+        return targets       # out-of-range targets match no column already
+    outside = -1 if ignore_index != -1 else -2
+    local = targets - v_start
+    local = torch.where((local >= 0) & (local < v), local, torch.full_like(local, outside))
+    return torch.where(targets == ignore_index, targets, local).contiguous()
+
+
+def lce_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor,
+                  grad_scale: float, v_start: int = 0, ignore_index: int = IGNORE_INDEX,
+                  rows_per_chunk: int = 4096, weight_t: torch.Tensor | None = None
+                  ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Gradients of ``grad_scale * sum_i loss_i`` for the vocabulary rows ``weight`` holds
+    (``v_start ...`` of the LM head): ``d_weight`` for those rows, and this shard's
+    contribution to ``d_hidden`` (the whole ``d_hidden`` when ``weight`` is the whole head).
+
+    ``rows_per_chunk`` rows at a time: the logits of the chunk are recomputed on the tensor
+    cores and turned into ``dlogits = (exp(logit - lse) - onehot) * grad_scale`` in the
+    epilogue (``[rows, V]`` in the storage type - the only logits-sized buffer), then
+    ``d_hidden = dlogits @ W`` and ``d_weight += dlogits^T @ hidden`` run on the same GEMM
+    engine, ``d_weight`` accumulating in fp32 across chunks."""
+    n, h = hidden.shape
+    v = weight.shape[0]
+    if not (_fused_ok(hidden, weight) and hidden.is_cuda) or v % 8 != 0:
+        raise ValueError("the gradient path needs float16/bfloat16 CUDA inputs with H and V multiples of 8")
+    local = _local_targets(targets, v_start, v, ignore_index)
+    w_t = weight_t if weight_t is not None else weight.t().contiguous()          # [H, V]
+    d_hidden = torch.empty_like(hidden)
+    d_weight = torch.zeros(v, h, dtype=torch.float32, device=hidden.device)
+    for r0 in range(0, n, rows_per_chunk):
+        r1 = min(n, r0 + rows_per_chunk)
+        rows = r1 - r0
+        hc = hidden[r0:r1]
+        dl = torch.empty(rows, v, dtype=hidden.dtype, device=hidden.device)
+        _native.lce_dlogits_fwd(hc, weight, local[r0:r1], lse[r0:r1], ignore_index, grad_scale, dl)
+        _native.matmul_add_bias_fwd(dl, w_t, None, d_hidden[r0:r1])                # [r, V] x [H, V]^T
+        if rows % 8:       # K of the weight-gradient GEMM is the row count: pad it to a multiple of 8
+            pad = 8 - rows % 8
+            dl_t = torch.nn.functional.pad(dl.t(), (0, pad)).contiguous()
+            hc_t = torch.nn.functional.pad(hc.t(), (0, pad)).contiguous()
+        else:
+            dl_t, hc_t = dl.t().contiguous(), hc.t().contiguous()
+        _native.matmul_accumulate_f32_fwd(dl_t, hc_t, d_weight)                    # [V, r] x [H, r]^T
+    return d_hidden, d_weight.to(hidden.dtype)
+
+
+def lce_grad_scale(targets: torch.Tensor, ignore_index: int, reduction: str) -> float:
+    """d(loss)/d(loss_i): 1 for 'sum', 1 / (rows not ignored) for 'mean' (nan when all are)."""
+    if reduction not in ("mean", "sum"):
+        raise ValueError(f"reduction must be 'mean' or 'sum' for the gradient path, got {reduction!r}")
+    if reduction == "sum":
+        return 1.0
+    valid = int((targets != ignore_index).sum().item())
+    return 1.0 / valid if valid else float("nan")
+
+
+def linear_cross_entropy_fwd_bwd(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor,
+                                 ignore_index: int = IGNORE_INDEX, reduction: str = "mean",
+                                 rows_per_chunk: int = 4096, weight_t: torch.Tensor | None = None
+                                 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Loss and its gradients with respect to ``hidden`` and ``weight`` (for an upstream gradient
+    of 1) - what the reference names as its missing piece (custom_cuda/kernels/
+    linear_cross_entropy.py:11-18).  float16/bfloat16, ``H`` and ``V`` multiples of 8.
+
+    Forward: the fused kernel (logits never stored).  Backward: ``lce_gradients``.  ``weight_t``
+    may pass a cached ``weight.T.contiguous()``.  Returns ``(loss, d_hidden, d_weight)``."""
+    scale = lce_grad_scale(targets, ignore_index, reduction)
+    stats = lce_row_stats(hidden, weight, targets).unsqueeze(0)
+    loss = lce_loss_from_stats(stats, targets, ignore_index, reduction)
+    d_hidden, d_weight = lce_gradients(hidden, weight, targets, lce_lse_from_stats(stats), scale, 0, ignore_index,
+                                       rows_per_chunk, weight_t)
+    return loss, d_hidden, d_weight
+
+
+class _LinearCrossEntropyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, ignore_index, reduction, rows_per_chunk):
+        loss, d_hidden, d_weight = linear_cross_entropy_fwd_bwd(
+            hidden.detach(), weight.detach(), targets, ignore_index, reduction, rows_per_chunk)
+        ctx.save_for_backward(d_hidden, d_weight)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        d_hidden, d_weight = ctx.saved_tensors
+        return d_hidden * grad_out.to(d_hidden.dtype), d_weight * grad_out.to(d_weight.dtype), None, None, None, None
+
+
+def linear_cross_entropy_trainable(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor,
+                                   ignore_index: int = IGNORE_INDEX, reduction: str = "mean",
+                                   rows_per_chunk: int = 4096) -> torch.Tensor:
+    """``linear_cross_entropy`` with autograd support: the gradients are computed together with
+    the loss (see ``linear_cross_entropy_fwd_bwd``) and handed to autograd in ``backward``.
+    ``linear_cross_entropy`` itself stays forward-only, as in the reference."""
+    return _LinearCrossEntropyFn.apply(hidden, weight, targets, ignore_index, reduction, rows_per_chunk)

@@ -149,6 +149,22 @@ int32_t launch_matmul_add_bias_residual_fwd(const void* x, const void* weight, c
                                             const void* residual, void* y, int64_t m, int64_t k, int64_t n,
                                             int32_t dtype, void* stream);
 
+/* Backward helper of the linear cross entropy (the reference is forward-only): d(loss)/d(logits)
+ * for rows [0, n) over the whole vocabulary, dlogits[i, j] = (exp(logit_ij - lse[i]) - [j ==
+ * targets[i]]) * grad_scale, 0 for rows whose target is ignore_index, written as [n, v] in the
+ * storage type.  The logits are recomputed by the tensor-core mainloop and never stored.
+ * lse[i] = max + log(sum-exp) of row i from launch_linear_cross_entropy_fwd's row_stats.
+ * dtype CCK_BF16 or CCK_F16, h % 8 == 0, aligned operands; otherwise cudaErrorInvalidValue. */
+int32_t launch_lce_dlogits_fwd(const void* hidden, const void* weight, const int64_t* targets, const float* lse,
+                               int64_t n, int64_t h, int64_t v, int64_t ignore_index, float grad_scale,
+                               void* dlogits, int32_t dtype, void* stream);
+
+/* y[m, n] (float32) += x[m, k] @ weight[n, k]^T with 16-bit operands: a GEMM that accumulates
+ * into its output across calls (a weight gradient summed over row blocks).  k % 8 == 0,
+ * 16-byte aligned x, weight and y; otherwise cudaErrorInvalidValue. */
+int32_t launch_matmul_accumulate_f32_fwd(const void* x, const void* weight, float* y, int64_t m, int64_t k,
+                                         int64_t n, int32_t dtype, void* stream);
+
 /* Number of two-CTA pairs the tensor-core GEMM keeps resident on the current device; 0 means
  * the pair kernel is unavailable (or disabled with CCK_GEMM_SINGLE_CTA=1) and the single-CTA
  * kernel is used. */

@@ -78,6 +78,66 @@ def test_vocab_parallel_exchange_two_gloo_ranks(tmp_path):
     assert outs[0]["range"][1] == outs[1]["range"][0]
 
 
+def _grad_rank_main(rank, world, port, out_dir, scatter):
+    """The vocabulary-parallel gradient path on two gloo ranks.  The three GPU kernels it
+    calls are replaced by fp32 torch stand-ins; the target localisation, the log-sum-exp
+    merge, the gradient scale and both collectives are the library's own."""
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_from_env(timeout_s=60)
+    from custom_cuda_kernals_b200.kernels import linear_cross_entropy as lce
+
+    def row_stats(h, w, t, v_start=0, chunk_size=0):
+        return torch.stack(ops.lce_partials(h, w, t, v_start)).float()
+
+    def loss_from_stats(stats, t, ignore_index=-100, reduction="mean"):
+        per_row = ops.lce_merge([(g[0].double(), g[1].double(), g[2].double()) for g in stats])
+        keep = t != ignore_index
+        total = per_row[keep].sum()
+        return (total / keep.sum() if reduction == "mean" else total).float()
+
+    def gradients(h, w, t, lse, scale, v_start=0, ignore_index=-100, rows_per_chunk=4096, weight_t=None):
+        local = lce._local_targets(t, v_start, w.shape[0], ignore_index)
+        dl = torch.exp(h.float() @ w.float().T - lse[:, None])
+        hit = (local >= 0) & (local < w.shape[0]) & (t != ignore_index)
+        dl[hit.nonzero().squeeze(1), local[hit]] -= 1.0
+        dl = dl * scale * (t != ignore_index)[:, None]
+        return dl @ w.float(), dl.T @ h.float()
+
+    lce.lce_row_stats, lce.lce_loss_from_stats, lce.lce_gradients = row_stats, loss_from_stats, gradients
+    g = torch.Generator().manual_seed(5)
+    n, hd, v = 64, 32, 384
+    h = torch.randn(n, hd, generator=g)
+    w = 0.2 * torch.randn(v, hd, generator=g)
+    t = torch.randint(0, v, (n,), generator=g)
+    t[::7] = -100
+    t[1] = dist.vocab_range(v, 1, world)[0] - 100   # its index within shard 1 equals ignore_index: must not be ignored
+    v0, v1 = dist.vocab_range(v, rank, world)
+    loss, dh, dw = dist.vocab_parallel_linear_cross_entropy_fwd_bwd(h, w[v0:v1], t, v0, scatter_rows=scatter)
+    torch.save({"loss": loss, "dh": dh, "dw": dw, "range": (v0, v1)}, os.path.join(out_dir, f"g{rank}.pt"))
+    td.destroy_process_group()
+
+
+def test_vocab_parallel_gradients_two_gloo_ranks(tmp_path):
+    world = 2
+    mp.spawn(_grad_rank_main, args=(world, _free_port(), str(tmp_path), False), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(5)
+    n, hd, v = 64, 32, 384
+    h = torch.randn(n, hd, generator=g).requires_grad_(True)
+    w = (0.2 * torch.randn(v, hd, generator=g)).requires_grad_(True)
+    t = torch.randint(0, v, (n,), generator=g)
+    t[::7] = -100
+    t[1] = dist.vocab_range(v, 1, world)[0] - 100
+    want = torch.nn.functional.cross_entropy(h @ w.T, t, ignore_index=-100)
+    want.backward()
+    outs = [torch.load(tmp_path / f"g{r}.pt") for r in range(world)]
+    for o in outs:
+        torch.testing.assert_close(o["loss"], want.detach(), rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(o["dh"], h.grad, rtol=1e-4, atol=1e-6)       # all-reduced: whole d_hidden
+        v0, v1 = o["range"]
+        torch.testing.assert_close(o["dw"], w.grad[v0:v1], rtol=1e-4, atol=1e-6)  # own rows, no exchange
+
+
 def _rank_that_loses_its_peer(rank, world, port, out_dir):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
                       MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))

@@ -145,3 +145,44 @@ def test_lce_config5_full_size_properties():
     want = ops.linear_cross_entropy_fp64(h[pick], w, t[pick], reduction="none")
     torch.testing.assert_close(rows[pick.to(DEV)].cpu().double(), want, rtol=1e-4, atol=1e-5)
     assert device_status_clean(mean)
+
+
+def _grad_close(got, want, what):
+    got, want = got.float().cpu(), want.float().cpu()
+    scale = want.abs().max().item()
+    err = (got - want).abs()
+    assert err.max().item() <= 3e-2 * scale + 1e-9, (what, err.max().item(), scale)
+    assert (err.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()).item() <= 1e-2, what
+
+
+@pytest.mark.parametrize("shape", [(300, 256, 5000), (1000, 512, 9000), (130, 64, 264)])
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+def test_lce_gradients_match_autograd(shape, reduction):
+    """d_hidden and d_weight against torch autograd on fp32 copies of the same bf16 inputs;
+    several row chunks (rows_per_chunk 128, ragged last chunk), 20 % ignored rows."""
+    from custom_cuda_kernals_b200.kernels.linear_cross_entropy import (linear_cross_entropy_fwd_bwd,
+                                                                          linear_cross_entropy_trainable)
+    n, hdim, v = shape
+    g = torch.Generator().manual_seed(n + v)
+    h = torch.randn(n, hdim, generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(v, hdim, generator=g)).to(torch.bfloat16)
+    t = torch.randint(0, v, (n,), generator=g)
+    t[::5] = -100
+    h32 = h.float().requires_grad_(True)
+    w32 = w.float().requires_grad_(True)
+    want = torch.nn.functional.cross_entropy(h32 @ w32.T, t, ignore_index=-100, reduction=reduction)
+    want.backward()
+    loss, dh, dw = linear_cross_entropy_fwd_bwd(*to_dev(h, w, t), reduction=reduction, rows_per_chunk=128)
+    torch.testing.assert_close(loss.cpu(), want.detach(), rtol=1e-4, atol=1e-5)
+    _grad_close(dh, h32.grad, "d_hidden")
+    _grad_close(dw, w32.grad, "d_weight")
+    assert torch.all(dh[::5] == 0)                         # ignored rows get no gradient
+    # the autograd wrapper hands the same gradients to .backward(), scaled by the upstream gradient
+    hd = h.to(DEV).requires_grad_(True)
+    wd = w.to(DEV).requires_grad_(True)
+    out = linear_cross_entropy_trainable(hd, wd, t.to(DEV), reduction=reduction, rows_per_chunk=128)
+    assert out.grad_fn is not None
+    (2.0 * out).backward()
+    _grad_close(hd.grad, 2.0 * h32.grad, "autograd d_hidden")
+    _grad_close(wd.grad, 2.0 * w32.grad, "autograd d_weight")
+    assert device_status_clean(out)

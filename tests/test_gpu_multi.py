@@ -38,6 +38,20 @@ def _rank_main(rank, world, port, out_dir):
     rows = dist.vocab_parallel_linear_cross_entropy(h, w[v0:v1].contiguous(), t, v0, reduction="none")
     single = linear_cross_entropy(h, w, t)
     single_rows = linear_cross_entropy(h, w, t, reduction="none")
+    # --- vocabulary-parallel gradients: all-reduced d_hidden, own rows of d_weight
+    from custom_cuda_kernals_b200.kernels.linear_cross_entropy import linear_cross_entropy_fwd_bwd
+    hg, wg, tg = workloads.lce_bf16(tokens=512, hidden=1024, vocab=20480)
+    hg, wg, tg = hg.to(dev), wg.to(dev), tg.to(dev)
+    g0, g1 = dist.vocab_range(wg.shape[0], rank, world)
+    p_loss, p_dh, p_dw = dist.vocab_parallel_linear_cross_entropy_fwd_bwd(hg, wg[g0:g1].contiguous(), tg, g0)
+    s_loss, s_dh, s_dw = linear_cross_entropy_fwd_bwd(hg, wg, tg)
+    _, p_dh_rows, _ = dist.vocab_parallel_linear_cross_entropy_fwd_bwd(hg, wg[g0:g1].contiguous(), tg, g0, scatter_rows=True)
+    r0, r1 = dist.row_range(hg.shape[0], rank, world)
+    dh_scale = s_dh.float().abs().max()
+    grads_ok = bool(torch.allclose(p_loss, s_loss, rtol=1e-6, atol=1e-6)
+                    and (p_dh.float() - s_dh.float()).abs().max() <= 2e-2 * dh_scale
+                    and (p_dh_rows.float() - s_dh[r0:r1].float()).abs().max() <= 2e-2 * dh_scale
+                    and (p_dw.float() - s_dw[g0:g1].float()).abs().max() <= 2e-2 * s_dw.float().abs().max())
     # --- GEMM column shards written into one output
     a, wt, b = workloads.gemm_bf16(m=512, k=1024, n=2048)
     a, wt, b = a.to(dev), wt.to(dev), b.to(dev)
@@ -55,6 +69,7 @@ def _rank_main(rank, world, port, out_dir):
         full = block(x)
     torch.cuda.synchronize()
     torch.save({"loss": loss.cpu(), "single": single.cpu(), "rows_equal": bool(torch.allclose(rows, single_rows, rtol=1e-6, atol=1e-6)),
+                "grads_ok": grads_ok,
                 "gemm_equal": bool(torch.equal(y_part, y_full[:, n0:n1])),
                 "block_equal": bool(torch.equal(part, full[b0:b1]))}, os.path.join(out_dir, f"r{rank}.pt"))
     td.barrier()
@@ -68,5 +83,5 @@ def test_two_ranks_match_single_gpu(tmp_path):
     outs = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
     for o in outs:
         torch.testing.assert_close(o["loss"], o["single"], rtol=1e-6, atol=1e-6)
-        assert o["rows_equal"] and o["gemm_equal"] and o["block_equal"]
+        assert o["rows_equal"] and o["gemm_equal"] and o["block_equal"] and o["grads_ok"]
     assert torch.equal(outs[0]["loss"], outs[1]["loss"])
