@@ -384,6 +384,26 @@ def bench_ops(dev, rank, world, peaks, src):
         ch, cwv, ct = h[:256].cpu(), wv.cpu(), t[:256].cpu()
         cpu("linear_cross_entropy_bf16", 2 * 256 * 4096 * (v1 - v0), lambda: O.linear_cross_entropy(ch, cwv, ct),
             "256 of 16384 rows (eager: full logits, then cross entropy)")
+    # the same problem with gradients (no counterpart in the reference): loss, d_hidden, d_weight;
+    # three contractions are the algorithmic minimum, the rest is overhead
+    def lce_grads(hh, ww, tt):
+        return dist.vocab_parallel_linear_cross_entropy_fwd_bwd(hh, ww, tt, v0)
+
+    record("linear_cross_entropy_fwd_bwd_bf16", "tensor", 3 * 2 * 16384 * 4096 * (v1 - v0),
+           timed_loop(lce_grads, [(h, wv, t)], 3 if world == 1 else 6, warm=2), f"vocab rows {v1 - v0} of 128256")
+    if world == 1:
+        def torch_autograd(hh, ww, tt):       # eager PyTorch, rows chunked so that the logits fit
+            hg, wg = hh.detach().requires_grad_(True), ww.detach().requires_grad_(True)
+            valid = (tt != -100).sum()
+            for r0 in range(0, hg.shape[0], 2048):
+                lg = (hg[r0:r0 + 2048] @ wg.T).float()
+                (torch.nn.functional.cross_entropy(lg, tt[r0:r0 + 2048], reduction="sum") / valid).backward()
+            return hg.grad, wg.grad
+        secs = timed_loop(torch_autograd, [(h, wv, t)], 3, warm=1)
+        out["linear_cross_entropy_fwd_bwd_bf16"]["torch_autograd"] = {
+            "achieved": round(3 * 2 * 16384 * 4096 * (v1 - v0) / secs / 1e12, 2), "unit": "TFLOP/s",
+            "us_per_launch": round(secs * 1e6, 2),
+            "what": "eager PyTorch on the same GPU: cuBLAS logits per 2048-row chunk, fp32 cross entropy, autograd"}
     return out
 
 
@@ -568,7 +588,7 @@ def run_ours(args, rank, world, local):
         emit(line)
 
 
-PROFILE_CASES = ("gemm", "gemm_fp8", "lce", "swiglu", "rmsnorm", "rope", "fp8_token", "fp8_block")
+PROFILE_CASES = ("gemm", "gemm_fp8", "lce", "lce_dlogits", "swiglu", "rmsnorm", "rope", "fp8_token", "fp8_block")
 
 
 def run_profile_case(name, launches=3):
@@ -599,6 +619,13 @@ def run_profile_case(name, launches=3):
         h, w = rn(2048, 4096), rn(32064, 4096, scale=0.02)
         t = torch.randint(0, 32064, (2048,), device=dev)
         fn = lambda: linear_cross_entropy(h, w, t)
+    elif name == "lce_dlogits":  # the gradient path's bandwidth pass: 263 MB of fp32 logits in, 2 x 131 MB out
+        from custom_cuda_kernals_b200 import _native
+        lg = rn(2048, 32064, dtype=torch.float32)
+        t = torch.randint(0, 32064, (2048,), device=dev)
+        lse = torch.logsumexp(lg, dim=1)
+        dl, dl_t = torch.empty(2048, 32064, dtype=bf, device=dev), torch.empty(32064, 2048, dtype=bf, device=dev)
+        fn = lambda: _native.lce_dlogits_from_logits(lg, t, lse, -100, 1.0 / 2048, dl, dl_t)
     elif name == "swiglu":      # config 2a at 1/4 of the rows: 3 x 59 MB
         a, b = rn(2048, 14336), rn(2048, 14336)
         fn = lambda: swiglu(a, b)

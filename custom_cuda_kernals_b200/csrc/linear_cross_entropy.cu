@@ -67,13 +67,17 @@ struct SchedLce {
     };
 };
 
-struct EpiLce {
+// kStore: also write the fp32 logits tile to `logits` [N, v_count] (the gradient path reads
+// it back once instead of running the contraction a second time).
+template <bool kStore>
+struct EpiLceT {
     struct Params {
         const int64_t* targets;   // [N] global class ids (or ignore_index)
         float* partials;          // [splits][3][N]
         int64_t n_rows;
         int64_t v_count;          // rows of this weight slice
         int64_t v_start;          // global id of the slice's first row
+        float* logits;            // kStore only
     };
     struct Thread {
         float mx, sm, tg;
@@ -89,11 +93,27 @@ struct EpiLce {
             th.tgt_local = row < p.n_rows ? p.targets[row] - p.v_start : -1;
         }
     }
-    __device__ static __forceinline__ void chunk(const Params& p, Thread& th, const TileWork& w, int, int c0,
-                                                 float (&acc)[32], const float*) {
+    __device__ static __forceinline__ void chunk(const Params& p, Thread& th, const TileWork& w, int row_in_tile,
+                                                 int c0, float (&acc)[32], const float*) {
         const int64_t col0 = static_cast<int64_t>(w.n_tile) * kBN + c0;
         if (col0 >= p.v_count) return;
         const int valid = p.v_count - col0 < 32 ? static_cast<int>(p.v_count - col0) : 32;
+        if constexpr (kStore) {
+            const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+            if (row < p.n_rows) {
+                float* out = p.logits + row * p.v_count + col0;
+                if (valid == 32) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<float4*>(out + 4 * q) =
+                            make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < valid) out[j] = acc[j];
+                }
+            }
+        }
         const int64_t t_off = th.tgt_local - col0;
         if (t_off >= 0 && t_off < valid) {
 #pragma unroll
@@ -124,6 +144,8 @@ struct EpiLce {
         base[2 * p.n_rows] = th.tg;
     }
 };
+
+using EpiLce = EpiLceT<false>;
 
 // ---- backward helper: d(loss)/d(logits) for a block of rows, written in the storage type.
 //   dl[i, j] = (exp(l_ij - lse_i) - [j == target_i]) * grad_scale   (0 for ignored rows)
@@ -298,20 +320,21 @@ extern "C" int64_t cck_lce_workspace_bytes(int64_t n, int64_t v_count) {
     return cck_lce_num_splits(n, v_count) * 3 * n * static_cast<int64_t>(sizeof(float));
 }
 
-extern "C" int32_t launch_linear_cross_entropy_fwd(const void* hidden, const void* weight, const int64_t* targets,
-                                                   int64_t v_start, int64_t n, int64_t h, int64_t v_count,
-                                                   float* row_stats, void* workspace, int64_t workspace_bytes,
-                                                   int32_t dtype, void* stream) {
-    using namespace cck;
-    using namespace cck::tc;
+namespace cck {
+namespace tc {
+template <bool kStore>
+cudaError_t lce_forward(const void* hidden, const void* weight, const int64_t* targets, int64_t v_start, int64_t n,
+                        int64_t h, int64_t v_count, float* row_stats, void* workspace, int64_t workspace_bytes,
+                        float* logits, int32_t dtype, cudaStream_t s) {
+    using Epi = EpiLceT<kStore>;
     if (n <= 0 || v_count <= 0 || h <= 0) return cudaSuccess;
     if (dtype != kBF16 && dtype != kF16) return cudaErrorInvalidValue;
     if (h % 8 != 0 || !aligned16(hidden) || !aligned16(weight) || n >= (1LL << 31) || v_count >= (1LL << 31) ||
         h >= (1LL << 31))
         return cudaErrorInvalidValue;
+    if (kStore && (logits == nullptr || !aligned16(logits) || v_count % 4 != 0)) return cudaErrorInvalidValue;
     const LcePlan plan = lce_plan(n, v_count);
     if (workspace == nullptr || workspace_bytes < static_cast<int64_t>(plan.splits) * 3 * n * 4) return cudaErrorInvalidValue;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool is_bf16 = dtype == kBF16;
     const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap ta, tb;
@@ -321,18 +344,222 @@ extern "C" int32_t launch_linear_cross_entropy_fwd(const void* hidden, const voi
     if (e != cudaSuccess) return e;
     SchedLce::Params sp{plan.m_units, plan.n_tiles, plan.splits,
                         raster_group(plan.pair ? 2 * kBM : kBM, h, 2, plan.m_units)};
-    EpiLce::Params ep{targets, static_cast<float*>(workspace), n, v_count, v_start};
+    typename Epi::Params ep{targets, static_cast<float*>(workspace), n, v_count, v_start, logits};
     const int64_t units = static_cast<int64_t>(plan.m_units) * plan.splits;
     const uint32_t fmt = is_bf16 ? 1u : 0u;
     if (plan.pair) {
-        e = launch_pair<false, SchedLce, EpiLce>(ta, tb, sp, ep, h, ptx::instr_desc(fmt, fmt, 2 * kBM, kBN), units, s);
+        e = launch_pair<false, SchedLce, Epi>(ta, tb, sp, ep, h, ptx::instr_desc(fmt, fmt, 2 * kBM, kBN), units, s);
     } else {
         const int ctas = static_cast<int>(units < plan.workers ? units : plan.workers);
-        e = launch<false, SchedLce, EpiLce>(ta, tb, sp, ep, h, ptx::instr_desc(fmt, fmt, kBM, kBN), ctas, s);
+        e = launch<false, SchedLce, Epi>(ta, tb, sp, ep, h, ptx::instr_desc(fmt, fmt, kBM, kBN), ctas, s);
     }
     if (e != cudaSuccess) return e;
     lce_merge_kernel<<<static_cast<unsigned>(ceil_div64(n, 256)), 256, 0, s>>>(
         static_cast<const float*>(workspace), plan.splits, n, row_stats);
+    return cudaGetLastError();
+}
+
+// ---- d(loss)/d(logits) from stored fp32 logits, written row-major AND transposed.
+//   dl[i, j] = (exp(l_ij - lse_i) - [j == target_i]) * grad_scale   (0 for ignored rows)
+// One CTA owns a 64-row x 128-column tile.
+//   Pass 0: 64 threads put each row's (-lse * log2 e, scale) in shared memory.
+//   Pass 1: a warp walks 8 rows, a lane owns four adjacent columns (16-byte loads, all 8 in
+//           flight before the first use), stores the four rounded values to dl (8 bytes per
+//           lane) and to a shared tile in which row r sits in slot r/4 + 16 * (r % 4).
+//   Pass 1b: the one element per row that carries the "- 1" of its target column is patched
+//           by one thread per row, in dl and in the shared tile (the main loop stays free of
+//           per-row 64-bit target arithmetic).
+//   Pass 2: a lane owns one row QUAD of two adjacent columns - slots q, q + 16, q + 32, q + 48
+//           - and writes 8 bytes per column to dl_t: 16 lanes cover 128 contiguous bytes; the
+//           other half-warp works on the next column pair, which keeps the shared-memory
+//           reads (even word pitch) conflict-free.
+// HBM-bound: 4 (read) + 2 + 2 (writes) bytes per logit.
+constexpr int kDlRows = 64;
+constexpr int kDlCols = 128;
+constexpr int kDlPitchW = kDlCols / 2 + 2;   // 32-bit words per slot; even, so 8-byte stores stay aligned
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+lce_dlogits_from_logits_kernel(const float* __restrict__ logits, const int64_t* __restrict__ targets,
+                               const float* __restrict__ lse, int64_t n, int64_t v, int64_t ignore_index,
+                               float grad_scale, T* __restrict__ dl, T* __restrict__ dl_t, int64_t ld_t) {
+    __shared__ __align__(16) uint32_t tile[kDlRows * kDlPitchW];
+    __shared__ float2 row_par[kDlRows];               // (-lse * log2 e, scale)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t col0 = static_cast<int64_t>(blockIdx.x) * kDlCols;
+    const int64_t row0 = static_cast<int64_t>(blockIdx.y) * kDlRows;
+    const int64_t col = col0 + 4 * lane;
+    const bool col_ok = col < v;                      // v % 4 == 0: all four columns or none
+
+    float4 lg[8];
+    const float* src = logits + (row0 + warp * 8) * v + col;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        lg[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (row0 + warp * 8 + i < n && col_ok) {
+            const Vec16 x = ld_stream(src + i * v);
+            lg[i] = make_float4(__uint_as_float(x.w[0]), __uint_as_float(x.w[1]), __uint_as_float(x.w[2]),
+                                __uint_as_float(x.w[3]));
+        }
+    }
+    int64_t my_target = -1;                           // threads 0..63: target column of row `threadIdx.x`
+    if (threadIdx.x < kDlRows) {
+        const int64_t row = row0 + threadIdx.x;
+        float2 par = make_float2(0.0f, 0.0f);
+        if (row < n) {
+            const int64_t t = targets[row];
+            par = make_float2(-lse[row] * kLog2e, t == ignore_index ? 0.0f : grad_scale);
+            if (t != ignore_index && t >= col0 && t < col0 + kDlCols && t < v) my_target = t;
+        }
+        row_par[threadIdx.x] = par;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = warp * 8 + i;
+        const float2 par = row_par[r];
+        const float a = ex2_approx(fmaf(lg[i].x, kLog2e, par.x)) * par.y;
+        const float b = ex2_approx(fmaf(lg[i].y, kLog2e, par.x)) * par.y;
+        const float c = ex2_approx(fmaf(lg[i].z, kLog2e, par.x)) * par.y;
+        const float d = ex2_approx(fmaf(lg[i].w, kLog2e, par.x)) * par.y;
+        const uint32_t p0 = Store<T>::pack2(a, b), p1 = Store<T>::pack2(c, d);
+        if (row0 + r < n && col_ok) st_stream8(dl + (row0 + r) * v + col, p0, p1);
+        const int slot = (r >> 2) + 16 * (r & 3);
+        *reinterpret_cast<uint2*>(&tile[slot * kDlPitchW + 2 * lane]) = make_uint2(p0, p1);
+    }
+    __syncthreads();
+    if (my_target >= 0) {                             // the target column's element: (p - 1) * scale
+        const int r = threadIdx.x;
+        const float2 par = row_par[r];
+        const float l = logits[(row0 + r) * v + my_target];
+        T val;
+        Store<T>::store1(&val, (ex2_approx(fmaf(l, kLog2e, par.x)) - 1.0f) * par.y);
+        dl[(row0 + r) * v + my_target] = val;
+        const int c = static_cast<int>(my_target - col0);
+        reinterpret_cast<T*>(&tile[((r >> 2) + 16 * (r & 3)) * kDlPitchW])[c] = val;
+    }
+    __syncthreads();
+    const int quad = lane & 15, half = lane >> 4;
+    const int64_t rq = row0 + 4 * quad;               // first row of this lane's quad
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int cw = warp * 8 + 2 * i + half;       // column-pair index within the tile
+        const int64_t c = col0 + 2 * cw;
+        if (c >= v || rq >= n) continue;
+        const uint32_t w0 = tile[quad * kDlPitchW + cw], w1 = tile[(quad + 16) * kDlPitchW + cw];
+        const uint32_t w2 = tile[(quad + 32) * kDlPitchW + cw], w3 = tile[(quad + 48) * kDlPitchW + cw];
+        const uint32_t lo01 = __byte_perm(w0, w1, 0x5410), lo23 = __byte_perm(w2, w3, 0x5410);   // column c
+        const uint32_t hi01 = __byte_perm(w0, w1, 0x7632), hi23 = __byte_perm(w2, w3, 0x7632);   // column c + 1
+        T* out = dl_t + c * ld_t + rq;
+        if (rq + 4 <= n) {
+            st_stream8(out, lo01, lo23);
+            st_stream8(out + ld_t, hi01, hi23);
+        } else {
+            const uint32_t lo[2] = {lo01, lo23}, hi[2] = {hi01, hi23};
+            uint16_t* o16 = reinterpret_cast<uint16_t*>(out);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (rq + k < n) {
+                    o16[k] = static_cast<uint16_t>(lo[k >> 1] >> (16 * (k & 1)));
+                    o16[ld_t + k] = static_cast<uint16_t>(hi[k >> 1] >> (16 * (k & 1)));
+                }
+        }
+    }
+}
+
+// ---- out[c, r] = in[r, c] for 2-byte elements (any 16-bit type), out's row pitch ld_out >= rows;
+// out[c, rows..ld_out) is zero-filled.  The gradient GEMMs contract over the row index, so
+// their operands have to be row-contiguous: this makes hidden^T and W^T.  Same tiling and
+// shared-memory slot layout as lce_dlogits_from_logits_kernel (64 x 128 tile, 8-byte loads,
+// 8-byte stores in 128-byte runs).  HBM-bound: 4 bytes per element.
+__global__ void __launch_bounds__(256)
+transpose16_kernel(const uint16_t* __restrict__ in, int64_t rows, int64_t cols, uint16_t* __restrict__ out,
+                   int64_t ld_out) {
+    __shared__ __align__(16) uint32_t tile[kDlRows * kDlPitchW];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t col0 = static_cast<int64_t>(blockIdx.x) * kDlCols;
+    const int64_t row0 = static_cast<int64_t>(blockIdx.y) * kDlRows;
+    const int64_t col = col0 + 4 * lane;
+    uint2 x[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int64_t row = row0 + warp * 8 + i;
+        x[i] = make_uint2(0u, 0u);
+        if (row < rows && col < cols)
+            asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+                         : "=r"(x[i].x), "=r"(x[i].y)
+                         : "l"(in + row * cols + col));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = warp * 8 + i;
+        *reinterpret_cast<uint2*>(&tile[((r >> 2) + 16 * (r & 3)) * kDlPitchW + 2 * lane]) = x[i];
+    }
+    __syncthreads();
+    const int quad = lane & 15, half = lane >> 4;
+    const int64_t rq = row0 + 4 * quad;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int cw = warp * 8 + 2 * i + half;
+        const int64_t c = col0 + 2 * cw;
+        if (c >= cols || rq >= ld_out) continue;
+        const uint32_t w0 = tile[quad * kDlPitchW + cw], w1 = tile[(quad + 16) * kDlPitchW + cw];
+        const uint32_t w2 = tile[(quad + 32) * kDlPitchW + cw], w3 = tile[(quad + 48) * kDlPitchW + cw];
+        // rows beyond `rows` were loaded as zeros, so the padding comes out as zeros
+        uint16_t* o = out + c * ld_out + rq;
+        st_stream8(o, __byte_perm(w0, w1, 0x5410), __byte_perm(w2, w3, 0x5410));
+        st_stream8(o + ld_out, __byte_perm(w0, w1, 0x7632), __byte_perm(w2, w3, 0x7632));
+    }
+}
+}  // namespace tc
+}  // namespace cck
+
+extern "C" int32_t launch_linear_cross_entropy_fwd(const void* hidden, const void* weight, const int64_t* targets,
+                                                   int64_t v_start, int64_t n, int64_t h, int64_t v_count,
+                                                   float* row_stats, void* workspace, int64_t workspace_bytes,
+                                                   int32_t dtype, void* stream) {
+    return cck::tc::lce_forward<false>(hidden, weight, targets, v_start, n, h, v_count, row_stats, workspace,
+                                       workspace_bytes, nullptr, dtype, static_cast<cudaStream_t>(stream));
+}
+
+// The same launch that also leaves the fp32 logits in `logits` [n, v_count] (v_count % 4 == 0,
+// 16-byte aligned) for launch_lce_dlogits_from_logits.  No counterpart in the reference.
+extern "C" int32_t launch_linear_cross_entropy_fwd_store(const void* hidden, const void* weight,
+                                                         const int64_t* targets, int64_t v_start, int64_t n,
+                                                         int64_t h, int64_t v_count, float* row_stats,
+                                                         void* workspace, int64_t workspace_bytes, float* logits,
+                                                         int32_t dtype, void* stream) {
+    return cck::tc::lce_forward<true>(hidden, weight, targets, v_start, n, h, v_count, row_stats, workspace,
+                                      workspace_bytes, logits, dtype, static_cast<cudaStream_t>(stream));
+}
+
+// d(loss)/d(logits) from stored logits: dlogits [n, v] and its transpose dlogits_t [v, ld_t]
+// (ld_t >= n, a multiple of 4; columns n..ld_t of dlogits_t are not written), both in the
+// storage type.  `targets` index the columns of `logits` (a value outside [0, v) selects none);
+// v % 4 == 0.
+extern "C" int32_t launch_lce_dlogits_from_logits(const float* logits, const int64_t* targets, const float* lse,
+                                                  int64_t n, int64_t v, int64_t ignore_index, float grad_scale,
+                                                  void* dlogits, void* dlogits_t, int64_t ld_t, int32_t dtype,
+                                                  void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (n <= 0 || v <= 0) return cudaSuccess;
+    if (dtype != kBF16 && dtype != kF16) return cudaErrorInvalidValue;
+    if (v % 4 != 0 || ld_t < n || ld_t % 4 != 0 || !aligned16(logits) || (reinterpret_cast<uintptr_t>(dlogits) & 7u) ||
+        (reinterpret_cast<uintptr_t>(dlogits_t) & 7u))
+        return cudaErrorInvalidValue;
+    const int64_t gx = ceil_div64(v, kDlCols), gy = ceil_div64(n, kDlRows);
+    if (gy > 65535) return cudaErrorInvalidValue;
+    const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == kBF16)
+        lce_dlogits_from_logits_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+            logits, targets, lse, n, v, ignore_index, grad_scale, static_cast<__nv_bfloat16*>(dlogits),
+            static_cast<__nv_bfloat16*>(dlogits_t), ld_t);
+    else
+        lce_dlogits_from_logits_kernel<__half><<<grid, 256, 0, s>>>(
+            logits, targets, lse, n, v, ignore_index, grad_scale, static_cast<__half*>(dlogits),
+            static_cast<__half*>(dlogits_t), ld_t);
     return cudaGetLastError();
 }
 
@@ -441,4 +668,23 @@ extern "C" int32_t launch_lce_dlogits_fwd(const void* hidden, const void* weight
                                              static_cast<int>(tiles < sm_count() ? tiles : sm_count()), s);
     };
     return dtype == kBF16 ? run(__nv_bfloat16{}) : run(__half{});
+}
+
+// out[c, r] = in[r, c] for a contiguous [rows, cols] matrix of 2-byte elements; out is
+// [cols, ld_out] with ld_out >= rows, and out[:, rows..ld_out) is set to zero.  cols % 4 == 0,
+// ld_out % 4 == 0, both pointers 8-byte aligned.  No counterpart in the reference.
+extern "C" int32_t launch_transpose_2byte(const void* in, int64_t rows, int64_t cols, void* out, int64_t ld_out,
+                                          void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (rows <= 0 || cols <= 0) return cudaSuccess;
+    if (cols % 4 != 0 || ld_out < rows || ld_out % 4 != 0 || (reinterpret_cast<uintptr_t>(in) & 7u) ||
+        (reinterpret_cast<uintptr_t>(out) & 7u))
+        return cudaErrorInvalidValue;
+    const int64_t gx = ceil_div64(cols, kDlCols), gy = ceil_div64(ld_out, kDlRows);
+    if (gy > 65535) return cudaErrorInvalidValue;
+    transpose16_kernel<<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(gy)), 256, 0,
+                         static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(in), rows, cols,
+                                                              static_cast<uint16_t*>(out), ld_out);
+    return cudaGetLastError();
 }

@@ -468,7 +468,8 @@ void linear_ce_chunk_update(const at::Tensor& logits_chunk, const at::Tensor& ta
 
 // fused path (no counterpart in the reference)
 void linear_cross_entropy_fwd(const at::Tensor& hidden, const at::Tensor& weight, const at::Tensor& targets,
-                              int64_t v_start, const at::Tensor& row_stats, const at::Tensor& workspace) {
+                              int64_t v_start, const at::Tensor& row_stats, const at::Tensor& workspace,
+                              const c10::optional<at::Tensor>& logits) {
     const int32_t dt = tag_of("hidden", hidden);
     if (dt != CCK_BF16 && dt != CCK_F16)
         value_error(std::string("unsupported dtype '") + tag_name(dt) + "' for the fused path; expected float16 or bfloat16");
@@ -492,6 +493,22 @@ void linear_cross_entropy_fwd(const at::Tensor& hidden, const at::Tensor& weight
     if (ws_bytes < cck_lce_workspace_bytes(n, v))
         value_error("shape mismatch: workspace has " + std::to_string(ws_bytes) + " bytes, needs " +
                     std::to_string(cck_lce_workspace_bytes(n, v)));
+    if (logits.has_value()) {      // gradient path: also keep the fp32 logits
+        const at::Tensor& lg = *logits;
+        expect_f32("logits", tag_of("logits", lg));
+        if (lg.dim() != 2 || lg.size(0) != n || lg.size(1) != v)
+            value_error("shape mismatch: logits shape " + shape_str(lg) + " must be [" + std::to_string(n) + ", " +
+                        std::to_string(v) + "]");
+        if (v % 4 != 0) value_error("shape mismatch: storing the logits needs a vocabulary size that is a multiple of 4");
+        Launch l(hidden, {&weight, &targets, &row_stats, &workspace, &lg});
+        check_launch("launch_linear_cross_entropy_fwd_store",
+                     launch_linear_cross_entropy_fwd_store(hidden.data_ptr(), weight.data_ptr(),
+                                                           static_cast<const int64_t*>(targets.data_ptr()), v_start, n,
+                                                           h, v, static_cast<float*>(row_stats.data_ptr()),
+                                                           workspace.data_ptr(), ws_bytes,
+                                                           static_cast<float*>(lg.data_ptr()), dt, l.stream));
+        return;
+    }
     Launch l(hidden, {&weight, &targets, &row_stats, &workspace});
     check_launch("launch_linear_cross_entropy_fwd",
                  launch_linear_cross_entropy_fwd(hidden.data_ptr(), weight.data_ptr(),
@@ -523,6 +540,49 @@ void lce_dlogits_fwd(const at::Tensor& hidden, const at::Tensor& weight, const a
                  launch_lce_dlogits_fwd(hidden.data_ptr(), weight.data_ptr(), static_cast<const int64_t*>(targets.data_ptr()),
                                         static_cast<const float*>(lse.data_ptr()), n, h, v, ignore_index,
                                         static_cast<float>(grad_scale), dlogits.data_ptr(), dt, l.stream));
+}
+
+void lce_dlogits_from_logits(const at::Tensor& logits, const at::Tensor& targets, const at::Tensor& lse,
+                             int64_t ignore_index, double grad_scale, const at::Tensor& dlogits,
+                             const at::Tensor& dlogits_t) {
+    expect_f32("logits", tag_of("logits", logits));
+    expect_f32("lse", tag_of("lse", lse));
+    expect_int("targets", targets, at::kLong, "int64");
+    const int32_t dt = tag_of("dlogits", dlogits);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
+    expect_same_dtype("dlogits_t", tag_of("dlogits_t", dlogits_t), dt);
+    if (logits.dim() != 2) value_error("shape mismatch: logits must be 2-D; got " + shape_str(logits));
+    const int64_t n = logits.size(0), v = logits.size(1);
+    if (targets.numel() != n || lse.numel() != n)
+        value_error("shape mismatch: targets and lse must have " + std::to_string(n) + " elements");
+    if (dlogits.dim() != 2 || dlogits.size(0) != n || dlogits.size(1) != v)
+        value_error("shape mismatch: dlogits shape " + shape_str(dlogits) + " must be " + shape_str(logits));
+    if (dlogits_t.dim() != 2 || dlogits_t.size(0) != v || dlogits_t.size(1) < n || dlogits_t.size(1) % 4 != 0)
+        value_error("shape mismatch: dlogits_t shape " + shape_str(dlogits_t) + " must be [" + std::to_string(v) +
+                    ", >= " + std::to_string(n) + " and a multiple of 4]");
+    if (v % 4 != 0) value_error("shape mismatch: the vocabulary size must be a multiple of 4");
+    Launch l(logits, {&targets, &lse, &dlogits, &dlogits_t});
+    check_launch("launch_lce_dlogits_from_logits",
+                 launch_lce_dlogits_from_logits(static_cast<const float*>(logits.data_ptr()),
+                                                static_cast<const int64_t*>(targets.data_ptr()),
+                                                static_cast<const float*>(lse.data_ptr()), n, v, ignore_index,
+                                                static_cast<float>(grad_scale), dlogits.data_ptr(),
+                                                dlogits_t.data_ptr(), dlogits_t.size(1), dt, l.stream));
+}
+
+void transpose_2byte(const at::Tensor& in, const at::Tensor& out) {
+    const int32_t dt = tag_of("in", in);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
+    expect_same_dtype("out", tag_of("out", out), dt);
+    if (in.dim() != 2 || out.dim() != 2 || out.size(0) != in.size(1) || out.size(1) < in.size(0))
+        value_error("shape mismatch: in [R, C] and out [C, >= R] expected; got in=" + shape_str(in) + ", out=" + shape_str(out));
+    if (in.size(1) % 4 != 0 || out.size(1) % 4 != 0)
+        value_error("shape mismatch: in's columns and out's row length must be multiples of 4");
+    Launch l(in, {&out});
+    check_launch("launch_transpose_2byte",
+                 launch_transpose_2byte(in.data_ptr(), in.size(0), in.size(1), out.data_ptr(), out.size(1), l.stream));
 }
 
 void matmul_accumulate_f32_fwd(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& y) {
@@ -607,9 +667,13 @@ PYBIND11_MODULE(_native, m) {
     m.def("matmul_add_bias_residual_fwd", &matmul_add_bias_residual_fwd, py::arg("x"), py::arg("weight"),
           py::arg("bias").none(true), py::arg("residual"), py::arg("y"));
     m.def("linear_cross_entropy_fwd", &linear_cross_entropy_fwd, py::arg("hidden"), py::arg("weight"),
-          py::arg("targets"), py::arg("v_start"), py::arg("row_stats"), py::arg("workspace"));
+          py::arg("targets"), py::arg("v_start"), py::arg("row_stats"), py::arg("workspace"),
+          py::arg("logits") = py::none());
+    m.def("lce_dlogits_from_logits", &lce_dlogits_from_logits, py::arg("logits"), py::arg("targets"), py::arg("lse"),
+          py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"), py::arg("dlogits_t"));
     m.def("lce_dlogits_fwd", &lce_dlogits_fwd, py::arg("hidden"), py::arg("weight"), py::arg("targets"), py::arg("lse"),
           py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"));
+    m.def("transpose_2byte", &transpose_2byte, py::arg("input"), py::arg("out"));
     m.def("matmul_accumulate_f32_fwd", &matmul_accumulate_f32_fwd, py::arg("x"), py::arg("weight"), py::arg("y"));
     m.def("lce_workspace_bytes", &lce_workspace_bytes, py::arg("like"), py::arg("n"), py::arg("v_count"));
     m.def("lce_finalize", &lce_finalize, py::arg("stats"), py::arg("targets"), py::arg("ignore_index"),

@@ -117,22 +117,22 @@ def vocab_parallel_linear_cross_entropy(hidden: torch.Tensor, weight_shard: torc
 
 def vocab_parallel_linear_cross_entropy_fwd_bwd(hidden: torch.Tensor, weight_shard: torch.Tensor,
                                                 targets: torch.Tensor, v_start: int, ignore_index: int = -100,
-                                                reduction: str = "mean", rows_per_chunk: int = 4096,
+                                                reduction: str = "mean", rows_per_chunk: int = 8192,
                                                 scatter_rows: bool = False, group=None
                                                 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Loss, ``d_hidden`` and this rank's ``d_weight`` rows for a vocabulary-sharded LM head.
 
-    Two collectives: the ``[3, N]`` all-gather of the forward, and one reduction of the
-    per-shard ``d_hidden`` contributions - an all-reduce, or with ``scatter_rows`` (``N``
-    divisible by the world size) a reduce-scatter that leaves each rank with its
-    ``row_range`` of ``d_hidden``.  ``d_weight`` needs no exchange: every rank owns its rows."""
-    from .kernels.linear_cross_entropy import (lce_grad_scale, lce_gradients, lce_loss_from_stats,
-                                               lce_lse_from_stats, lce_row_stats)
-    scale = lce_grad_scale(targets, ignore_index, reduction)
-    stats = gather_row_stats(lce_row_stats(hidden, weight_shard, targets, v_start), group)
-    loss = lce_loss_from_stats(stats, targets, ignore_index, reduction)
-    d_hidden, d_weight = lce_gradients(hidden, weight_shard, targets, lce_lse_from_stats(stats), scale, v_start,
-                                       ignore_index, rows_per_chunk)
+    Collectives: the ``[3, rows]`` statistics all-gather of the forward (one per row chunk),
+    and one reduction of the per-shard ``d_hidden`` contributions - an all-reduce, or with
+    ``scatter_rows`` (``N`` divisible by the world size) a reduce-scatter that leaves each rank
+    with its ``row_range`` of ``d_hidden``.  ``d_weight`` needs no exchange: every rank owns its
+    rows."""
+    from .kernels import linear_cross_entropy as lce
+    scale = lce.lce_grad_scale(targets, ignore_index, reduction)
+    stats, d_hidden, d_weight = lce.lce_stats_and_gradients(
+        hidden, weight_shard, targets, scale, v_start, ignore_index, rows_per_chunk,
+        gather=lambda st: gather_row_stats(st, group))
+    loss = lce.lce_loss_from_stats(stats, targets, ignore_index, reduction)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         world = dist.get_world_size(group)
         if scatter_rows:

@@ -15,7 +15,7 @@ import torch
 
 from .. import _native
 
-__all__ = ["linear_cross_entropy", "lce_row_stats", "lce_loss_from_stats", "linear_cross_entropy_fwd_bwd", "lce_gradients", "lce_lse_from_stats", "lce_grad_scale",
+__all__ = ["linear_cross_entropy", "lce_row_stats", "lce_loss_from_stats", "linear_cross_entropy_fwd_bwd", "lce_stats_and_gradients", "lce_lse_from_stats", "lce_grad_scale",
            "linear_cross_entropy_trainable", "DEFAULT_CHUNK_SIZE"]
 
 DEFAULT_CHUNK_SIZE = 4096
@@ -113,44 +113,6 @@ def _local_targets(targets: torch.Tensor, v_start: int, v: int, ignore_index: in
     return torch.where(targets == ignore_index, targets, local).contiguous()
 
 
-def lce_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor,
-                  grad_scale: float, v_start: int = 0, ignore_index: int = IGNORE_INDEX,
-                  rows_per_chunk: int = 4096, weight_t: torch.Tensor | None = None
-                  ) -> tuple[torch.Tensor, torch.Tensor]:
-    """Gradients of ``grad_scale * sum_i loss_i`` for the vocabulary rows ``weight`` holds
-    (``v_start ...`` of the LM head): ``d_weight`` for those rows, and this shard's
-    contribution to ``d_hidden`` (the whole ``d_hidden`` when ``weight`` is the whole head).
-
-    ``rows_per_chunk`` rows at a time: the logits of the chunk are recomputed on the tensor
-    cores and turned into ``dlogits = (exp(logit - lse) - onehot) * grad_scale`` in the
-    epilogue (``[rows, V]`` in the storage type - the only logits-sized buffer), then
-    ``d_hidden = dlogits @ W`` and ``d_weight += dlogits^T @ hidden`` run on the same GEMM
-    engine, ``d_weight`` accumulating in fp32 across chunks."""
-    n, h = hidden.shape
-    v = weight.shape[0]
-    if not (_fused_ok(hidden, weight) and hidden.is_cuda) or v % 8 != 0:
-        raise ValueError("the gradient path needs float16/bfloat16 CUDA inputs with H and V multiples of 8")
-    local = _local_targets(targets, v_start, v, ignore_index)
-    w_t = weight_t if weight_t is not None else weight.t().contiguous()          # [H, V]
-    d_hidden = torch.empty_like(hidden)
-    d_weight = torch.zeros(v, h, dtype=torch.float32, device=hidden.device)
-    for r0 in range(0, n, rows_per_chunk):
-        r1 = min(n, r0 + rows_per_chunk)
-        rows = r1 - r0
-        hc = hidden[r0:r1]
-        dl = torch.empty(rows, v, dtype=hidden.dtype, device=hidden.device)
-        _native.lce_dlogits_fwd(hc, weight, local[r0:r1], lse[r0:r1], ignore_index, grad_scale, dl)
-        _native.matmul_add_bias_fwd(dl, w_t, None, d_hidden[r0:r1])                # [r, V] x [H, V]^T
-        if rows % 8:       # K of the weight-gradient GEMM is the row count: pad it to a multiple of 8
-            pad = 8 - rows % 8
-            dl_t = torch.nn.functional.pad(dl.t(), (0, pad)).contiguous()
-            hc_t = torch.nn.functional.pad(hc.t(), (0, pad)).contiguous()
-        else:
-            dl_t, hc_t = dl.t().contiguous(), hc.t().contiguous()
-        _native.matmul_accumulate_f32_fwd(dl_t, hc_t, d_weight)                    # [V, r] x [H, r]^T
-    return d_hidden, d_weight.to(hidden.dtype)
-
-
 def lce_grad_scale(targets: torch.Tensor, ignore_index: int, reduction: str) -> float:
     """d(loss)/d(loss_i): 1 for 'sum', 1 / (rows not ignored) for 'mean' (nan when all are)."""
     if reduction not in ("mean", "sum"):
@@ -161,22 +123,95 @@ def lce_grad_scale(targets: torch.Tensor, ignore_index: int, reduction: str) -> 
     return 1.0 / valid if valid else float("nan")
 
 
+def _padded_transpose(x: torch.Tensor, width: int | None = None) -> torch.Tensor:
+    """``x.T`` as a contiguous ``[cols, width]`` tensor (``width >= rows``, a multiple of 4),
+    zero-filled beyond ``x``'s rows."""
+    rows, cols = x.shape
+    width = rows if width is None else width
+    out = torch.empty(cols, width, dtype=x.dtype, device=x.device)
+    if cols % 4 == 0 and width % 4 == 0 and x.is_contiguous():
+        _native.transpose_2byte(x, out)
+    else:
+        out[:, :rows] = x.t()
+        out[:, rows:] = 0
+    return out
+
+
+def lce_stats_and_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, grad_scale: float,
+                            v_start: int = 0, ignore_index: int = IGNORE_INDEX, rows_per_chunk: int = 8192,
+                            weight_t: torch.Tensor | None = None, gather=None, recompute: bool = False
+                            ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Forward statistics and gradients of ``grad_scale * sum_i loss_i`` for the vocabulary
+    rows ``weight`` holds (``v_start ...`` of the LM head), ``rows_per_chunk`` rows at a time:
+
+    1. the fused forward kernel, which here also leaves the chunk's fp32 logits in a scratch
+       buffer ``[rows, V]`` (with ``recompute`` it does not, and step 2 runs the contraction a
+       second time instead - no fp32 buffer, one more GEMM);
+    2. ``gather`` (the statistics all-gather of a vocabulary-sharded run) and the row-wise
+       log-sum-exp; ``dlogits = (exp(logit - lse) - onehot) * grad_scale`` written in the storage
+       type, row-major and transposed, by one bandwidth-bound pass over the logits;
+    3. ``d_hidden[chunk] = dlogits @ W`` and ``d_weight += dlogits^T @ hidden[chunk]`` on the
+       tcgen05 GEMM (fp32 accumulation across chunks; written directly when one chunk covers
+       all rows).
+
+    Returns ``(stats [shards, 3, N], d_hidden - this shard's contribution, d_weight)``."""
+    n, h = hidden.shape
+    v = weight.shape[0]
+    if not (_fused_ok(hidden, weight) and hidden.is_cuda) or v % 8 != 0:
+        raise ValueError("the gradient path needs float16/bfloat16 CUDA inputs with H and V multiples of 8")
+    dev, dt = hidden.device, hidden.dtype
+    local = _local_targets(targets, v_start, v, ignore_index)
+    w_t = weight_t if weight_t is not None else _padded_transpose(weight)             # [H, V]
+    d_hidden = torch.empty_like(hidden)
+    one_chunk = n <= rows_per_chunk
+    d_weight = torch.empty(v, h, dtype=dt, device=dev) if one_chunk else torch.zeros(v, h, dtype=torch.float32, device=dev)
+    rows_max = min(n, rows_per_chunk)
+    logits = None if recompute else torch.empty(rows_max, v, dtype=torch.float32, device=dev)
+    dl_buf = torch.empty(rows_max, v, dtype=dt, device=dev)
+    stats_parts = []
+    for r0 in range(0, n, rows_per_chunk):
+        r1 = min(n, r0 + rows_per_chunk)
+        rows = r1 - r0
+        width = (rows + 7) // 8 * 8             # K of the weight-gradient GEMM, a multiple of 8
+        hc, tc = hidden[r0:r1], targets[r0:r1]
+        dl = dl_buf[:rows]
+        stats = torch.empty(3, rows, dtype=torch.float32, device=dev)
+        ws = torch.empty(max(1, _native.lce_workspace_bytes(hidden, rows, v)), dtype=torch.uint8, device=dev)
+        _native.linear_cross_entropy_fwd(hc, weight, tc, v_start, stats, ws, None if recompute else logits[:rows])
+        stats = gather(stats) if gather is not None else stats.unsqueeze(0)
+        stats_parts.append(stats)
+        lse = lce_lse_from_stats(stats)
+        if recompute:
+            _native.lce_dlogits_fwd(hc, weight, local[r0:r1], lse, ignore_index, grad_scale, dl)
+            dl_t = _padded_transpose(dl, width)
+        else:
+            dl_t = (torch.empty if width == rows else torch.zeros)(v, width, dtype=dt, device=dev)
+            _native.lce_dlogits_from_logits(logits[:rows], local[r0:r1], lse, ignore_index, grad_scale, dl, dl_t)
+        _native.matmul_add_bias_fwd(dl, w_t, None, d_hidden[r0:r1])                # [r, V] x [H, V]^T
+        hc_t = _padded_transpose(hc, width)
+        if one_chunk:
+            _native.matmul_add_bias_fwd(dl_t, hc_t, None, d_weight)                # [V, r] x [H, r]^T
+        else:
+            _native.matmul_accumulate_f32_fwd(dl_t, hc_t, d_weight)
+    stats_all = stats_parts[0] if one_chunk else torch.cat(stats_parts, dim=2)
+    return stats_all, d_hidden, d_weight if one_chunk else d_weight.to(dt)
+
+
 def linear_cross_entropy_fwd_bwd(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor,
                                  ignore_index: int = IGNORE_INDEX, reduction: str = "mean",
-                                 rows_per_chunk: int = 4096, weight_t: torch.Tensor | None = None
-                                 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                                 rows_per_chunk: int = 8192, weight_t: torch.Tensor | None = None,
+                                 recompute: bool = False) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Loss and its gradients with respect to ``hidden`` and ``weight`` (for an upstream gradient
     of 1) - what the reference names as its missing piece (custom_cuda/kernels/
     linear_cross_entropy.py:11-18).  float16/bfloat16, ``H`` and ``V`` multiples of 8.
 
-    Forward: the fused kernel (logits never stored).  Backward: ``lce_gradients``.  ``weight_t``
-    may pass a cached ``weight.T.contiguous()``.  Returns ``(loss, d_hidden, d_weight)``."""
+    See ``lce_stats_and_gradients``; scratch memory is ``rows_per_chunk * V * 8`` bytes (fp32
+    logits, dlogits and its transpose), ``* 4`` with ``recompute``.  ``weight_t`` may pass a
+    cached ``weight.T.contiguous()``.  Returns ``(loss, d_hidden, d_weight)``."""
     scale = lce_grad_scale(targets, ignore_index, reduction)
-    stats = lce_row_stats(hidden, weight, targets).unsqueeze(0)
-    loss = lce_loss_from_stats(stats, targets, ignore_index, reduction)
-    d_hidden, d_weight = lce_gradients(hidden, weight, targets, lce_lse_from_stats(stats), scale, 0, ignore_index,
-                                       rows_per_chunk, weight_t)
-    return loss, d_hidden, d_weight
+    stats, d_hidden, d_weight = lce_stats_and_gradients(hidden, weight, targets, scale, 0, ignore_index,
+                                                        rows_per_chunk, weight_t, None, recompute)
+    return lce_loss_from_stats(stats, targets, ignore_index, reduction), d_hidden, d_weight
 
 
 class _LinearCrossEntropyFn(torch.autograd.Function):
@@ -195,7 +230,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
 
 def linear_cross_entropy_trainable(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor,
                                    ignore_index: int = IGNORE_INDEX, reduction: str = "mean",
-                                   rows_per_chunk: int = 4096) -> torch.Tensor:
+                                   rows_per_chunk: int = 8192) -> torch.Tensor:
     """``linear_cross_entropy`` with autograd support: the gradients are computed together with
     the loss (see ``linear_cross_entropy_fwd_bwd``) and handed to autograd in ``backward``.
     ``linear_cross_entropy`` itself stays forward-only, as in the reference."""

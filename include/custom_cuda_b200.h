@@ -159,6 +159,30 @@ int32_t launch_lce_dlogits_fwd(const void* hidden, const void* weight, const int
                                int64_t n, int64_t h, int64_t v, int64_t ignore_index, float grad_scale,
                                void* dlogits, int32_t dtype, void* stream);
 
+/* launch_linear_cross_entropy_fwd that also leaves the fp32 logits in logits[n, v_count]
+ * (v_count % 4 == 0, 16-byte aligned) for launch_lce_dlogits_from_logits - the gradient path
+ * then reads them once instead of running the contraction a second time.  No reference
+ * counterpart. */
+int32_t launch_linear_cross_entropy_fwd_store(const void* hidden, const void* weight, const int64_t* targets,
+                                              int64_t v_start, int64_t n, int64_t h, int64_t v_count,
+                                              float* row_stats, void* workspace, int64_t workspace_bytes,
+                                              float* logits, int32_t dtype, void* stream);
+
+/* d(loss)/d(logits) from stored fp32 logits[n, v] (formula of launch_lce_dlogits_fwd), written
+ * both as dlogits[n, v] and transposed as dlogits_t[v, ld_t] (ld_t >= n, a multiple of 4; columns
+ * n..ld_t are left untouched) in the storage type `dtype` (CCK_BF16 / CCK_F16).  targets index
+ * the columns of logits; a value outside [0, v) selects none.  v % 4 == 0; logits 16-byte,
+ * dlogits and dlogits_t 8-byte aligned.  No reference counterpart. */
+int32_t launch_lce_dlogits_from_logits(const float* logits, const int64_t* targets, const float* lse, int64_t n,
+                                       int64_t v, int64_t ignore_index, float grad_scale, void* dlogits,
+                                       void* dlogits_t, int64_t ld_t, int32_t dtype, void* stream);
+
+/* out[c, r] = in[r, c] for a contiguous [rows, cols] matrix of 2-byte elements (float16 or
+ * bfloat16); out is [cols, ld_out], ld_out >= rows, and out[:, rows..ld_out) is zero-filled.
+ * cols % 4 == 0, ld_out % 4 == 0, 8-byte aligned pointers.  Makes the row-contiguous operands
+ * (hidden^T, W^T) of the gradient GEMMs.  No reference counterpart. */
+int32_t launch_transpose_2byte(const void* in, int64_t rows, int64_t cols, void* out, int64_t ld_out, void* stream);
+
 /* y[m, n] (float32) += x[m, k] @ weight[n, k]^T with 16-bit operands: a GEMM that accumulates
  * into its output across calls (a weight gradient summed over row blocks).  k % 8 == 0,
  * 16-byte aligned x, weight and y; otherwise cudaErrorInvalidValue. */

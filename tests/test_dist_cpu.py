@@ -87,24 +87,24 @@ def _grad_rank_main(rank, world, port, out_dir, scatter):
     dist.init_from_env(timeout_s=60)
     from custom_cuda_kernals_b200.kernels import linear_cross_entropy as lce
 
-    def row_stats(h, w, t, v_start=0, chunk_size=0):
-        return torch.stack(ops.lce_partials(h, w, t, v_start)).float()
-
     def loss_from_stats(stats, t, ignore_index=-100, reduction="mean"):
         per_row = ops.lce_merge([(g[0].double(), g[1].double(), g[2].double()) for g in stats])
         keep = t != ignore_index
         total = per_row[keep].sum()
         return (total / keep.sum() if reduction == "mean" else total).float()
 
-    def gradients(h, w, t, lse, scale, v_start=0, ignore_index=-100, rows_per_chunk=4096, weight_t=None):
+    def stats_and_gradients(h, w, t, scale, v_start=0, ignore_index=-100, rows_per_chunk=8192, weight_t=None,
+                            gather=None, recompute=False):
+        stats = gather(torch.stack(ops.lce_partials(h, w, t, v_start)).float())
+        lse = lce.lce_lse_from_stats(stats)
         local = lce._local_targets(t, v_start, w.shape[0], ignore_index)
         dl = torch.exp(h.float() @ w.float().T - lse[:, None])
         hit = (local >= 0) & (local < w.shape[0]) & (t != ignore_index)
         dl[hit.nonzero().squeeze(1), local[hit]] -= 1.0
         dl = dl * scale * (t != ignore_index)[:, None]
-        return dl @ w.float(), dl.T @ h.float()
+        return stats, dl @ w.float(), dl.T @ h.float()
 
-    lce.lce_row_stats, lce.lce_loss_from_stats, lce.lce_gradients = row_stats, loss_from_stats, gradients
+    lce.lce_loss_from_stats, lce.lce_stats_and_gradients = loss_from_stats, stats_and_gradients
     g = torch.Generator().manual_seed(5)
     n, hd, v = 64, 32, 384
     h = torch.randn(n, hd, generator=g)

@@ -155,11 +155,16 @@ def _grad_close(got, want, what):
     assert (err.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()).item() <= 1e-2, what
 
 
-@pytest.mark.parametrize("shape", [(300, 256, 5000), (1000, 512, 9000), (130, 64, 264)])
+@pytest.mark.parametrize("shape", [(300, 256, 5000), (1000, 512, 9000), (130, 64, 264), (77, 64, 1000)])
 @pytest.mark.parametrize("reduction", ["mean", "sum"])
-def test_lce_gradients_match_autograd(shape, reduction):
-    """d_hidden and d_weight against torch autograd on fp32 copies of the same bf16 inputs;
-    several row chunks (rows_per_chunk 128, ragged last chunk), 20 % ignored rows."""
+@pytest.mark.parametrize("mode", ["chunks", "one_chunk", "recompute"])
+def test_lce_gradients_match_autograd(shape, reduction, mode):
+    """d_hidden and d_weight against torch autograd on fp32 copies of the same bf16 inputs:
+    several row chunks (128 rows each, ragged last chunk), one chunk over all rows (a row count
+    that is not a multiple of 8 among them), and the variant that recomputes the logits
+    instead of storing them; 20 % ignored rows."""
+    kw = {"chunks": dict(rows_per_chunk=128), "one_chunk": dict(rows_per_chunk=8192),
+          "recompute": dict(rows_per_chunk=128, recompute=True)}[mode]
     from custom_cuda_kernals_b200.kernels.linear_cross_entropy import (linear_cross_entropy_fwd_bwd,
                                                                           linear_cross_entropy_trainable)
     n, hdim, v = shape
@@ -172,7 +177,7 @@ def test_lce_gradients_match_autograd(shape, reduction):
     w32 = w.float().requires_grad_(True)
     want = torch.nn.functional.cross_entropy(h32 @ w32.T, t, ignore_index=-100, reduction=reduction)
     want.backward()
-    loss, dh, dw = linear_cross_entropy_fwd_bwd(*to_dev(h, w, t), reduction=reduction, rows_per_chunk=128)
+    loss, dh, dw = linear_cross_entropy_fwd_bwd(*to_dev(h, w, t), reduction=reduction, **kw)
     torch.testing.assert_close(loss.cpu(), want.detach(), rtol=1e-4, atol=1e-5)
     _grad_close(dh, h32.grad, "d_hidden")
     _grad_close(dw, w32.grad, "d_weight")
@@ -186,3 +191,41 @@ def test_lce_gradients_match_autograd(shape, reduction):
     _grad_close(hd.grad, 2.0 * h32.grad, "autograd d_hidden")
     _grad_close(wd.grad, 2.0 * w32.grad, "autograd d_weight")
     assert device_status_clean(out)
+
+
+@pytest.mark.parametrize("n,v", [(64, 64), (200, 1000), (77, 332), (1, 8), (513, 4100)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dlogits_from_logits_row_major_and_transposed(n, v, dtype):
+    """The bandwidth pass alone: both layouts hold the same values, and they are the rounded
+    (softmax - onehot) * scale of the stored logits; padding columns of the transpose stay
+    untouched; ragged tiles in both directions."""
+    from custom_cuda_kernals_b200 import _native
+    g = torch.Generator().manual_seed(n * 7 + v)
+    logits = 3.0 * torch.randn(n, v, generator=g)
+    t = torch.randint(0, v, (n,), generator=g)
+    t[::4] = -100
+    if n > 2:
+        t[2] = -1                                            # matches no column, row still counted
+    lse = torch.logsumexp(logits, dim=1)
+    width = (n + 7) // 8 * 8
+    dl = torch.empty(n, v, dtype=dtype, device=DEV)
+    dl_t = torch.full((v, width), 7.0, dtype=dtype, device=DEV)
+    _native.lce_dlogits_from_logits(logits.to(DEV), t.to(DEV), lse.to(DEV), -100, 0.25, dl, dl_t)
+    want = torch.exp(logits - lse[:, None])
+    hit = t >= 0
+    want[hit.nonzero().squeeze(1), t[hit]] -= 1.0
+    want = want * 0.25 * (t != -100)[:, None]
+    torch.testing.assert_close(dl.float().cpu(), want, rtol=2 ** -8 if dtype == torch.bfloat16 else 2 ** -10, atol=1e-6)
+    assert torch.equal(dl_t[:, :n].cpu(), dl.t().cpu())
+    assert torch.all(dl_t[:, n:] == 7.0)
+
+
+@pytest.mark.parametrize("rows,cols,width", [(64, 128, 64), (77, 332, 80), (1, 4, 4), (1000, 4096, 1000), (130, 260, 136)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_transpose_2byte_is_exact_and_zero_pads(rows, cols, width, dtype):
+    from custom_cuda_kernals_b200 import _native
+    x = torch.randn(rows, cols, generator=torch.Generator().manual_seed(rows + cols)).to(dtype).to(DEV)
+    out = torch.full((cols, width), 3.0, dtype=dtype, device=DEV)
+    _native.transpose_2byte(x, out)
+    assert torch.equal(out[:, :rows], x.t())
+    assert torch.all(out[:, rows:] == 0)
