@@ -178,6 +178,68 @@ void swiglu_fwd(const at::Tensor& gate, const at::Tensor& up, const at::Tensor& 
                  launch_swiglu_fwd(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.numel(), dt, l.stream));
 }
 
+// gradients of the two ops above (no counterpart in the reference)
+void swiglu_bwd(const at::Tensor& gate, const at::Tensor& up, const at::Tensor& dy, const at::Tensor& dgate,
+                const at::Tensor& dup) {
+    const int32_t dt = tag_of("gate", gate);
+    expect_float_input("gate", dt);
+    expect_same_dtype("up", tag_of("up", up), dt);
+    expect_same_dtype("dy", tag_of("dy", dy), dt);
+    expect_same_dtype("dgate", tag_of("dgate", dgate), dt);
+    expect_same_dtype("dup", tag_of("dup", dup), dt);
+    if (up.sizes() != gate.sizes() || dy.sizes() != gate.sizes() || dgate.sizes() != gate.sizes() ||
+        dup.sizes() != gate.sizes())
+        value_error("shape mismatch: gate/up/dy/dgate/dup must share the same shape; got gate=" + shape_str(gate) +
+                    ", up=" + shape_str(up) + ", dy=" + shape_str(dy));
+    Launch l(gate, {&up, &dy, &dgate, &dup});
+    check_launch("launch_swiglu_bwd", launch_swiglu_bwd(gate.data_ptr(), up.data_ptr(), dy.data_ptr(), dgate.data_ptr(),
+                                                        dup.data_ptr(), gate.numel(), dt, l.stream));
+}
+
+void rmsnorm_residual_bwd(const at::Tensor& dy, const c10::optional<at::Tensor>& d_residual_out,
+                          const at::Tensor& residual_out, const at::Tensor& weight, const at::Tensor& dx,
+                          const at::Tensor& dweight, const at::Tensor& workspace, double eps) {
+    const int32_t dt = tag_of("dy", dy);
+    expect_float_input("dy", dt);
+    expect_same_dtype("residual_out", tag_of("residual_out", residual_out), dt);
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_same_dtype("dx", tag_of("dx", dx), dt);
+    expect_same_dtype("dweight", tag_of("dweight", dweight), dt);
+    check_cuda_contiguous("workspace", workspace);
+    if (residual_out.sizes() != dy.sizes() || dx.sizes() != dy.sizes())
+        value_error("shape mismatch: dy/residual_out/dx must share the same shape; got dy=" + shape_str(dy) +
+                    ", residual_out=" + shape_str(residual_out) + ", dx=" + shape_str(dx));
+    if (dy.dim() < 1) value_error("shape mismatch: dy must have at least 1 dimension");
+    const int64_t cols = dy.size(-1);
+    if (weight.dim() != 1 || weight.size(0) != cols || dweight.dim() != 1 || dweight.size(0) != cols)
+        value_error("shape mismatch: weight and dweight must be [" + std::to_string(cols) + "]");
+    const void* dro = nullptr;
+    if (d_residual_out.has_value()) {
+        expect_same_dtype("d_residual_out", tag_of("d_residual_out", *d_residual_out), dt);
+        if (d_residual_out->sizes() != dy.sizes())
+            value_error("shape mismatch: d_residual_out shape " + shape_str(*d_residual_out) + " must match dy " + shape_str(dy));
+        dro = d_residual_out->data_ptr();
+    }
+    const int64_t rows = cols > 0 ? dy.numel() / cols : 0;
+    const int64_t per_vec = dt == CCK_F32 ? 4 : 8;
+    if (cols % per_vec != 0 || cols / per_vec > 1024)
+        value_error("shape mismatch: the gradient kernel needs a column count that is a multiple of " +
+                    std::to_string(per_vec) + " and at most " + std::to_string(1024 * per_vec));
+    const int64_t ws_bytes = static_cast<int64_t>(workspace.numel()) * workspace.element_size();
+    if (ws_bytes < cck_rmsnorm_bwd_workspace_bytes(rows, cols))
+        value_error("shape mismatch: workspace has " + std::to_string(ws_bytes) + " bytes, needs " +
+                    std::to_string(cck_rmsnorm_bwd_workspace_bytes(rows, cols)));
+    const at::Tensor undefined;
+    Launch l(dy, {&residual_out, &weight, &dx, &dweight, &workspace,
+                  d_residual_out.has_value() ? &*d_residual_out : &undefined});
+    check_launch("launch_rmsnorm_residual_bwd",
+                 launch_rmsnorm_residual_bwd(dy.data_ptr(), dro, residual_out.data_ptr(), weight.data_ptr(), dx.data_ptr(),
+                                             dweight.data_ptr(), workspace.data_ptr(), ws_bytes, rows, cols,
+                                             static_cast<float>(eps), dt, l.stream));
+}
+
+int64_t rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t cols) { return cck_rmsnorm_bwd_workspace_bytes(rows, cols); }
+
 // ------------------------------------------------------------------ src/kernels/rope.rs:42-153
 void rope_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& cos, const at::Tensor& sin,
               const at::Tensor& q_out, const at::Tensor& k_out) {
@@ -673,6 +735,11 @@ PYBIND11_MODULE(_native, m) {
           py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"), py::arg("dlogits_t"));
     m.def("lce_dlogits_fwd", &lce_dlogits_fwd, py::arg("hidden"), py::arg("weight"), py::arg("targets"), py::arg("lse"),
           py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"));
+    m.def("swiglu_bwd", &swiglu_bwd, py::arg("gate"), py::arg("up"), py::arg("dy"), py::arg("dgate"), py::arg("dup"));
+    m.def("rmsnorm_residual_bwd", &rmsnorm_residual_bwd, py::arg("dy"), py::arg("d_residual_out"),
+          py::arg("residual_out"), py::arg("weight"), py::arg("dx"), py::arg("dweight"), py::arg("workspace"),
+          py::arg("eps"));
+    m.def("rmsnorm_bwd_workspace_bytes", &rmsnorm_bwd_workspace_bytes, py::arg("rows"), py::arg("cols"));
     m.def("transpose_2byte", &transpose_2byte, py::arg("input"), py::arg("out"));
     m.def("matmul_accumulate_f32_fwd", &matmul_accumulate_f32_fwd, py::arg("x"), py::arg("weight"), py::arg("y"));
     m.def("lce_workspace_bytes", &lce_workspace_bytes, py::arg("like"), py::arg("n"), py::arg("v_count"));

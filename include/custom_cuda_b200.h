@@ -177,6 +177,24 @@ int32_t launch_lce_dlogits_from_logits(const float* logits, const int64_t* targe
                                        int64_t v, int64_t ignore_index, float grad_scale, void* dlogits,
                                        void* dlogits_t, int64_t ld_t, int32_t dtype, void* stream);
 
+/* Gradients of launch_swiglu_fwd for an upstream gradient dy: dgate = dy * up * silu'(gate),
+ * dup = dy * silu(gate), flat over n elements, fp32 arithmetic, one rounding.  No reference
+ * counterpart (the reference is forward-only). */
+int32_t launch_swiglu_bwd(const void* gate, const void* up, const void* dy, void* dgate, void* dup, int64_t n,
+                          int32_t dtype, void* stream);
+
+/* Gradients of launch_rmsnorm_residual_fwd.  Inputs: dy, the saved residual_out, weight, and
+ * d_residual_out - the gradient arriving through the second output, or NULL.  Outputs: dx
+ * (the gradient of x and, being equal, of residual) and dweight [cols] in the storage type.
+ * workspace: cck_rmsnorm_bwd_workspace_bytes(rows, cols) bytes of device memory.  cols must be a
+ * multiple of the 16-byte vector width and at most 8192 (16-bit) / 4096 (fp32), every pointer
+ * 16-byte aligned; otherwise cudaErrorInvalidValue.  No reference counterpart. */
+int64_t cck_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t cols);
+int32_t launch_rmsnorm_residual_bwd(const void* dy, const void* d_residual_out, const void* residual_out,
+                                    const void* weight, void* dx, void* dweight, void* workspace,
+                                    int64_t workspace_bytes, int64_t rows, int64_t cols, float eps, int32_t dtype,
+                                    void* stream);
+
 /* out[c, r] = in[r, c] for a contiguous [rows, cols] matrix of 2-byte elements (float16 or
  * bfloat16); out is [cols, ld_out], ld_out >= rows, and out[:, rows..ld_out) is zero-filled.
  * cols % 4 == 0, ld_out % 4 == 0, 8-byte aligned pointers.  Makes the row-contiguous operands
