@@ -298,6 +298,19 @@ def bench_ops(dev, rank, world, peaks, src):
     if cpu_on:
         cg, cu = sets[0][0][:2048].cpu(), sets[0][1][:2048].cpu()
         cpu("swiglu_bf16", 2048 * 14336 * 6, lambda: O.swiglu(cg, cu), "2048 of 8192 rows")
+    # gradients of the two elementwise ops (no counterpart in the reference): same shapes
+    from custom_cuda_kernals_b200.kernels.autograd import rmsnorm_residual_backward, swiglu_backward
+    bsets = [(a, b, rn(rows, 14336)) for a, b in sets[:2]]
+    record("swiglu_bwd_bf16", "hbm", rows * 14336 * 2 * 5, timed_loop(swiglu_backward, bsets, 20, graph=True),
+           f"rows {rows} of 8192; reads gate, up, dy, writes d_gate, d_up")
+    del bsets
+    r0b, r1b = dist.row_range(16384, rank, world)
+    rows_b = r1b - r0b
+    nsets = [(rn(rows_b, 4096), rn(rows_b, 4096), rn(rows_b, 4096), 1 + 0.1 * rn(4096), 1e-5) for _ in range(3)]
+    record("rmsnorm_residual_bwd_bf16", "hbm", rows_b * 4096 * 2 * 4,
+           timed_loop(rmsnorm_residual_backward, nsets, 30, graph=True),
+           f"rows {rows_b} of 16384 (the block's token count); reads dy, d_residual_out, residual_out, writes dx")
+    del nsets
     del sets
     # config 2b: rope bf16 q [4,2048,32,128], k [4,2048,8,128]; sequences sharded, then positions
     if world <= 4:

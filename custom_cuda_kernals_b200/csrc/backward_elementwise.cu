@@ -109,40 +109,64 @@ constexpr int kRnMaxThreads = 256;
 constexpr int kRnCtasPerSm = 8;   // upper bound on resident CTAs per SM (sizes the d_weight partials)
 
 // Persistent CTAs, each walking rows blockIdx.x, blockIdx.x + gridDim.x, ...  A thread owns the
-// same columns in every row, so its slice of `weight` (as fp32) and of the CTA's partial
-// d_weight stay in registers for the whole kernel, and a row's dy / ro / d_ro vectors stay in
-// registers between the reduction and the store.  Every CTA ends by writing its d_weight
-// partial to dw_part[blockIdx.x][cols]; rmsnorm_dw_reduce_kernel sums the partials.
+// same columns in every row.  Its slice of `weight` (as fp32) and of the CTA's partial d_weight
+// live in shared memory as float4 planes [kPer / 4][n_vec] - plane q holds elements 4q..4q+3 of
+// every vector, so a warp's 16-byte accesses are contiguous and only the owning thread touches
+// a slot (no atomics, no barriers) - which keeps the register budget for the row itself: the
+// dy / ro / d_ro vectors stay in registers between the reduction and the store.  Every CTA
+// ends by writing its d_weight partial to dw_part[blockIdx.x][cols]; rmsnorm_dw_reduce_kernel
+// sums the partials.
 template <typename T, bool kHasDro>
 __global__ void __launch_bounds__(kRnMaxThreads)
 rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ dro_in, const T* __restrict__ ro,
                    const T* __restrict__ w, T* __restrict__ dx, float* __restrict__ dw_part, int64_t rows,
                    int cols, int n_vec, float eps) {
     constexpr int kPer = Store<T>::kPerVec;
+    constexpr int kPlanes = kPer / 4;
+    extern __shared__ __align__(16) float4 planes[];
+    float4* w4 = planes;                               // [kPlanes][n_vec]
+    float4* dw4 = planes + kPlanes * n_vec;            // [kPlanes][n_vec]
     __shared__ float2 slots[32];
-    float w_r[kRnVpt][kPer], dw_r[kRnVpt][kPer];
 #pragma unroll
     for (int j = 0; j < kRnVpt; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) {
+            float wf[kPer];
+            unpack<T>(ld_cached(reinterpret_cast<const Vec16*>(w) + i), wf);
 #pragma unroll
-        for (int e = 0; e < kPer; ++e) {
-            w_r[j][e] = 0.0f;
-            dw_r[j][e] = 0.0f;
+            for (int q = 0; q < kPlanes; ++q) {
+                w4[q * n_vec + i] = make_float4(wf[4 * q], wf[4 * q + 1], wf[4 * q + 2], wf[4 * q + 3]);
+                dw4[q * n_vec + i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
         }
-        if (i < n_vec) unpack<T>(ld_cached(reinterpret_cast<const Vec16*>(w) + i), w_r[j]);
     }
     const int warps = blockDim.x >> 5, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float inv_cols = 1.0f / static_cast<float>(cols);
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const int64_t off = row * n_vec;
-        Vec16 dv[kRnVpt], rv[kRnVpt], iv[kRnVpt];
+    // software pipeline over rows: the next row's vectors are requested before this row is
+    // reduced, so a CTA always has one row of loads in flight
+    // (the residual_out gradient is only needed at the store, so it is requested at the top of
+    // its own row's iteration and costs no second register set)
+    Vec16 dv[kRnVpt], rv[kRnVpt], iv[kRnVpt], dn[kRnVpt], rn[kRnVpt];
+    auto request = [&](int64_t row, Vec16 (&d)[kRnVpt], Vec16 (&r)[kRnVpt]) {
+        const int64_t o = row * n_vec;
 #pragma unroll
         for (int j = 0; j < kRnVpt; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
-            if (i < n_vec) {
-                dv[j] = ld_stream(reinterpret_cast<const Vec16*>(dy) + off + i);
-                rv[j] = ld_stream(reinterpret_cast<const Vec16*>(ro) + off + i);
-                if constexpr (kHasDro) iv[j] = ld_stream(reinterpret_cast<const Vec16*>(dro_in) + off + i);
+            if (i < n_vec && row < rows) {
+                d[j] = ld_stream(reinterpret_cast<const Vec16*>(dy) + o + i);
+                r[j] = ld_stream(reinterpret_cast<const Vec16*>(ro) + o + i);
+            }
+        }
+    };
+    request(blockIdx.x, dv, rv);
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int64_t off = row * n_vec;
+        request(row + gridDim.x, dn, rn);
+        if constexpr (kHasDro) {
+#pragma unroll
+            for (int j = 0; j < kRnVpt; ++j) {
+                const int i = threadIdx.x + j * blockDim.x;
+                if (i < n_vec) iv[j] = ld_stream(reinterpret_cast<const Vec16*>(dro_in) + off + i);
             }
         }
         float sq = 0.0f, gr = 0.0f;                    // sum ro^2, sum (dy * w) * ro
@@ -154,9 +178,14 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ dro_in, const
                 unpack<T>(dv[j], d);
                 unpack<T>(rv[j], r);
 #pragma unroll
-                for (int e = 0; e < kPer; ++e) {
-                    sq = fmaf(r[e], r[e], sq);
-                    gr = fmaf(d[e] * w_r[j][e], r[e], gr);
+                for (int q = 0; q < kPlanes; ++q) {
+                    const float4 wq = w4[q * n_vec + i];
+                    const float wf[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        sq = fmaf(r[4 * q + e], r[4 * q + e], sq);
+                        gr = fmaf(d[4 * q + e] * wf[e], r[4 * q + e], gr);
+                    }
                 }
             }
         }
@@ -186,9 +215,17 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ dro_in, const
                 unpack<T>(dv[j], d);
                 unpack<T>(rv[j], r);
 #pragma unroll
-                for (int e = 0; e < kPer; ++e) {
-                    o[e] = fmaf(rstd * w_r[j][e], d[e], -coef * r[e]);
-                    dw_r[j][e] = fmaf(d[e] * rstd, r[e], dw_r[j][e]);
+                for (int q = 0; q < kPlanes; ++q) {
+                    const float4 wq = w4[q * n_vec + i];
+                    float4 acc = dw4[q * n_vec + i];
+                    const float wf[4] = {wq.x, wq.y, wq.z, wq.w};
+                    float af[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        o[4 * q + e] = fmaf(rstd * wf[e], d[4 * q + e], -coef * r[4 * q + e]);
+                        af[e] = fmaf(d[4 * q + e] * rstd, r[4 * q + e], af[e]);
+                    }
+                    dw4[q * n_vec + i] = make_float4(af[0], af[1], af[2], af[3]);
                 }
                 if constexpr (kHasDro) {
                     float a[kPer];
@@ -199,6 +236,11 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ dro_in, const
                 st_stream(reinterpret_cast<Vec16*>(dx) + off + i, pack<T>(o));
             }
         }
+#pragma unroll
+        for (int j = 0; j < kRnVpt; ++j) {
+            dv[j] = dn[j];
+            rv[j] = rn[j];
+        }
     }
     float* part = dw_part + static_cast<int64_t>(blockIdx.x) * cols;
 #pragma unroll
@@ -206,21 +248,41 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ dro_in, const
         const int i = threadIdx.x + j * blockDim.x;
         if (i < n_vec) {
 #pragma unroll
-            for (int q = 0; q < kPer / 4; ++q)
-                *reinterpret_cast<float4*>(part + i * kPer + 4 * q) =
-                    make_float4(dw_r[j][4 * q], dw_r[j][4 * q + 1], dw_r[j][4 * q + 2], dw_r[j][4 * q + 3]);
+            for (int q = 0; q < kPlanes; ++q)
+                *reinterpret_cast<float4*>(part + i * kPer + 4 * q) = dw4[q * n_vec + i];
         }
     }
 }
 
+// d_weight[c] = sum over the CTAs' partials.  A CTA owns 32 columns; its 8 warps take every
+// eighth partial each (coalesced 128-byte reads, 8 independent loads in flight per thread)
+// and meet in shared memory.
 template <typename T>
 __global__ void __launch_bounds__(256)
 rmsnorm_dw_reduce_kernel(const float* __restrict__ dw_part, int parts, int cols, T* __restrict__ dw) {
-    const int c = blockIdx.x * 256 + threadIdx.x;
-    if (c >= cols) return;
+    __shared__ float partial[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
     float acc = 0.0f;
-    for (int p = 0; p < parts; ++p) acc += dw_part[static_cast<int64_t>(p) * cols + c];
-    Store<T>::store1(dw + c, acc);
+    if (c < cols) {
+        int p = warp;
+        for (; p + 56 < parts; p += 64) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = dw_part[static_cast<int64_t>(p + 8 * u) * cols + c];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc += v[u];
+        }
+        for (; p < parts; p += 8) acc += dw_part[static_cast<int64_t>(p) * cols + c];
+    }
+    partial[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && c < cols) {
+        float total = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) total += partial[i][lane];
+        Store<T>::store1(dw + c, total);
+    }
 }
 
 inline int rmsnorm_bwd_ctas(int64_t rows, int per_sm = kRnCtasPerSm) {
@@ -241,20 +303,40 @@ cudaError_t run_rmsnorm_bwd(const void* dy, const void* dro_in, const void* ro, 
     int threads = static_cast<int>(ceil_div64(ceil_div64(n_vec, kRnVpt), 32) * 32);
     if (threads < 32) threads = 32;
     int ctas = 0;
+    const size_t smem = static_cast<size_t>(cols) * 2 * sizeof(float);   // weight + d_weight partial, fp32
     auto launch = [&](auto kernel) -> cudaError_t {
         // the row loop is persistent: launch exactly as many CTAs as can be resident at once
-        int per_sm = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0);
+        // occupancy depends on (kernel, threads, smem) only: ask once per combination and device
+        static thread_local struct { const void* fn; int threads; size_t smem; int dev; int per_sm; } memo[8] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
+        int per_sm = 0;
+        const void* fn = reinterpret_cast<const void*>(kernel);
+        for (const auto& m : memo)
+            if (m.fn == fn && m.threads == threads && m.smem == smem && m.dev == dev) per_sm = m.per_sm;
+        if (per_sm == 0) {
+            // the limit is a property of the function, not of this launch: always raise it to the
+            // largest row this kernel accepts, so a later launch with a wider row still fits
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kRnVpt * kRnMaxThreads * kPer * 2 * static_cast<int>(sizeof(float)));
+            if (e != cudaSuccess) return e;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
+            if (e != cudaSuccess) return e;
+            if (per_sm < 1) return cudaErrorInvalidValue;
+            static thread_local int next = 0;
+            memo[next] = {fn, threads, smem, dev, per_sm};
+            next = (next + 1) % 8;
+        }
         ctas = rmsnorm_bwd_ctas(rows, per_sm);
-        kernel<<<ctas, threads, 0, s>>>(static_cast<const T*>(dy), static_cast<const T*>(dro_in),
+        kernel<<<ctas, threads, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(dro_in),
                                            static_cast<const T*>(ro), static_cast<const T*>(w), static_cast<T*>(dx), ws,
                                            rows, static_cast<int>(cols), static_cast<int>(n_vec), eps);
         return cudaGetLastError();
     };
     cudaError_t e = dro_in != nullptr ? launch(rmsnorm_bwd_kernel<T, true>) : launch(rmsnorm_bwd_kernel<T, false>);
     if (e != cudaSuccess) return e;
-    rmsnorm_dw_reduce_kernel<T><<<static_cast<unsigned>(ceil_div64(cols, 256)), 256, 0, s>>>(
+    rmsnorm_dw_reduce_kernel<T><<<static_cast<unsigned>(ceil_div64(cols, 32)), 256, 0, s>>>(
         ws, ctas, static_cast<int>(cols), static_cast<T*>(dw));
     return cudaGetLastError();
 }
