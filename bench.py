@@ -352,6 +352,38 @@ def bench_ops(dev, rank, world, peaks, src):
         cx8 = sets[0][0].cpu()
         cpu("fp8_quant_token_bf16", rows * 4096 * 3, lambda: O.fp8_quant(cx8, "e4m3", "token"), "all 8192 rows")
         cpu("fp8_quant_block_bf16", rows * 4096 * 3, lambda: O.fp8_quant(cx8, "e4m3", "block"), "all 8192 rows")
+    # mixture-of-experts neighbours of the block at its token count (16384 tokens, rows sharded):
+    # router over 256 experts top-8 and 8 experts top-2, row gather into expert order, weighted combine
+    from custom_cuda_kernals_b200.kernels.moe_router import moe_router
+    from custom_cuda_kernals_b200.kernels.token_permute import compute_permutation, token_combine, token_gather
+    have_ref_moe = bool(ref) and ref.has_moe()
+    t0_, t1_ = dist.row_range(16384, rank, world)
+    toks = t1_ - t0_
+    for experts, topk in ((256, 8), (8, 2)):
+        name = f"moe_router_bf16_e{experts}_k{topk}"
+        n_sets = min(64, max(4, -(-(160 << 20) // (toks * experts * 2))))    # rotate through > L2 where that is feasible
+        rsets = [(rn(toks, experts), topk) for _ in range(n_sets)]
+        record(name, "hbm", toks * experts * 2 + toks * topk * 12, timed_loop(moe_router, rsets, 64, graph=True),
+               f"tokens {toks} of 16384; logits in, fp32 weights + int64 ids out; {n_sets} input sets"
+               + ("" if n_sets * toks * experts * 2 > (126 << 20) else " (L2-resident: a launch-latency figure)"))
+        if have_ref_moe:
+            reference_kernel(name, ref.moe_router, rsets, toks * experts * 2 + toks * topk * 12, 64)
+        del rsets
+    gidx = torch.randint(0, 8, (toks, 2), device=dev, generator=g)
+    perm, unperm = compute_permutation(gidx)
+    gw = torch.rand(toks, 2, device=dev, generator=g)
+    xs = [rn(toks, 4096) for _ in range(3)]
+    gsets = [(xx, perm) for xx in xs]
+    record("token_gather_bf16", "hbm", 2 * toks * 2 * 4096 * 2, timed_loop(token_gather, gsets, 30, graph=True),
+           f"{2 * toks} rows of 4096 gathered from {toks} tokens (top-2)")
+    if have_ref_moe:
+        reference_kernel("token_gather_bf16", ref.token_gather, gsets, 2 * toks * 2 * 4096 * 2, 30)
+    csets = [(token_gather(xx, perm), unperm, gw) for xx in xs]
+    record("token_combine_bf16", "hbm", 3 * toks * 4096 * 2, timed_loop(token_combine, csets, 30, graph=True),
+           f"tokens {toks} of 16384, top-2, 4096 columns; reads 2 rows per token, writes 1")
+    if have_ref_moe:
+        reference_kernel("token_combine_bf16", ref.token_combine, csets, 3 * toks * 4096 * 2, 30)
+    del xs, gsets, csets
     # config 3: matmul_add_bias bf16 8192 x 4096 x 14336, output columns sharded
     n0, n1 = dist.column_range(14336, rank, world)
     a, w, bias = rn(8192, 4096), rn(n1 - n0, 4096, scale=0.02), rn(n1 - n0, scale=0.02)

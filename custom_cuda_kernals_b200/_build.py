@@ -29,7 +29,7 @@ OBJ = PKG / "build"
 LIB = PKG / "libcustom_cuda_b200.so"
 
 CU_SOURCES = ["swiglu.cu", "rmsnorm_residual.cu", "rope.cu", "fp8_quant.cu", "linear_ce_chunk_update.cu",
-              "matmul_add_bias.cu", "matmul_fused.cu", "linear_cross_entropy.cu", "backward_elementwise.cu"]
+              "matmul_add_bias.cu", "matmul_fused.cu", "linear_cross_entropy.cu", "backward_elementwise.cu", "moe.cu"]
 HEADERS = ["common.cuh", "ptx.cuh", "gemm_simt.cuh", "gemm_tcgen05.cuh"]
 
 # No --use_fast_math anywhere: fp8_quant.cu relies on IEEE division.

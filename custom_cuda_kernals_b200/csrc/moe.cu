@@ -1,0 +1,366 @@
+// Mixture-of-experts neighbours of the decoder block: the top-k softmax router and the two
+// row movers around the expert FFNs (gather into per-expert order, weighted combine back).
+//
+// Replaces the reference's csrc/kernels/moe_router.cu (one warp per token whatever the
+// expert count) and csrc/kernels/token_permute.cu (one block per row, one 16-byte vector in
+// flight per thread).  Here:
+//   * router: a token is owned by a group of L = 1..32 lanes, L the smallest power of two with
+//     8 * L >= experts, each lane holding 8 logits in registers - 8 experts is one THREAD per
+//     token with a single 16-byte load, 256 experts a full warp.  Softmax statistics run on
+//     xor-shuffles inside the group; each of the k arg-max rounds is one integer max-reduction
+//     (redux.sync) + ballot + shuffle when the group is a whole warp, a shuffle butterfly
+//     otherwise; ties go to the lower expert id.
+//   * gather: warps walk destination rows; a lane keeps four 16-byte vectors in flight and the
+//     next row's index is fetched while the current row streams.
+//   * combine: warps walk tokens, fp32 accumulators in registers, the token's indices and
+//     weights fetched by one coalesced load and handed out by shuffles, two expert rows (8
+//     vectors per lane) in flight.
+// All three are HBM-bound; semantics follow baselines/moe_router.py:109-119 and
+// baselines/token_permute.py:196-226.
+#include "common.cuh"
+
+namespace cck {
+namespace {
+
+// ------------------------------------------------------------------ router
+constexpr int kRouterVals = 8;       // logits per lane
+constexpr int kRouterThreads = 256;
+
+template <typename T, int L>
+__global__ void __launch_bounds__(kRouterThreads)
+moe_router_kernel(const T* __restrict__ logits, float* __restrict__ topk_w, int64_t* __restrict__ topk_i,
+                  int64_t n_tokens, int experts, int k, int renormalize, int vec_ok) {
+    constexpr int kPer = Store<T>::kPerVec;
+    const int sub = threadIdx.x % L;                                       // lane within the token's group
+    const int64_t token = (static_cast<int64_t>(blockIdx.x) * kRouterThreads + threadIdx.x) / L;
+    const bool live = token < n_tokens;
+    const T* row = logits + (live ? token : 0) * experts;
+
+    float v[kRouterVals];
+#pragma unroll
+    for (int i = 0; i < kRouterVals; ++i) v[i] = -INFINITY;
+    if (live) {
+        if (vec_ok) {                          // experts % 8 == 0: whole 16-byte vectors
+            if (sub * kRouterVals < experts) {
+#pragma unroll
+                for (int q = 0; q < kRouterVals / kPer; ++q) {
+                    float f[kPer];
+                    unpack<T>(ld_stream(row + sub * kRouterVals + q * kPer), f);
+#pragma unroll
+                    for (int e = 0; e < kPer; ++e) v[q * kPer + e] = f[e];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < kRouterVals; ++i) {
+                const int e = sub * kRouterVals + i;
+                if (e < experts) v[i] = Store<T>::load1(row + e);
+            }
+        }
+    }
+    // softmax statistics over the group
+    float mx = v[0];
+#pragma unroll
+    for (int i = 1; i < kRouterVals; ++i) mx = fmaxf(mx, v[i]);
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kRouterVals; ++i) sum += __expf(v[i] - mx);         // exp(-inf) = 0 for the padding
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv_sum = 1.0f / sum;
+
+    // k rounds of arg-max; a selected logit is replaced by -inf in its owner's registers.
+    // Equal logits go to the lower expert id: strict '>' keeps the first of a lane's values,
+    // and across lanes the lower lane (= lower ids) wins.
+    float picked = 0.0f;                        // sum of the selected probabilities
+    for (int j = 0; j < k; ++j) {
+        float best = v[0];
+        int best_i = 0;
+#pragma unroll
+        for (int i = 1; i < kRouterVals; ++i)
+            if (v[i] > best) {
+                best = v[i];
+                best_i = i;
+            }
+        int best_e;
+        if constexpr (L == 32) {
+            // whole warp: one integer max-reduction on an order-preserving key, one ballot for
+            // the owner, one shuffle for the owner's slot - instead of ten shuffles
+            const uint32_t bits = __float_as_uint(best);
+            const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+            const uint32_t top = __reduce_max_sync(0xffffffffu, key);
+            const int owner = __ffs(__ballot_sync(0xffffffffu, key == top)) - 1;
+            best_e = owner * kRouterVals + __shfl_sync(0xffffffffu, best_i, owner);
+            best = __uint_as_float((top & 0x80000000u) ? (top & 0x7fffffffu) : ~top);
+        } else {
+            best_e = sub * kRouterVals + best_i;
+#pragma unroll
+            for (int o = L / 2; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ov > best || (ov == best && oe < best_e)) {
+                    best = ov;
+                    best_e = oe;
+                }
+            }
+        }
+        if (best_e / kRouterVals == sub) {
+#pragma unroll
+            for (int i = 0; i < kRouterVals; ++i)
+                if (i == best_e % kRouterVals) v[i] = -INFINITY;
+        }
+        const float p = __expf(best - mx) * inv_sum;
+        picked += p;
+        if (live && sub == j % L) {
+            topk_w[token * k + j] = p;
+            topk_i[token * k + j] = best_e;
+        }
+    }
+    if (renormalize && live) {
+        const float inv = 1.0f / picked;
+        for (int j = sub; j < k; j += L) topk_w[token * k + j] *= inv;      // each lane rescales what it wrote
+    }
+}
+
+template <typename T>
+cudaError_t run_router(const void* logits, float* w, int64_t* idx, int64_t n_tokens, int64_t experts, int64_t k,
+                       int renorm, cudaStream_t s) {
+    constexpr int kPer = Store<T>::kPerVec;
+    const T* lg = static_cast<const T*>(logits);
+    const int vec_ok = (experts % kRouterVals == 0 && aligned16(logits)) ? 1 : 0;
+    int lanes = 1;
+    while (lanes * kRouterVals < experts) lanes *= 2;
+    const int64_t tokens_per_cta = kRouterThreads / lanes;
+    const unsigned grid = static_cast<unsigned>(ceil_div64(n_tokens, tokens_per_cta));
+    const int e = static_cast<int>(experts), kk = static_cast<int>(k);
+    (void)kPer;
+    switch (lanes) {
+        case 1:  moe_router_kernel<T, 1><<<grid, kRouterThreads, 0, s>>>(lg, w, idx, n_tokens, e, kk, renorm, vec_ok); break;
+        case 2:  moe_router_kernel<T, 2><<<grid, kRouterThreads, 0, s>>>(lg, w, idx, n_tokens, e, kk, renorm, vec_ok); break;
+        case 4:  moe_router_kernel<T, 4><<<grid, kRouterThreads, 0, s>>>(lg, w, idx, n_tokens, e, kk, renorm, vec_ok); break;
+        case 8:  moe_router_kernel<T, 8><<<grid, kRouterThreads, 0, s>>>(lg, w, idx, n_tokens, e, kk, renorm, vec_ok); break;
+        case 16: moe_router_kernel<T, 16><<<grid, kRouterThreads, 0, s>>>(lg, w, idx, n_tokens, e, kk, renorm, vec_ok); break;
+        default: moe_router_kernel<T, 32><<<grid, kRouterThreads, 0, s>>>(lg, w, idx, n_tokens, e, kk, renorm, vec_ok); break;
+    }
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ gather
+constexpr int kGatherThreads = 256;
+constexpr int kGatherUnroll = 4;
+
+// dst[i] = src[indices[i]] as raw 16-byte vectors (no arithmetic, so the element type is irrelevant)
+__global__ void __launch_bounds__(kGatherThreads)
+token_gather_vec_kernel(const Vec16* __restrict__ src, const int64_t* __restrict__ indices, Vec16* __restrict__ dst,
+                        int64_t n_rows, int64_t n_vec) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (kGatherThreads / 32);
+    int64_t row = static_cast<int64_t>(blockIdx.x) * (kGatherThreads / 32) + (threadIdx.x >> 5);
+    int64_t from = row < n_rows ? indices[row] : 0;
+    for (; row < n_rows; row += warps) {
+        const int64_t next = row + warps;
+        const int64_t from_next = next < n_rows ? indices[next] : 0;       // fetched while this row streams
+        const Vec16* s = src + from * n_vec;
+        Vec16* d = dst + row * n_vec;
+        for (int64_t i0 = lane; i0 < n_vec; i0 += 32 * kGatherUnroll) {
+            Vec16 x[kGatherUnroll];
+#pragma unroll
+            for (int u = 0; u < kGatherUnroll; ++u)
+                if (i0 + 32 * u < n_vec) x[u] = ld_stream(s + i0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < kGatherUnroll; ++u)
+                if (i0 + 32 * u < n_vec) st_stream(d + i0 + 32 * u, x[u]);
+        }
+        from = from_next;
+    }
+}
+
+// rows that are not whole aligned 16-byte vectors: element by element
+template <typename T>
+__global__ void __launch_bounds__(kGatherThreads)
+token_gather_scalar_kernel(const T* __restrict__ src, const int64_t* __restrict__ indices, T* __restrict__ dst,
+                           int64_t n_rows, int64_t hidden) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (kGatherThreads / 32);
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * (kGatherThreads / 32) + (threadIdx.x >> 5); row < n_rows;
+         row += warps) {
+        const T* s = src + indices[row] * hidden;
+        T* d = dst + row * hidden;
+        for (int64_t c = lane; c < hidden; c += 32) d[c] = s[c];
+    }
+}
+
+inline unsigned warp_grid(int64_t rows) {
+    const int64_t ctas = ceil_div64(rows, kGatherThreads / 32);
+    const int64_t cap = static_cast<int64_t>(kNumSMs) * 8;
+    return static_cast<unsigned>(ctas < cap ? ctas : cap);
+}
+
+// ------------------------------------------------------------------ combine
+constexpr int kCombineVpt = 4;
+constexpr int kCombineMaxThreads = 256;
+
+template <typename T>
+__device__ __forceinline__ void fma_vec(float (&acc)[Store<T>::kPerVec], const Vec16& x, float w) {
+    float f[Store<T>::kPerVec];
+    unpack<T>(x, f);
+#pragma unroll
+    for (int e = 0; e < Store<T>::kPerVec; ++e) acc[e] = fmaf(w, f[e], acc[e]);
+}
+
+// combined[t] = sum_j weights[t, j] * expert_output[unpermute_index[t, j]], fp32 accumulation
+// in index order.  Warps walk tokens (grid-stride).  Lane j of the warp holds the token's j-th
+// (index, weight) pair - one coalesced load per token, handed out by shuffles - so no row load
+// waits on an index of its own; a lane owns kCombineVpt vectors of the 32 * kCombineVpt-vector
+// slab being reduced and keeps two expert rows (8 vectors) in flight.
+template <typename T>
+__global__ void __launch_bounds__(kCombineMaxThreads)
+token_combine_vec_kernel(const T* __restrict__ expert_out, const int64_t* __restrict__ uidx,
+                         const float* __restrict__ weights, T* __restrict__ combined, int64_t n_tokens, int k,
+                         int64_t n_vec) {
+    constexpr int kPer = Store<T>::kPerVec;
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (kCombineMaxThreads / 32);
+    const Vec16* base = reinterpret_cast<const Vec16*>(expert_out);
+    for (int64_t token = static_cast<int64_t>(blockIdx.x) * (kCombineMaxThreads / 32) + (threadIdx.x >> 5);
+         token < n_tokens; token += warps) {
+        Vec16* out = reinterpret_cast<Vec16*>(combined) + token * n_vec;
+        for (int64_t slab = 0; slab < n_vec; slab += 32 * kCombineVpt) {     // warp-uniform: every lane shuffles
+            const int64_t i0 = slab + lane;
+            float acc[kCombineVpt][kPer];
+#pragma unroll
+            for (int u = 0; u < kCombineVpt; ++u)
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) acc[u][e] = 0.0f;
+            for (int j0 = 0; j0 < k; j0 += 32) {
+                const int mine = j0 + lane;
+                const int64_t my_row = mine < k ? __ldg(uidx + token * k + mine) : 0;
+                const float my_w = mine < k ? __ldg(weights + token * k + mine) : 0.0f;
+                const int in_chunk = k - j0 < 32 ? k - j0 : 32;
+                for (int c = 0; c < in_chunk; c += 2) {
+                    const bool two = c + 1 < in_chunk;
+                    const int64_t row0 = __shfl_sync(0xffffffffu, my_row, c);
+                    const int64_t row1 = __shfl_sync(0xffffffffu, my_row, two ? c + 1 : c);
+                    const float w0 = __shfl_sync(0xffffffffu, my_w, c);
+                    const float w1 = __shfl_sync(0xffffffffu, my_w, two ? c + 1 : c);
+                    const Vec16* r0 = base + row0 * n_vec;
+                    const Vec16* r1 = base + row1 * n_vec;
+                    Vec16 a[kCombineVpt], b[kCombineVpt];
+#pragma unroll
+                    for (int u = 0; u < kCombineVpt; ++u) {
+                        const int64_t i = i0 + 32 * u;
+                        if (i < n_vec) {
+                            a[u] = ld_stream(r0 + i);
+                            if (two) b[u] = ld_stream(r1 + i);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < kCombineVpt; ++u) {
+                        const int64_t i = i0 + 32 * u;
+                        if (i < n_vec) {
+                            fma_vec<T>(acc[u], a[u], w0);
+                            if (two) fma_vec<T>(acc[u], b[u], w1);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kCombineVpt; ++u) {
+                const int64_t i = i0 + 32 * u;
+                if (i < n_vec) st_stream(out + i, pack<T>(acc[u]));
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kCombineMaxThreads)
+token_combine_scalar_kernel(const T* __restrict__ expert_out, const int64_t* __restrict__ uidx,
+                            const float* __restrict__ weights, T* __restrict__ combined, int k, int64_t hidden) {
+    const int64_t token = blockIdx.x;
+    for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < k; ++j)
+            acc = fmaf(weights[token * k + j], Store<T>::load1(expert_out + uidx[token * k + j] * hidden + c), acc);
+        Store<T>::store1(combined + token * hidden + c, acc);
+    }
+}
+
+template <typename T>
+cudaError_t run_combine(const void* expert_out, const int64_t* uidx, const float* weights, void* combined,
+                        int64_t n_tokens, int64_t k, int64_t hidden, cudaStream_t s) {
+    constexpr int kPer = Store<T>::kPerVec;
+    if (n_tokens > 0x7fffffffLL || k > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const T* e = static_cast<const T*>(expert_out);
+    T* c = static_cast<T*>(combined);
+    if (hidden % kPer == 0 && aligned16(expert_out) && aligned16(combined)) {
+        const int64_t n_vec = hidden / kPer;
+        token_combine_vec_kernel<T><<<warp_grid(n_tokens), kCombineMaxThreads, 0, s>>>(e, uidx, weights, c, n_tokens,
+                                                                                     static_cast<int>(k), n_vec);
+    } else {
+        token_combine_scalar_kernel<T><<<static_cast<unsigned>(n_tokens), 128, 0, s>>>(e, uidx, weights, c, static_cast<int>(k), hidden);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace cck
+
+// csrc/includes/moe_router.h:20-29 of the reference: same signature and limits (at most 256
+// experts, else cudaErrorInvalidValue; nothing launched for num_tokens <= 0).
+extern "C" int32_t launch_moe_router_fwd(const void* logits, float* topk_weights, int64_t* topk_indices,
+                                         int64_t num_tokens, int64_t num_experts, int64_t k, int32_t dtype,
+                                         int32_t renormalize, void* stream) {
+    if (num_tokens <= 0) return cudaSuccess;
+    if (num_experts <= 0 || num_experts > 256 || k <= 0 || k > num_experts) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case cck::kF32:  return cck::run_router<float>(logits, topk_weights, topk_indices, num_tokens, num_experts, k, renormalize, s);
+        case cck::kF16:  return cck::run_router<__half>(logits, topk_weights, topk_indices, num_tokens, num_experts, k, renormalize, s);
+        case cck::kBF16: return cck::run_router<__nv_bfloat16>(logits, topk_weights, topk_indices, num_tokens, num_experts, k, renormalize, s);
+        default:         return cudaErrorInvalidValue;
+    }
+}
+
+// csrc/includes/token_permute.h:17-24 of the reference.
+extern "C" int32_t launch_token_gather_fwd(const void* src, const int64_t* indices, void* dst, int64_t n_dst_rows,
+                                           int64_t hidden_dim, int32_t dtype, void* stream) {
+    using namespace cck;
+    if (n_dst_rows <= 0 || hidden_dim <= 0) return cudaSuccess;
+    int64_t elem = 0;
+    switch (dtype) {
+        case kF32: elem = 4; break;
+        case kF16: case kBF16: elem = 2; break;
+        default: return cudaErrorInvalidValue;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t row_bytes = hidden_dim * elem;
+    const unsigned grid = warp_grid(n_dst_rows);
+    if (row_bytes % 16 == 0 && aligned16(src) && aligned16(dst)) {
+        token_gather_vec_kernel<<<grid, kGatherThreads, 0, s>>>(static_cast<const Vec16*>(src), indices,
+                                                                static_cast<Vec16*>(dst), n_dst_rows, row_bytes / 16);
+    } else if (elem == 4) {
+        token_gather_scalar_kernel<uint32_t><<<grid, kGatherThreads, 0, s>>>(
+            static_cast<const uint32_t*>(src), indices, static_cast<uint32_t*>(dst), n_dst_rows, hidden_dim);
+    } else {
+        token_gather_scalar_kernel<uint16_t><<<grid, kGatherThreads, 0, s>>>(
+            static_cast<const uint16_t*>(src), indices, static_cast<uint16_t*>(dst), n_dst_rows, hidden_dim);
+    }
+    return cudaGetLastError();
+}
+
+// csrc/includes/token_permute.h:32-41 of the reference.
+extern "C" int32_t launch_token_combine_fwd(const void* expert_output, const int64_t* unpermute_index,
+                                            const float* weights, void* combined, int64_t n_tokens, int64_t k,
+                                            int64_t hidden_dim, int32_t dtype, void* stream) {
+    if (n_tokens <= 0 || k <= 0 || hidden_dim <= 0) return cudaSuccess;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case cck::kF32:  return cck::run_combine<float>(expert_output, unpermute_index, weights, combined, n_tokens, k, hidden_dim, s);
+        case cck::kF16:  return cck::run_combine<__half>(expert_output, unpermute_index, weights, combined, n_tokens, k, hidden_dim, s);
+        case cck::kBF16: return cck::run_combine<__nv_bfloat16>(expert_output, unpermute_index, weights, combined, n_tokens, k, hidden_dim, s);
+        default:         return cudaErrorInvalidValue;
+    }
+}

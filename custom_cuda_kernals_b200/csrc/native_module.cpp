@@ -178,6 +178,87 @@ void swiglu_fwd(const at::Tensor& gate, const at::Tensor& up, const at::Tensor& 
                  launch_swiglu_fwd(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.numel(), dt, l.stream));
 }
 
+// ------------------------------------------------------------------ src/kernels/moe_router.rs, token_permute.rs
+void moe_router_fwd(const at::Tensor& logits, const at::Tensor& topk_weights, const at::Tensor& topk_indices,
+                    bool renormalize) {
+    const int32_t dt = tag_of("logits", logits);
+    expect_float_input("logits", dt);
+    const int32_t wdt = tag_of("topk_weights", topk_weights);
+    expect_int("topk_indices", topk_indices, at::kLong, "int64");
+    if (wdt != CCK_F32)
+        value_error(std::string("unsupported dtype 'topk_weights must be float32, got ") + tag_name(wdt) + "'");
+    if (logits.dim() != 2)
+        value_error("shape mismatch: logits must be 2-D [num_tokens, num_experts], got " + shape_str(logits));
+    const int64_t t = logits.size(0), e = logits.size(1);
+    if (topk_weights.dim() != 2 || topk_weights.size(0) != t)
+        value_error("shape mismatch: topk_weights shape " + shape_str(topk_weights) + " must be [" + std::to_string(t) + ", k]");
+    const int64_t k = topk_weights.size(1);
+    if (topk_indices.dim() != 2 || topk_indices.size(0) != t || topk_indices.size(1) != k)
+        value_error("shape mismatch: topk_indices shape " + shape_str(topk_indices) + " must match topk_weights' [" +
+                    std::to_string(t) + ", " + std::to_string(k) + "]");
+    if (k > e) throw std::runtime_error("k (" + std::to_string(k) + ") must be <= num_experts (" + std::to_string(e) + ")");
+    if (e > 256)
+        value_error("shape mismatch: num_experts (" + std::to_string(e) + ") exceeds this kernel's supported maximum of 256");
+    if (t == 0 || k == 0) return;
+    Launch l(logits, {&topk_weights, &topk_indices});
+    check_launch("launch_moe_router_fwd",
+                 launch_moe_router_fwd(logits.data_ptr(), static_cast<float*>(topk_weights.data_ptr()),
+                                       static_cast<int64_t*>(topk_indices.data_ptr()), t, e, k, dt, renormalize ? 1 : 0,
+                                       l.stream));
+}
+
+void token_gather_fwd(const at::Tensor& src, const at::Tensor& indices, const at::Tensor& dst) {
+    const int32_t dt = tag_of("src", src);
+    expect_float_input("src", dt);
+    expect_int("indices", indices, at::kLong, "int64");
+    expect_same_dtype("dst", tag_of("dst", dst), dt);
+    if (src.dim() != 2 || dst.dim() != 2)
+        value_error("shape mismatch: src and dst must be 2-D; got src=" + shape_str(src) + ", dst=" + shape_str(dst));
+    const int64_t h = src.size(1);
+    if (dst.size(1) != h)
+        value_error("shape mismatch: dst's hidden dim (" + std::to_string(dst.size(1)) + ") must match src's (" +
+                    std::to_string(h) + ")");
+    if (indices.dim() != 1 || indices.size(0) != dst.size(0))
+        value_error("shape mismatch: indices shape " + shape_str(indices) + " must be [" + std::to_string(dst.size(0)) +
+                    "] (dst's row count)");
+    Launch l(src, {&indices, &dst});
+    check_launch("launch_token_gather_fwd",
+                 launch_token_gather_fwd(src.data_ptr(), static_cast<const int64_t*>(indices.data_ptr()), dst.data_ptr(),
+                                         dst.size(0), h, dt, l.stream));
+}
+
+void token_combine_fwd(const at::Tensor& expert_output, const at::Tensor& unpermute_index, const at::Tensor& weights,
+                       const at::Tensor& combined) {
+    const int32_t dt = tag_of("expert_output", expert_output);
+    expect_float_input("expert_output", dt);
+    expect_int("unpermute_index", unpermute_index, at::kLong, "int64");
+    const int32_t wdt = tag_of("weights", weights);
+    expect_same_dtype("combined", tag_of("combined", combined), dt);
+    if (wdt != CCK_F32) value_error(std::string("unsupported dtype 'weights must be float32, got ") + tag_name(wdt) + "'");
+    if (expert_output.dim() != 2 || combined.dim() != 2)
+        value_error("shape mismatch: expert_output and combined must be 2-D; got expert_output=" +
+                    shape_str(expert_output) + ", combined=" + shape_str(combined));
+    const int64_t h = expert_output.size(1);
+    if (combined.size(1) != h)
+        value_error("shape mismatch: combined's hidden dim (" + std::to_string(combined.size(1)) +
+                    ") must match expert_output's (" + std::to_string(h) + ")");
+    if (unpermute_index.dim() != 2 || weights.dim() != 2)
+        value_error("shape mismatch: unpermute_index and weights must be 2-D [T, k]; got unpermute_index=" +
+                    shape_str(unpermute_index) + ", weights=" + shape_str(weights));
+    const int64_t t = unpermute_index.size(0), k = unpermute_index.size(1);
+    if (weights.size(0) != t || weights.size(1) != k)
+        value_error("shape mismatch: weights shape " + shape_str(weights) + " must match unpermute_index's [" +
+                    std::to_string(t) + ", " + std::to_string(k) + "]");
+    if (combined.size(0) != t)
+        value_error("shape mismatch: combined's row count (" + std::to_string(combined.size(0)) +
+                    ") must match unpermute_index's [" + std::to_string(t) + ", ...]");
+    Launch l(expert_output, {&unpermute_index, &weights, &combined});
+    check_launch("launch_token_combine_fwd",
+                 launch_token_combine_fwd(expert_output.data_ptr(), static_cast<const int64_t*>(unpermute_index.data_ptr()),
+                                          static_cast<const float*>(weights.data_ptr()), combined.data_ptr(), t, k, h, dt,
+                                          l.stream));
+}
+
 // gradients of the two ops above (no counterpart in the reference)
 void swiglu_bwd(const at::Tensor& gate, const at::Tensor& up, const at::Tensor& dy, const at::Tensor& dgate,
                 const at::Tensor& dup) {
@@ -735,6 +816,11 @@ PYBIND11_MODULE(_native, m) {
           py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"), py::arg("dlogits_t"));
     m.def("lce_dlogits_fwd", &lce_dlogits_fwd, py::arg("hidden"), py::arg("weight"), py::arg("targets"), py::arg("lse"),
           py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"));
+    m.def("moe_router_fwd", &moe_router_fwd, py::arg("logits"), py::arg("topk_weights"), py::arg("topk_indices"),
+          py::arg("renormalize"));
+    m.def("token_gather_fwd", &token_gather_fwd, py::arg("src"), py::arg("indices"), py::arg("dst"));
+    m.def("token_combine_fwd", &token_combine_fwd, py::arg("expert_output"), py::arg("unpermute_index"),
+          py::arg("weights"), py::arg("combined"));
     m.def("swiglu_bwd", &swiglu_bwd, py::arg("gate"), py::arg("up"), py::arg("dy"), py::arg("dgate"), py::arg("dup"));
     m.def("rmsnorm_residual_bwd", &rmsnorm_residual_bwd, py::arg("dy"), py::arg("d_residual_out"),
           py::arg("residual_out"), py::arg("weight"), py::arg("dx"), py::arg("dweight"), py::arg("workspace"),

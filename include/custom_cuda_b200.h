@@ -177,6 +177,26 @@ int32_t launch_lce_dlogits_from_logits(const float* logits, const int64_t* targe
                                        int64_t v, int64_t ignore_index, float grad_scale, void* dlogits,
                                        void* dlogits_t, int64_t ld_t, int32_t dtype, void* stream);
 
+/* ---- Mixture-of-experts neighbours of the block (reference csrc/includes/moe_router.h:20-29,
+ * csrc/includes/token_permute.h:17-41): same signatures and semantics. */
+
+/* probs = softmax(logits[t, :]) in fp32; topk_weights[t, :k] / topk_indices[t, :k] = the k largest
+ * probabilities (descending; ties to the lower expert id) and their expert ids; with renormalize
+ * the k weights are divided by their sum.  logits [num_tokens, num_experts] in `dtype`,
+ * num_experts <= 256 and 0 < k <= num_experts, else cudaErrorInvalidValue. */
+int32_t launch_moe_router_fwd(const void* logits, float* topk_weights, int64_t* topk_indices, int64_t num_tokens,
+                              int64_t num_experts, int64_t k, int32_t dtype, int32_t renormalize, void* stream);
+
+/* dst[i, :] = src[indices[i], :] for i < n_dst_rows; indices must lie inside src. */
+int32_t launch_token_gather_fwd(const void* src, const int64_t* indices, void* dst, int64_t n_dst_rows,
+                                int64_t hidden_dim, int32_t dtype, void* stream);
+
+/* combined[t, :] = sum_j weights[t, j] * expert_output[unpermute_index[t, j], :], accumulated in
+ * fp32, one rounding.  unpermute_index, weights: [n_tokens, k]; weights float32. */
+int32_t launch_token_combine_fwd(const void* expert_output, const int64_t* unpermute_index, const float* weights,
+                                 void* combined, int64_t n_tokens, int64_t k, int64_t hidden_dim, int32_t dtype,
+                                 void* stream);
+
 /* Gradients of launch_swiglu_fwd for an upstream gradient dy: dgate = dy * up * silu'(gate),
  * dup = dy * silu(gate), flat over n elements, fp32 arithmetic, one rounding.  No reference
  * counterpart (the reference is forward-only). */

@@ -25,7 +25,8 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 LIB = OUT / "libcustom_cuda_ref.so"
-KERNELS = ["rmsnorm_residual", "swiglu", "rope", "fp8_quant", "matmul_add_bias", "linear_cross_entropy"]
+KERNELS = ["rmsnorm_residual", "swiglu", "rope", "fp8_quant", "matmul_add_bias", "linear_cross_entropy",
+           "moe_router", "token_permute"]
 
 
 def build(reference: str | pathlib.Path, verbose: bool = False) -> pathlib.Path | None:

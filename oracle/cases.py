@@ -164,6 +164,64 @@ def lce_inputs(case, seed=0, device="cpu"):
     return hidden, weight, targets
 
 
+# --------------------------------------------------------------------------- MoE router
+# baselines/moe_router.py:78-100
+RouterCase = namedtuple("RouterCase", "name n_tokens n_experts k dtype renormalize", defaults=(True,))
+ROUTER_CASES = _cross(RouterCase, [
+    ("mixtral_like", 2048, 8, 2), ("deepseek_like", 2048, 160, 6), ("ksweep_k1", 1024, 32, 1),
+    ("ksweep_k2", 1024, 32, 2), ("ksweep_k4", 1024, 32, 4), ("ksweep_k8", 1024, 32, 8),
+    ("npot_experts", 256, 100, 4), ("npot_tokens", 257, 16, 2), ("single_expert", 64, 1, 1),
+    ("k_eq_experts", 64, 8, 8), ("large_expert_count", 128, 256, 8),
+], "tek") + _cross(RouterCase, [("no_renorm", 256, 16, 2)], "tek", extra=(False,)) + _cross(RouterCase, [
+    ("single_token", 1, 16, 2), ("empty_batch", 0, 16, 2)], "tek")
+
+
+def router_inputs(case, seed=0, device="cpu"):
+    """logits ~ N(0,1) (baselines/moe_router.py:103-106)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    return torch.randn((case.n_tokens, case.n_experts), dtype=case.dtype, device=device, generator=g)
+
+
+# --------------------------------------------------------------------------- token gather / combine
+# baselines/token_permute.py:139-167
+GatherCase = namedtuple("GatherCase", "name n_src_rows n_dst_rows hidden_dim dtype")
+GATHER_CASES = _cross(GatherCase, [
+    ("mixtral_like", 2048, 4096, 4096), ("large_hidden", 2048, 4096, 11008), ("npot_hidden", 257, 513, 100),
+    ("single_row", 1, 1, 256), ("empty_dst", 64, 0, 256), ("small_hidden", 128, 256, 16),
+], "sdh")
+CombineCase = namedtuple("CombineCase", "name n_tokens k hidden_dim dtype")
+COMBINE_CASES = _cross(CombineCase, [
+    ("mixtral_like", 2048, 2, 4096), ("deepseek_like", 2048, 6, 4096), ("k1", 256, 1, 512), ("k8", 256, 8, 512),
+    ("npot_hidden", 257, 3, 100), ("single_token", 1, 2, 256), ("empty_batch", 0, 2, 256), ("small_hidden", 128, 4, 16),
+], "tkh")
+
+
+def gather_inputs(case, seed=0, device="cpu"):
+    """src ~ N(0,1), then uniform row indices (baselines/token_permute.py:170-182)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    src = torch.randn((case.n_src_rows, case.hidden_dim), dtype=case.dtype, device=device, generator=g)
+    if case.n_dst_rows == 0 or case.n_src_rows == 0:
+        indices = torch.empty(case.n_dst_rows, dtype=torch.long, device=device)
+    else:
+        indices = torch.randint(0, case.n_src_rows, (case.n_dst_rows,), device=device, generator=g, dtype=torch.long)
+    return src, indices
+
+
+def combine_inputs(case, seed=0, device="cpu"):
+    """expert_output ~ N(0,1), weights ~ U(0,1) fp32, then a random permutation of the expert
+    rows as the index (baselines/token_permute.py:185-204).  Returns (expert_output,
+    unpermute_index, weights)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    n = case.n_tokens * case.k
+    expert_output = torch.randn((n, case.hidden_dim), dtype=case.dtype, device=device, generator=g)
+    weights = torch.rand(case.n_tokens, case.k, dtype=torch.float32, device=device, generator=g)
+    if n == 0:
+        index = torch.empty(case.n_tokens, case.k, dtype=torch.long, device=device)
+    else:
+        index = torch.randperm(n, device=device, generator=g).reshape(case.n_tokens, case.k)
+    return expert_output, index, weights
+
+
 def by_name(table, name):
     for case in table:
         if case.name == name:

@@ -284,6 +284,44 @@ def llama_block(x, w, n_heads=32, n_kv_heads=8, eps=1e-5, theta=500000.0):
 
 
 # --------------------------------------------------------------------------- comparison helper
+# --------------------------------------------------------------------------- mixture-of-experts neighbours
+def moe_router(logits, k, renormalize=True, wide=False):
+    """baselines/moe_router.py:109-119 (eager) and :139-148 (fp64 when ``wide``): softmax in
+    fp32, top-k probabilities and their expert ids, optional renormalisation."""
+    probs = torch.softmax(logits.to(torch.float64 if wide else torch.float32), dim=-1)
+    topk_weights, topk_indices = torch.topk(probs, k, dim=-1)
+    if renormalize:
+        topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
+    return topk_weights, topk_indices
+
+
+def compute_permutation(topk_indices):
+    """baselines/token_permute.py:58-72: stable argsort of the flattened expert assignments
+    and its inverse."""
+    t, k = topk_indices.shape
+    order = torch.argsort(topk_indices.reshape(-1), stable=True)
+    inverse = torch.empty_like(order)
+    inverse[order] = torch.arange(t * k, device=topk_indices.device)
+    return order // k, inverse.reshape(t, k)
+
+
+def token_gather(src, indices, wide=False):
+    """baselines/token_permute.py:196-198 (:209-210 when ``wide``)."""
+    return (src.to(torch.float64) if wide else src).index_select(0, indices)
+
+
+def token_combine(expert_output, unpermute_index, weights, wide=False):
+    """baselines/token_permute.py:213-226 (:240-248 when ``wide``): gather each token's k
+    expert rows, scale by the fp32 gate weights, sum in fp32, round once."""
+    if unpermute_index.numel() == 0:
+        return torch.zeros(unpermute_index.shape[0], expert_output.shape[-1],
+                           dtype=torch.float64 if wide else expert_output.dtype, device=expert_output.device)
+    if wide:
+        return (expert_output.to(torch.float64)[unpermute_index] * weights.to(torch.float64).unsqueeze(-1)).sum(dim=1)
+    gathered = expert_output[unpermute_index]
+    return (gathered.to(torch.float32) * weights.unsqueeze(-1)).sum(dim=1).to(expert_output.dtype)
+
+
 def assert_close_with_outliers(actual, expected, *, rtol, atol, max_outlier_fraction=0.0):
     """``|a-e| <= atol + rtol*|e|`` for all but ``max_outlier_fraction`` of the
     elements (bf16 results sitting on a rounding boundary can flip by one ulp

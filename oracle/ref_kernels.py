@@ -32,7 +32,10 @@ def lib():
         _lib = ctypes.CDLL(str(LIB_PATH))      # RTLD_LOCAL: its launch_* names do not shadow ours
         for name in ("launch_rmsnorm_residual_fwd", "launch_swiglu_fwd", "launch_rope_fwd",
                      "launch_fp8_quant_block_fwd", "launch_fp8_quant_tensor_fwd", "launch_matmul_add_bias_fwd",
-                     "launch_linear_ce_chunk_update"):
+                     "launch_linear_ce_chunk_update", "launch_moe_router_fwd", "launch_token_gather_fwd",
+                     "launch_token_combine_fwd"):
+            if not hasattr(_lib, name):          # a library built before the MoE kernels were added
+                continue
             getattr(_lib, name).restype = ctypes.c_int32
     return _lib
 
@@ -124,3 +127,35 @@ def linear_cross_entropy(hidden, weight, targets, ignore_index=-100, reduction="
     if reduction == "none":
         return loss
     return loss.sum() if reduction == "sum" else loss.sum() / keep.sum().float()
+
+
+def has_moe() -> bool:
+    return available() and hasattr(lib(), "launch_moe_router_fwd")
+
+
+def moe_router(logits, k, renormalize=True):
+    """custom_cuda/kernels/moe_router.py:18-30"""
+    t, e = logits.shape
+    w = torch.empty(t, k, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(t, k, dtype=torch.long, device=logits.device)
+    _ok(lib().launch_moe_router_fwd(_p(logits), _p(w), _p(idx), _i(t), _i(e), _i(k), ctypes.c_int32(_TAG[logits.dtype]),
+                                    ctypes.c_int32(1 if renormalize else 0), _s()), "moe_router")
+    return w, idx
+
+
+def token_gather(src, indices):
+    """custom_cuda/kernels/token_permute.py:18-26"""
+    dst = torch.empty(indices.shape[0], src.shape[1], dtype=src.dtype, device=src.device)
+    _ok(lib().launch_token_gather_fwd(_p(src), _p(indices), _p(dst), _i(indices.shape[0]), _i(src.shape[1]),
+                                      ctypes.c_int32(_TAG[src.dtype]), _s()), "token_gather")
+    return dst
+
+
+def token_combine(expert_output, unpermute_index, weights):
+    """custom_cuda/kernels/token_permute.py:29-42"""
+    t, k = unpermute_index.shape
+    out = torch.empty(t, expert_output.shape[1], dtype=expert_output.dtype, device=expert_output.device)
+    _ok(lib().launch_token_combine_fwd(_p(expert_output), _p(unpermute_index), _p(weights), _p(out), _i(t), _i(k),
+                                       _i(expert_output.shape[1]), ctypes.c_int32(_TAG[expert_output.dtype]), _s()),
+        "token_combine")
+    return out

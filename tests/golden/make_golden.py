@@ -45,6 +45,9 @@ SMALL = {
     "gemm": ["npot_dims", "single_row"],
     "lce": ["npot_tokens", "with_ignored", "all_ignored", "tiny_vocab", "reduction_sum",
             "reduction_none", "single_token"],
+    "router": ["npot_tokens", "single_expert", "k_eq_experts", "no_renorm", "single_token"],
+    "gather": ["npot_hidden", "single_row", "small_hidden"],
+    "combine": ["npot_hidden", "single_token", "small_hidden"],
 }
 SKIP_HEAVY = {"mlp_up", "mlp_down", "llama3_vocab", "llama2_vocab"}  # minutes of CPU GEMM each
 
@@ -78,7 +81,8 @@ def main():
     sys.path.insert(0, args.reference)
     ref = {k: importlib.import_module(f"baselines.{m}") for k, m in {
         "rmsnorm": "rmsnorm_residual", "swiglu": "swiglu", "rope": "rope", "fp8": "fp8_quant",
-        "gemm": "matmul_add_bias", "lce": "linear_cross_entropy"}.items()}
+        "gemm": "matmul_add_bias", "lce": "linear_cross_entropy", "router": "moe_router",
+        "permute": "token_permute"}.items()}
     torch.manual_seed(0)
 
     golden, digests = {}, {}
@@ -186,6 +190,47 @@ def main():
         note("lce", all(same(a, b) for a, b in zip(ri, mi)), same(ro, mo) and same(r64, m64), rc.name)
         if base_of(rc.name) in SMALL["lce"]:
             golden[f"lce/{rc.name}"] = {"loss": ro, "loss64": r64}
+
+    # ---- MoE router
+    mine = {c.name: c for c in cases.ROUTER_CASES}
+    for rc in ref["router"].ALL_CASES:
+        c = mine[rc.name]
+        ri = ref["router"].make_inputs(rc, device="cpu", seed=0)
+        mi = cases.router_inputs(c, seed=0)
+        ro = ref["router"].eager_moe_router(ri, rc.k, rc.renormalize)
+        mo = ops.moe_router(mi, c.k, c.renormalize)
+        r64 = ref["router"].reference_fp64(ri, rc.k, rc.renormalize)
+        m64 = ops.moe_router(mi, c.k, c.renormalize, wide=True)
+        note("router", same(ri, mi) and rc.renormalize == c.renormalize,
+             all(same(a, b) for a, b in zip(ro + r64, mo + m64)), rc.name)
+        if base_of(rc.name) in SMALL["router"]:
+            golden[f"router/{rc.name}"] = {"weights": ro[0], "indices": ro[1]}
+
+    # ---- token gather / combine and the permutation bookkeeping
+    mine = {c.name: c for c in cases.GATHER_CASES}
+    for rc in ref["permute"].GATHER_ALL_CASES:
+        c = mine[rc.name]
+        ri = ref["permute"].make_gather_inputs(rc, device="cpu", seed=0)
+        mi = cases.gather_inputs(c, seed=0)
+        ro, mo = ref["permute"].eager_token_gather(*ri), ops.token_gather(*mi)
+        note("gather", all(same(a, b) for a, b in zip(ri, mi)),
+             same(ro, mo) and same(ref["permute"].reference_gather_fp64(*ri), ops.token_gather(*mi, wide=True)), rc.name)
+        if base_of(rc.name) in SMALL["gather"]:
+            golden[f"gather/{rc.name}"] = {"dst": ro}
+    mine = {c.name: c for c in cases.COMBINE_CASES}
+    for rc in ref["permute"].COMBINE_ALL_CASES:
+        c = mine[rc.name]
+        ri = ref["permute"].make_combine_inputs(rc, device="cpu", seed=0)
+        mi = cases.combine_inputs(c, seed=0)
+        ro, mo = ref["permute"].eager_token_combine(*ri), ops.token_combine(*mi)
+        note("combine", all(same(a, b) for a, b in zip(ri, mi)),
+             same(ro, mo) and same(ref["permute"].reference_combine_fp64(*ri), ops.token_combine(*mi, wide=True)), rc.name)
+        if base_of(rc.name) in SMALL["combine"]:
+            golden[f"combine/{rc.name}"] = {"combined": ro}
+    topk = torch.randint(0, 8, (37, 3), generator=torch.Generator().manual_seed(3))
+    rp, mp = ref["permute"].compute_permutation(topk), ops.compute_permutation(topk)
+    note("combine", True, all(same(a, b) for a, b in zip(rp, mp)), "compute_permutation")
+    golden["combine/compute_permutation"] = {"topk": topk, "permute_index": rp[0], "unpermute_index": rp[1]}
 
     torch.save(golden, HERE / "golden_small.pt")
     (HERE / "fp8_digests.json").write_text(json.dumps(digests, indent=0, sort_keys=True))

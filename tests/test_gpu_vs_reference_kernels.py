@@ -78,3 +78,21 @@ def test_linear_cross_entropy(dtype):
     for red in ("mean", "none"):
         torch.testing.assert_close(linear_cross_entropy(h, w, t, reduction=red),
                                    ref_kernels.linear_cross_entropy(h, w, t, reduction=red), rtol=rtol, atol=atol)
+
+
+@pytest.mark.skipif(not ref_kernels.available() or not ref_kernels.has_moe(), reason="reference MoE kernels not built")
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_moe_router_gather_combine(dtype):
+    from custom_cuda.kernels.moe_router import moe_router
+    from custom_cuda.kernels.token_permute import compute_permutation, token_combine, token_gather
+    g = torch.Generator().manual_seed(4)
+    logits = torch.randn(1000, 64, generator=g).float().to(DEV)     # fp32 logits: no exact ties
+    w_mine, i_mine = moe_router(logits, 6)
+    w_ref, i_ref = ref_kernels.moe_router(logits, 6)
+    assert torch.equal(i_mine, i_ref)
+    torch.testing.assert_close(w_mine, w_ref, rtol=1e-5, atol=1e-6)
+    x = torch.randn(1000, 1024, generator=g).to(dtype).to(DEV)
+    perm, unperm = compute_permutation(i_mine)
+    rows = token_gather(x, perm)
+    assert torch.equal(rows, ref_kernels.token_gather(x, perm))
+    check(token_combine(rows, unperm, w_mine), ref_kernels.token_combine(rows, unperm, w_mine).cpu(), dtype)

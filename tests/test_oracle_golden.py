@@ -31,9 +31,9 @@ def _near(a, b, dtype):
 
 
 def test_pin_report_is_clean():
-    assert set(pin["ops"]) == {"rmsnorm", "swiglu", "rope", "fp8", "gemm", "lce"}
+    assert set(pin["ops"]) == {"rmsnorm", "swiglu", "rope", "fp8", "gemm", "lce", "router", "gather", "combine"}
     for op, r in pin["ops"].items():
-        assert r["cases"] >= 24, op
+        assert r["cases"] >= 18, op
         assert not r["input_mismatch"] and not r["output_mismatch"], op
 
 
@@ -153,3 +153,38 @@ def test_block_oracle_runs_and_is_finite():
     x = workloads.block_input(2, 16, 256)
     y = ops.llama_block(x, w, n_heads=4, n_kv_heads=2)
     assert y.shape == x.shape and y.dtype == torch.bfloat16 and torch.isfinite(y.float()).all()
+
+
+@pytest.mark.parametrize("key", [k for k in golden if k.startswith("router/")])
+def test_moe_router(key):
+    c = cases.by_name(cases.ROUTER_CASES, key.split("/")[1])
+    w, i = ops.moe_router(cases.router_inputs(c), c.k, c.renormalize)
+    assert w.dtype == torch.float32 and i.dtype == torch.int64
+    _near(w, golden[key]["weights"], torch.float32)
+    assert torch.equal(i, golden[key]["indices"])
+
+
+@pytest.mark.parametrize("key", [k for k in golden if k.startswith("gather/")])
+def test_token_gather(key):
+    c = cases.by_name(cases.GATHER_CASES, key.split("/")[1])
+    assert torch.equal(ops.token_gather(*cases.gather_inputs(c)), golden[key]["dst"])
+
+
+@pytest.mark.parametrize("key", [k for k in golden if k.startswith("combine/") and "permutation" not in k])
+def test_token_combine(key):
+    c = cases.by_name(cases.COMBINE_CASES, key.split("/")[1])
+    _near(ops.token_combine(*cases.combine_inputs(c)), golden[key]["combined"], c.dtype)
+
+
+def test_compute_permutation_golden_and_round_trip():
+    g = golden["combine/compute_permutation"]
+    perm, unperm = ops.compute_permutation(g["topk"])
+    assert torch.equal(perm, g["permute_index"]) and torch.equal(unperm, g["unpermute_index"])
+    # gather into expert order, combine back with unit weight on one choice: the identity
+    t, k = g["topk"].shape
+    x = torch.randn(t, 16, generator=torch.Generator().manual_seed(1))
+    expert_rows = ops.token_gather(x, perm)
+    assert torch.all(g["topk"].reshape(-1)[torch.argsort(g["topk"].reshape(-1), stable=True)].diff() >= 0)
+    w = torch.zeros(t, k)
+    w[:, 1] = 1.0
+    assert torch.equal(ops.token_combine(expert_rows, unperm, w), x)
