@@ -80,6 +80,25 @@ class _NoTimer:
         return fn(*args, **kwargs)
 
 
+def host_pipeline_groups(batch: int, chunks: int | None = None) -> list[tuple[int, int]]:
+    """Sequence ranges ``[b0, b1)`` of the host pipeline's groups.  Only the first group's
+    copy-in and the last group's copy-out cannot hide behind another group's kernels, so by
+    default those two groups are one sequence each and the sequences between them form (at
+    most) two large groups, which keeps the GEMMs of the bulk of the batch at an efficient
+    size.  ``chunks`` asks for that many equal groups instead."""
+    if batch <= 0:
+        return []
+    if chunks is not None:
+        n = max(1, min(batch, chunks))
+        return [(batch * i // n, batch * (i + 1) // n) for i in range(n)]
+    if batch <= 3:
+        return [(i, i + 1) for i in range(batch)]
+    middle = batch - 2
+    cut = 1 + (middle + 1) // 2
+    groups = [(0, 1), (1, cut), (cut, batch - 1), (batch - 1, batch)]
+    return [g for g in groups if g[1] > g[0]]
+
+
 class LlamaBlock:
     """One decoder block; ``weights`` maps PARAM_NAMES to CUDA tensors
     (projections as ``[out_features, in_features]``, the nn.Linear layout)."""
@@ -168,17 +187,16 @@ class LlamaBlock:
 
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunks: int | None = None) -> torch.Tensor:
         """Host-buffer entry point: ``x_host`` / ``out_host`` are pinned CPU tensors
-        ``[B, S, hidden]``.  The batch is cut into ``chunks`` groups of whole sequences
-        (default: up to 4) that flow through three streams - copy-in, compute (the current
-        stream) and copy-out - so the PCIe transfers of one group overlap the kernels of
-        another.  Returns ``out_host`` once every group has landed in it."""
+        ``[B, S, hidden]``.  The batch is cut into groups of whole sequences
+        (``host_pipeline_groups``) that flow through three streams - copy-in, compute (the
+        current stream) and copy-out - so the PCIe transfers of one group overlap the kernels
+        of another.  Returns ``out_host`` once every group has landed in it."""
         dev = self.device
         b = x_host.shape[0]
-        n = max(1, min(b, chunks if chunks is not None else 4))
         if not hasattr(self, "_copy_in"):
             self._copy_in, self._copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         compute = torch.cuda.current_stream(dev)
-        bounds = [(b * i // n, b * (i + 1) // n) for i in range(n)]
+        bounds = host_pipeline_groups(b, chunks)
         self._copy_in.wait_stream(compute)
         staged = []
         with torch.cuda.stream(self._copy_in):

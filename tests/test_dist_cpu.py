@@ -167,3 +167,16 @@ def test_single_process_needs_no_group():
     s = torch.zeros(3, 5)
     assert dist.gather_row_stats(s).shape == (1, 3, 5)
     assert dist.max_over_ranks(3.5) == 3.5
+
+
+def test_host_pipeline_groups_cover_the_batch_with_single_sequence_ends():
+    from custom_cuda_kernals_b200.llama_block import host_pipeline_groups
+    for batch in range(0, 20):
+        groups = host_pipeline_groups(batch)
+        assert [g for g in groups if g[1] <= g[0]] == []
+        assert sum(b1 - b0 for b0, b1 in groups) == batch
+        assert all(a[1] == b[0] for a, b in zip(groups[:-1], groups[1:]))
+        if batch >= 4:      # only the first copy-in and the last copy-out are exposed: keep them small
+            assert groups[0] == (0, 1) and groups[-1] == (batch - 1, batch) and len(groups) <= 4
+    assert host_pipeline_groups(8, 4) == [(0, 2), (2, 4), (4, 6), (6, 8)]
+    assert host_pipeline_groups(3, 8) == [(0, 1), (1, 2), (2, 3)]
