@@ -46,6 +46,7 @@ constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 25
 
 struct TileWork {
     int m_tile, n_tile;
+    int n0;             // first output column of the tile (n_tile x the kernel's tile width)
     int split;          // LCE: vocabulary split this tile belongs to
     bool first, last;   // first / last tile of a unit (a unit = tiles sharing epilogue row state)
 };
@@ -98,10 +99,11 @@ struct SchedGemm {
 template <class Epi, class = void> struct PairedHalves { static constexpr bool value = false; };
 template <class Epi> struct PairedHalves<Epi, std::enable_if_t<Epi::kPairedHalves>> { static constexpr bool value = true; };
 
-template <class Epi>
+template <class Epi, int BN = kBN>
 __device__ __forceinline__ void drain_tile(const typename Epi::Params& ep, typename Epi::Thread& th, const TileWork& w,
                                            int row_in_tile, uint32_t t0, float* scratch) {
     if constexpr (PairedHalves<Epi>::value) {
+        static_assert(BN == kBN, "paired halves need the full-width tile");
 #pragma unroll 1
         for (int c = 0; c < kBN / 64; ++c) {
             float lo[32], hi[32];
@@ -111,7 +113,7 @@ __device__ __forceinline__ void drain_tile(const typename Epi::Params& ep, typen
         }
     } else {
 #pragma unroll 1
-        for (int c = 0; c < kBN / 32; ++c) {
+        for (int c = 0; c < BN / 32; ++c) {
             float acc[32];
             ptx::tmem_ld32(t0 + c * 32, acc);
             Epi::chunk(ep, th, w, row_in_tile, c * 32, acc, scratch);
@@ -120,11 +122,25 @@ __device__ __forceinline__ void drain_tile(const typename Epi::Params& ep, typen
 }
 
 // ---- kernel
-template <bool kFp8, class Sched, class Epi>
+// BN = 256 is the throughput shape.  BN = 64 is for problems with too few 128 x 256 tiles to
+// occupy the machine (small M: decode-sized batches): four times as many CTAs pull the weight
+// matrix, 24 KB stages let the ring run 8 deep, and the two accumulators take 128 TMEM columns.
+template <int BN> struct TileShape {
+    static constexpr int kStagesN = BN == kBN ? kStages : 8;
+    static constexpr int kBBytesN = BN * kRowBytes;
+    static constexpr int kStageBytesN = kABytes + kBBytesN;
+    static constexpr int kTmemColsN = 2 * BN;
+    static constexpr int kSmemBytesN = kStagesN * kStageBytesN + 1024 + 256 + kEpiWarps * kScratchFloatsPerWarp * 4;
+};
+
+template <bool kFp8, class Sched, class Epi, int BN = kBN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const typename Sched::Params sp, const typename Epi::Params ep, int k_blocks, uint32_t idesc,
             unsigned int* status) {
+    constexpr int kStages = TileShape<BN>::kStagesN;          // shadow the full-width constants
+    constexpr int kStageBytes = TileShape<BN>::kStageBytesN;
+    constexpr int kTmemCols = TileShape<BN>::kTmemColsN;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_addr(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;            // stage ring, 1024-byte aligned
@@ -174,7 +190,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             typename Sched::Iter it(sp, blockIdx.x, gridDim.x);
             TileWork w;
             while (ok && it.next(w)) {
-                const int m0 = w.m_tile * kBM, n0 = w.n_tile * kBN;
+                const int m0 = w.m_tile * kBM, n0 = w.n_tile * BN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
@@ -199,7 +215,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const uint32_t acc_phase = (acc_iter >> 1) & 1;
                 if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag)) break;
                 ptx::tc_fence_after_sync();
-                const uint32_t d = tmem_base + buf * kBN;
+                const uint32_t d = tmem_base + buf * BN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
@@ -229,6 +245,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         typename Sched::Iter it(sp, blockIdx.x, gridDim.x);
         TileWork w;
         while (it.next(w)) {
+            w.n0 = w.n_tile * BN;
             const int buf = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1;
             __syncwarp();
@@ -237,8 +254,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const bool got = ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag);
             if (!__all_sync(0xffffffffu, got)) break;
             ptx::tc_fence_after_sync();
-            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
-            drain_tile<Epi>(ep, th, w, row_in_tile, t0, my_scratch);
+            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            drain_tile<Epi, BN>(ep, th, w, row_in_tile, t0, my_scratch);
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
@@ -402,6 +419,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         TileWork w;
         while (it.next(w)) {
             w.m_tile = w.m_tile * 2 + static_cast<int>(rank);
+            w.n0 = w.n_tile * kBN;
             const int buf = acc_iter & 1;
             const uint32_t acc_phase = (acc_iter >> 1) & 1;
             __syncwarp();
@@ -463,6 +481,15 @@ inline bool pair_kernels_enabled() {
     return on;
 }
 
+// CCK_GEMM_NO_NARROW=1 keeps small problems on the full-width tiles.
+inline bool narrow_tiles_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("CCK_GEMM_NO_NARROW");
+        return !(v && v[0] == '1');
+    }();
+    return on;
+}
+
 inline int sm_count() {
     static int n = [] {
         int dev = 0, v = 0;
@@ -473,10 +500,11 @@ inline int sm_count() {
     return n;
 }
 
-template <bool kFp8, class Sched, class Epi>
+template <bool kFp8, class Sched, class Epi, int BN = kBN>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const typename Sched::Params& sp,
                    const typename Epi::Params& ep, int64_t k_elems, uint32_t idesc, int ctas, cudaStream_t s) {
-    auto kern = gemm_kernel<kFp8, Sched, Epi>;
+    auto kern = gemm_kernel<kFp8, Sched, Epi, BN>;
+    constexpr int kSmemBytes = TileShape<BN>::kSmemBytesN;
     static bool configured = false;   // per instantiation
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);

@@ -44,7 +44,7 @@ struct EpiBias {
     struct Thread {};
     __device__ static __forceinline__ void tile_begin(const Params& p, Thread&, const TileWork& w, float* scratch,
                                                       int lane, int) {
-        const int64_t n0 = static_cast<int64_t>(w.n_tile) * kBN;
+        const int64_t n0 = w.n0;
 #pragma unroll
         for (int i = 0; i < kBN / 32; ++i) {
             const int64_t col = n0 + lane + 32 * i;
@@ -54,7 +54,7 @@ struct EpiBias {
     __device__ static __forceinline__ void chunk(const Params& p, Thread&, const TileWork& w, int row_in_tile,
                                                  int c0, float (&acc)[32], const float* scratch) {
         const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
-        const int64_t col = static_cast<int64_t>(w.n_tile) * kBN + c0;
+        const int64_t col = static_cast<int64_t>(w.n0) + c0;
         if (row >= p.m || col >= p.n) return;
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] += scratch[c0 + j];
@@ -140,10 +140,22 @@ cudaError_t gemm_tc(const void* x, const void* w, const void* bias, void* y, int
     typename EpiBias<T>::Params ep{static_cast<const T*>(bias), static_cast<T*>(y), m, n,
                                    (n % 8 == 0 && aligned16(y)) ? 1 : 0};
     const uint32_t fmt = is_bf16 ? 1u : 0u;
-    const bool pair = m_tiles >= 2 && pair_kernels_enabled() && max_pairs<false, SchedGemm, EpiBias<T>>() > 0;
     CUtensorMap ta, tb;
     cudaError_t e = make_tmap(&ta, dt, 2, x, m, k, kBM);
     if (e != cudaSuccess) return e;
+    // Too few full-width tiles to occupy a quarter of the SMs (small M): 128 x 64 tiles, four times
+    // the CTAs pulling the weights.  Measured on B200, K = N = 4096: M = 128 20 us against 29 us,
+    // M = 256 21 against 26; from M = 512 on the full-width tiles win again.
+    constexpr int kNarrow = 64;
+    if (static_cast<int64_t>(m_tiles) * n_tiles <= sm_count() / 4 && narrow_tiles_enabled()) {
+        e = make_tmap(&tb, dt, 2, w, n, k, kNarrow);
+        if (e != cudaSuccess) return e;
+        SchedGemm::Params sp{m_tiles, static_cast<int>(ceil_div64(n, kNarrow)), m_tiles};
+        const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
+        return launch<false, SchedGemm, EpiBias<T>, kNarrow>(ta, tb, sp, ep, k, ptx::instr_desc(fmt, fmt, kBM, kNarrow),
+                                                             static_cast<int>(tiles < sm_count() ? tiles : sm_count()), s);
+    }
+    const bool pair = m_tiles >= 2 && pair_kernels_enabled() && max_pairs<false, SchedGemm, EpiBias<T>>() > 0;
     e = make_tmap(&tb, dt, 2, w, n, k, pair ? 128 : kBN);     // a CTA of a pair loads half of the B tile
     if (e != cudaSuccess) return e;
     if (pair) {

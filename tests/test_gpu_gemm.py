@@ -51,6 +51,24 @@ def test_tensor_core_path_ragged_shapes(shape, dtype):
     assert device_status_clean(y)
 
 
+@pytest.mark.parametrize("shape", [(128, 4096, 4096), (16, 4096, 11008), (256, 1024, 4096), (100, 512, 1000),
+                                   (512, 4096, 4096), (128, 4096, 72), (1, 8192, 4096)])
+def test_small_m_narrow_tiles_match_oracle(shape):
+    """Decode-sized batches (few 128 x 256 tiles) run on 128 x 64 tiles: same results as the
+    oracle's bf16 chain and as an fp32 evaluation, ragged column counts included."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    m, k, n = shape
+    g = torch.Generator().manual_seed(m + k + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    b = (0.02 * torch.randn(n, generator=g)).to(torch.bfloat16)
+    y = matmul_add_bias(*to_dev(x, w, b))
+    check(y.double(), ops.matmul_add_bias_fp64(x, w, b), torch.bfloat16, ops.TOLERANCE_GEMM)
+    exact = x.float() @ w.float().T + b.float()
+    assert (y.float().cpu() - exact).abs().max() <= 2 ** -8 * exact.abs().max() + 1e-3
+    assert device_status_clean(y)
+
+
 def test_matmul_identity_is_exact():
     """x @ I + 0 reproduces x bit for bit (every product is exact, one addend per sum)."""
     from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
