@@ -490,6 +490,18 @@ inline bool narrow_tiles_enabled() {
     return on;
 }
 
+// CCK_GEMM_SPLITK=1 lets decode-sized problems split K over a thread-block cluster
+// (gemm_splitk.cuh).  Off by default: the other kernels add a row's products in one fixed order
+// whatever M and N are, so a row shard or a column shard of a problem gives bit for bit the
+// rows / columns of the whole; partial sums over K slices are added in another order.
+inline bool splitk_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("CCK_GEMM_SPLITK");
+        return v && v[0] == '1';
+    }();
+    return on;
+}
+
 inline int sm_count() {
     static int n = [] {
         int dev = 0, v = 0;

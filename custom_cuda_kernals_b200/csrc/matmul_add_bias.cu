@@ -13,7 +13,7 @@
 #include <type_traits>
 
 #include "gemm_simt.cuh"
-#include "gemm_tcgen05.cuh"
+#include "gemm_splitk.cuh"
 
 namespace cck {
 namespace tc {
@@ -143,17 +143,27 @@ cudaError_t gemm_tc(const void* x, const void* w, const void* bias, void* y, int
     CUtensorMap ta, tb;
     cudaError_t e = make_tmap(&ta, dt, 2, x, m, k, kBM);
     if (e != cudaSuccess) return e;
-    // Too few full-width tiles to occupy a quarter of the SMs (small M): 128 x 64 tiles, four times
-    // the CTAs pulling the weights.  Measured on B200, K = N = 4096: M = 128 20 us against 29 us,
-    // M = 256 21 against 26; from M = 512 on the full-width tiles win again.
+    // Too few full-width tiles to occupy the machine (small M, decode-sized batches): 128 x 64 tiles,
+    // and while even those leave SMs idle, a cluster of 2-8 CTAs per tile that splits K
+    // (gemm_splitk.cuh).  Measured on B200, K = N = 4096, device time per call: M = 128 full-width
+    // 29 us, narrow 20 us; M = 256 26 / 21; from M = 512 on the full-width tiles win again.
     constexpr int kNarrow = 64;
-    if (static_cast<int64_t>(m_tiles) * n_tiles <= sm_count() / 4 && narrow_tiles_enabled()) {
-        e = make_tmap(&tb, dt, 2, w, n, k, kNarrow);
-        if (e != cudaSuccess) return e;
-        SchedGemm::Params sp{m_tiles, static_cast<int>(ceil_div64(n, kNarrow)), m_tiles};
-        const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
-        return launch<false, SchedGemm, EpiBias<T>, kNarrow>(ta, tb, sp, ep, k, ptx::instr_desc(fmt, fmt, kBM, kNarrow),
-                                                             static_cast<int>(tiles < sm_count() ? tiles : sm_count()), s);
+    const int64_t wide_tiles = static_cast<int64_t>(m_tiles) * n_tiles;
+    if (wide_tiles <= sm_count() / 2 && narrow_tiles_enabled()) {
+        const int n_narrow = static_cast<int>(ceil_div64(n, kNarrow));
+        const int splits = splitk_enabled() ? splitk_factor(static_cast<int64_t>(m_tiles) * n_narrow,
+                                                            static_cast<int>(ceil_div64(k, 64))) : 1;
+        if (splits > 1 || wide_tiles <= sm_count() / 4) {
+            e = make_tmap(&tb, dt, 2, w, n, k, kNarrow);
+            if (e != cudaSuccess) return e;
+            const uint32_t idesc = ptx::instr_desc(fmt, fmt, kBM, kNarrow);
+            if (splits > 1)
+                return launch_splitk<T>(ta, tb, ep.bias, ep.y, m, n, m_tiles, n_narrow, k, idesc, ep.vec_ok, splits, s);
+            SchedGemm::Params sp{m_tiles, n_narrow, m_tiles};
+            const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
+            return launch<false, SchedGemm, EpiBias<T>, kNarrow>(ta, tb, sp, ep, k, idesc,
+                                                                 static_cast<int>(tiles < sm_count() ? tiles : sm_count()), s);
+        }
     }
     const bool pair = m_tiles >= 2 && pair_kernels_enabled() && max_pairs<false, SchedGemm, EpiBias<T>>() > 0;
     e = make_tmap(&tb, dt, 2, w, n, k, pair ? 128 : kBN);     // a CTA of a pair loads half of the B tile

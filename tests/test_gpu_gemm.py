@@ -69,6 +69,54 @@ def test_small_m_narrow_tiles_match_oracle(shape):
     assert device_status_clean(y)
 
 
+def test_row_and_column_shards_are_bitwise_slices_of_the_whole_at_small_sizes():
+    """The default kernels (full-width and 128 x 64 tiles) add a row's products in one order
+    whatever the problem size: shards reproduce the whole exactly."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(768, 1024, generator=g).to(torch.bfloat16).to(DEV)
+    w = (0.05 * torch.randn(1536, 1024, generator=g)).to(torch.bfloat16).to(DEV)
+    whole = matmul_add_bias(x, w)
+    assert torch.equal(matmul_add_bias(x[:128].contiguous(), w), whole[:128])
+    assert torch.equal(matmul_add_bias(x[300:316].contiguous(), w), whole[300:316])
+    assert torch.equal(matmul_add_bias(x, w[512:1024].contiguous()), whole[:, 512:1024])
+
+
+_SPLITK_CHILD = r"""
+import torch
+from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+from custom_cuda_kernals_b200 import _native
+dev = torch.device("cuda", 0)
+for (m, k, n) in [(128, 4096, 4096), (16, 4096, 4096), (256, 1024, 4096), (100, 512, 1000), (128, 4096, 72),
+                  (1, 8192, 4096), (128, 11008, 4096), (77, 4096, 520)]:
+    g = torch.Generator().manual_seed(m + k + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    b = (0.02 * torch.randn(n, generator=g)).to(torch.bfloat16)
+    y = matmul_add_bias(x.to(dev), w.to(dev), b.to(dev))
+    exact = x.double() @ w.double().T + b.double()
+    err = (y.cpu().double() - exact).abs().max().item()
+    assert err <= 2 ** -8 * exact.abs().max().item() + 1e-3, (m, k, n, err)
+    again = matmul_add_bias(x.to(dev), w.to(dev), b.to(dev))
+    assert torch.equal(y, again), "split-K must be deterministic"
+    y16 = matmul_add_bias(x.to(dev).half(), w.to(dev).half(), None)
+    assert (y16.cpu().double() - x.half().double() @ w.half().double().T).abs().max().item() <= 2e-2
+assert _native.take_device_status(y) == 0
+print("SPLITK_OK")
+"""
+
+
+def test_cluster_split_k_mode_matches_fp64_and_is_deterministic():
+    """CCK_GEMM_SPLITK=1 (read once per process, so a child process): decode-sized problems run
+    on clusters of 2-8 CTAs per tile that split K and reduce through distributed shared memory."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, CCK_GEMM_SPLITK="1", PYTHONPATH=os.pathsep.join([os.getcwd(), os.environ.get("PYTHONPATH", "")]))
+    out = subprocess.run([sys.executable, "-c", _SPLITK_CHILD], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "SPLITK_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
 def test_matmul_identity_is_exact():
     """x @ I + 0 reproduces x bit for bit (every product is exact, one addend per sum)."""
     from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
