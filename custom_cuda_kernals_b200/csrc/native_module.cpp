@@ -694,16 +694,21 @@ void lce_dlogits_from_logits(const at::Tensor& logits, const at::Tensor& targets
     const int32_t dt = tag_of("dlogits", dlogits);
     if (dt != CCK_BF16 && dt != CCK_F16)
         value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
-    expect_same_dtype("dlogits_t", tag_of("dlogits_t", dlogits_t), dt);
+    // dlogits_t may be a column range of a wider row-major matrix (the transposes of several row
+    // chunks side by side): rows are stride(0) apart, elements within a row adjacent
+    if (!dlogits_t.is_cuda()) value_error("argument 'dlogits_t' must be a CUDA tensor");
+    if (dlogits_t.scalar_type() != dlogits.scalar_type())
+        value_error("dtype mismatch: 'dlogits_t' must have dlogits' dtype");
     if (logits.dim() != 2) value_error("shape mismatch: logits must be 2-D; got " + shape_str(logits));
     const int64_t n = logits.size(0), v = logits.size(1);
     if (targets.numel() != n || lse.numel() != n)
         value_error("shape mismatch: targets and lse must have " + std::to_string(n) + " elements");
     if (dlogits.dim() != 2 || dlogits.size(0) != n || dlogits.size(1) != v)
         value_error("shape mismatch: dlogits shape " + shape_str(dlogits) + " must be " + shape_str(logits));
-    if (dlogits_t.dim() != 2 || dlogits_t.size(0) != v || dlogits_t.size(1) < n || dlogits_t.size(1) % 4 != 0)
+    if (dlogits_t.dim() != 2 || dlogits_t.size(0) != v || dlogits_t.size(1) < n || dlogits_t.stride(1) != 1 ||
+        dlogits_t.stride(0) < dlogits_t.size(1) || dlogits_t.stride(0) % 4 != 0 || dlogits_t.storage_offset() % 4 != 0)
         value_error("shape mismatch: dlogits_t shape " + shape_str(dlogits_t) + " must be [" + std::to_string(v) +
-                    ", >= " + std::to_string(n) + " and a multiple of 4]");
+                    ", >= " + std::to_string(n) + "] with unit inner stride, and a row pitch and offset that are multiples of 4");
     if (v % 4 != 0) value_error("shape mismatch: the vocabulary size must be a multiple of 4");
     Launch l(logits, {&targets, &lse, &dlogits, &dlogits_t});
     check_launch("launch_lce_dlogits_from_logits",
@@ -711,7 +716,7 @@ void lce_dlogits_from_logits(const at::Tensor& logits, const at::Tensor& targets
                                                 static_cast<const int64_t*>(targets.data_ptr()),
                                                 static_cast<const float*>(lse.data_ptr()), n, v, ignore_index,
                                                 static_cast<float>(grad_scale), dlogits.data_ptr(),
-                                                dlogits_t.data_ptr(), dlogits_t.size(1), dt, l.stream));
+                                                dlogits_t.data_ptr(), dlogits_t.stride(0), dt, l.stream));
 }
 
 void transpose_2byte(const at::Tensor& in, const at::Tensor& out) {

@@ -123,6 +123,9 @@ def lce_grad_scale(targets: torch.Tensor, ignore_index: int, reduction: str) -> 
     return 1.0 / valid if valid else float("nan")
 
 
+_DLT_BYTES_MAX = 16 << 30
+
+
 def _padded_transpose(x: torch.Tensor, width: int | None = None) -> torch.Tensor:
     """``x.T`` as a contiguous ``[cols, width]`` tensor (``width >= rows``, a multiple of 4),
     zero-filled beyond ``x``'s rows."""
@@ -164,7 +167,16 @@ def lce_stats_and_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets:
     w_t = weight_t if weight_t is not None else _padded_transpose(weight)             # [H, V]
     d_hidden = torch.empty_like(hidden)
     one_chunk = n <= rows_per_chunk
-    d_weight = torch.empty(v, h, dtype=dt, device=dev) if one_chunk else torch.zeros(v, h, dtype=torch.float32, device=dev)
+    n_pad = (n + 7) // 8 * 8
+    # Weight gradient: with the transposed dlogits of every chunk side by side ([V, N], 2*V*N
+    # bytes) it is ONE contraction over all N rows, written directly in the storage type; beyond
+    # _DLT_BYTES_MAX the chunks are contracted one at a time into an fp32 accumulator instead.
+    side_by_side = not recompute and rows_per_chunk % 8 == 0 and v * n_pad * hidden.element_size() <= _DLT_BYTES_MAX
+    if side_by_side:
+        dl_t_all = (torch.empty if n_pad == n else torch.zeros)(v, n_pad, dtype=dt, device=dev)
+        d_weight = torch.empty(v, h, dtype=dt, device=dev)
+    else:
+        d_weight = torch.empty(v, h, dtype=dt, device=dev) if one_chunk else torch.zeros(v, h, dtype=torch.float32, device=dev)
     rows_max = min(n, rows_per_chunk)
     logits = None if recompute else torch.empty(rows_max, v, dtype=torch.float32, device=dev)
     dl_buf = torch.empty(rows_max, v, dtype=dt, device=dev)
@@ -185,16 +197,23 @@ def lce_stats_and_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets:
             _native.lce_dlogits_fwd(hc, weight, local[r0:r1], lse, ignore_index, grad_scale, dl)
             dl_t = _padded_transpose(dl, width)
         else:
-            dl_t = (torch.empty if width == rows else torch.zeros)(v, width, dtype=dt, device=dev)
+            if side_by_side:
+                dl_t = dl_t_all[:, r0:r0 + width]
+            else:
+                dl_t = (torch.empty if width == rows else torch.zeros)(v, width, dtype=dt, device=dev)
             _native.lce_dlogits_from_logits(logits[:rows], local[r0:r1], lse, ignore_index, grad_scale, dl, dl_t)
         _native.matmul_add_bias_fwd(dl, w_t, None, d_hidden[r0:r1])                # [r, V] x [H, V]^T
+        if side_by_side:
+            continue
         hc_t = _padded_transpose(hc, width)
         if one_chunk:
             _native.matmul_add_bias_fwd(dl_t, hc_t, None, d_weight)                # [V, r] x [H, r]^T
         else:
             _native.matmul_accumulate_f32_fwd(dl_t, hc_t, d_weight)
+    if side_by_side:
+        _native.matmul_add_bias_fwd(dl_t_all, _padded_transpose(hidden, n_pad), None, d_weight)   # [V, N] x [H, N]^T
     stats_all = stats_parts[0] if one_chunk else torch.cat(stats_parts, dim=2)
-    return stats_all, d_hidden, d_weight if one_chunk else d_weight.to(dt)
+    return stats_all, d_hidden, d_weight if d_weight.dtype == dt else d_weight.to(dt)
 
 
 def linear_cross_entropy_fwd_bwd(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor,
@@ -205,8 +224,10 @@ def linear_cross_entropy_fwd_bwd(hidden: torch.Tensor, weight: torch.Tensor, tar
     of 1) - what the reference names as its missing piece (custom_cuda/kernels/
     linear_cross_entropy.py:11-18).  float16/bfloat16, ``H`` and ``V`` multiples of 8.
 
-    See ``lce_stats_and_gradients``; scratch memory is ``rows_per_chunk * V * 8`` bytes (fp32
-    logits, dlogits and its transpose), ``* 4`` with ``recompute``.  ``weight_t`` may pass a
+    See ``lce_stats_and_gradients``; scratch memory is ``rows_per_chunk * V * 6`` bytes (fp32
+    logits and dlogits of a chunk) plus ``2 * N * V`` for the transposed dlogits of all rows
+    (capped at 16 GiB, beyond which it is per chunk again); ``rows_per_chunk * V * 4`` with
+    ``recompute``.  ``weight_t`` may pass a
     cached ``weight.T.contiguous()``.  Returns ``(loss, d_hidden, d_weight)``."""
     scale = lce_grad_scale(targets, ignore_index, reduction)
     stats, d_hidden, d_weight = lce_stats_and_gradients(hidden, weight, targets, scale, 0, ignore_index,

@@ -141,3 +141,36 @@ def test_dispatch_round_trip_full_size():
     assert torch.equal(rows, x[perm])
     back = token_combine(rows, unperm, w)
     torch.testing.assert_close(back.float(), x.float(), rtol=2 ** -7, atol=1e-6)
+
+
+def test_gather_and_combine_reject_what_the_reference_rejects():
+    src = torch.randn(8, 16, device=DEV)
+    idx = torch.zeros(4, dtype=torch.long, device=DEV)
+    with pytest.raises(ValueError):
+        token_gather(torch.randn(8, 16), torch.zeros(4, dtype=torch.long))       # CPU tensors
+    with pytest.raises(ValueError):
+        token_gather(src, idx.int())                                              # indices not int64
+    with pytest.raises(ValueError):
+        token_gather(src.t(), idx)                                                # not contiguous
+    rows = torch.randn(8, 16, device=DEV, dtype=torch.bfloat16)
+    u = torch.arange(8, device=DEV).reshape(4, 2)
+    with pytest.raises(ValueError):
+        token_combine(rows, u, torch.rand(4, 2, device=DEV, dtype=torch.bfloat16))   # weights must be float32
+    with pytest.raises(ValueError):
+        token_combine(rows, u, torch.rand(4, 3, device=DEV))                      # weights shape
+    from custom_cuda_kernals_b200 import _native
+    with pytest.raises(ValueError):
+        _native.token_combine_fwd(rows, u, torch.rand(4, 2, device=DEV), torch.empty(4, 16, device=DEV))  # dtype mismatch
+
+
+@pytest.mark.parametrize("hidden", [8, 24, 100, 257, 4096 + 8])
+def test_combine_vector_tail_and_scalar_fallback(hidden):
+    """Row widths around the vector width: whole vectors, ragged (scalar path), and a slab that
+    is only partly filled (reference: test_combine_vectorization_tail_and_fallback_path)."""
+    g = torch.Generator().manual_seed(hidden)
+    rows = torch.randn(60, hidden, generator=g).to(torch.bfloat16)
+    u = torch.randperm(60, generator=g).reshape(20, 3)
+    w = torch.rand(20, 3, generator=g)
+    got = token_combine(*to_dev(rows, u, w))
+    check(got.cpu(), ops.token_combine(rows, u, w), torch.bfloat16, ROUTER_TOL)
+    assert torch.equal(token_gather(rows.to(DEV), u.reshape(-1).to(DEV)).cpu(), rows[u.reshape(-1)])
