@@ -481,7 +481,7 @@ def base_line(args, world, value, ms):
     return {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "Llama-3-8B decoder block forward, batch 8 x seq 2048 (BASELINE configs[3])",
+            "config": {"workload": "Llama-3-8B decoder block forward, batch 8 x seq 2048",
                        "global_batch": BATCH, "seq_len": SEQ, "hidden": CFG["hidden"], "ffn": CFG["ffn"],
                        "heads": "32q/8kv x 128", "parallelism": f"token-dp{world} (sequences sharded, weights replicated)",
                        "l2": "working set (436 MB weights + >1 GB activations) exceeds the 126 MB L2"}}

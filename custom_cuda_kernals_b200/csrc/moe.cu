@@ -192,9 +192,11 @@ token_gather_scalar_kernel(const T* __restrict__ src, const int64_t* __restrict_
     }
 }
 
+// One warp per row up to 64 waves of CTAs (the hardware hands out CTAs as SMs free up, which
+// balances better than a fixed number of rows per warp); beyond that the warps loop.
 inline unsigned warp_grid(int64_t rows) {
     const int64_t ctas = ceil_div64(rows, kGatherThreads / 32);
-    const int64_t cap = static_cast<int64_t>(kNumSMs) * 8;
+    const int64_t cap = static_cast<int64_t>(kNumSMs) * 8 * 64;
     return static_cast<unsigned>(ctas < cap ? ctas : cap);
 }
 
