@@ -87,7 +87,8 @@ moe_router_kernel(const T* __restrict__ logits, float* __restrict__ topk_w, int6
         int best_e;
         if constexpr (L == 32) {
             // whole warp: one integer max-reduction on an order-preserving key, one ballot for
-            // the owner, one shuffle for the owner's slot - instead of ten shuffles
+            // the owner, one shuffle for the owner's slot - instead of ten shuffles.  (Sub-warp
+            // groups keep the butterfly: redux.sync with one mask per group measured slower.)
             const uint32_t bits = __float_as_uint(best);
             const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
             const uint32_t top = __reduce_max_sync(0xffffffffu, key);
@@ -229,6 +230,9 @@ token_combine_vec_kernel(const T* __restrict__ expert_out, const int64_t* __rest
     for (int64_t token = static_cast<int64_t>(blockIdx.x) * (kCombineMaxThreads / 32) + (threadIdx.x >> 5);
          token < n_tokens; token += warps) {
         Vec16* out = reinterpret_cast<Vec16*>(combined) + token * n_vec;
+        // the first 32 (index, weight) pairs are fetched once per token, not once per slab
+        const int64_t first_row = lane < k ? __ldg(uidx + token * k + lane) : 0;
+        const float first_w = lane < k ? __ldg(weights + token * k + lane) : 0.0f;
         for (int64_t slab = 0; slab < n_vec; slab += 32 * kCombineVpt) {     // warp-uniform: every lane shuffles
             const int64_t i0 = slab + lane;
             float acc[kCombineVpt][kPer];
@@ -238,8 +242,8 @@ token_combine_vec_kernel(const T* __restrict__ expert_out, const int64_t* __rest
                 for (int e = 0; e < kPer; ++e) acc[u][e] = 0.0f;
             for (int j0 = 0; j0 < k; j0 += 32) {
                 const int mine = j0 + lane;
-                const int64_t my_row = mine < k ? __ldg(uidx + token * k + mine) : 0;
-                const float my_w = mine < k ? __ldg(weights + token * k + mine) : 0.0f;
+                const int64_t my_row = j0 == 0 ? first_row : (mine < k ? __ldg(uidx + token * k + mine) : 0);
+                const float my_w = j0 == 0 ? first_w : (mine < k ? __ldg(weights + token * k + mine) : 0.0f);
                 const int in_chunk = k - j0 < 32 ? k - j0 : 32;
                 for (int c = 0; c < in_chunk; c += 2) {
                     const bool two = c + 1 < in_chunk;
