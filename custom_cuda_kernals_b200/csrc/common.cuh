@@ -157,4 +157,13 @@ __host__ __device__ constexpr int64_t ceil_div64(int64_t a, int64_t b) { return 
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Function attributes (dynamic shared memory limit) and occupancy figures belong to a
+// (function, device) pair: per-instantiation caches are indexed by the current device.
+constexpr int kMaxDevices = 64;
+inline int current_device_slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+}
+
 }  // namespace cck

@@ -422,11 +422,13 @@ cudaError_t run_block(const void* x, uint8_t* codes, float* scale, int64_t m, in
         if (r == CUDA_SUCCESS && st != nullptr) {
             constexpr int kSmem = kTile * kTile * static_cast<int>(sizeof(T));
             auto kern = fp8_block_tma_kernel<T, E5M2>;
-            static bool configured = false;
-            if (!configured) {
+            static bool configured[kMaxDevices] = {};
+            const int slot = current_device_slot();
+            if (slot < 0) return cudaErrorInvalidDevice;
+            if (!configured[slot]) {
                 cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
                 if (e != cudaSuccess) return e;
-                configured = true;
+                configured[slot] = true;
             }
             kern<<<grid, kTmaThreads, kSmem, s>>>(map, codes, scale, m, n, st);
             return cudaGetLastError();

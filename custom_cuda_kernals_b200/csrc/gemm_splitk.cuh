@@ -225,11 +225,13 @@ cudaError_t launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const T*
                           int m_tiles, int n_tiles, int64_t k_elems, uint32_t idesc, int vec_ok, int splits,
                           cudaStream_t s) {
     auto kern = gemm_splitk_kernel<T>;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[kMaxDevices] = {};
+    const int slot = current_device_slot();
+    if (slot < 0) return cudaErrorInvalidDevice;
+    if (!configured[slot]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemBytes);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured[slot] = true;
     }
     unsigned int* st = status_word();
     if (!st) return cudaErrorMemoryAllocation;

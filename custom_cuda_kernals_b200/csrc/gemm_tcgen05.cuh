@@ -517,11 +517,13 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const typename 
                    const typename Epi::Params& ep, int64_t k_elems, uint32_t idesc, int ctas, cudaStream_t s) {
     auto kern = gemm_kernel<kFp8, Sched, Epi, BN>;
     constexpr int kSmemBytes = TileShape<BN>::kSmemBytesN;
-    static bool configured = false;   // per instantiation
-    if (!configured) {
+    static bool configured[kMaxDevices] = {};   // per instantiation and device
+    const int slot = current_device_slot();
+    if (slot < 0) return cudaErrorInvalidDevice;
+    if (!configured[slot]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured[slot] = true;
     }
     unsigned int* st = status_word();
     if (!st) return cudaErrorMemoryAllocation;
@@ -534,7 +536,10 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const typename 
 // Number of CTA pairs that can be resident at once (at most one pair per TPC).
 template <bool kFp8, class Sched, class Epi>
 int max_pairs() {
-    static int cached = 0;
+    static int cached_per_device[kMaxDevices] = {};
+    const int slot = current_device_slot();
+    if (slot < 0) return 0;
+    int& cached = cached_per_device[slot];
     if (cached > 0) return cached;
     auto kern = gemm_pair_kernel<kFp8, Sched, Epi>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess) return 0;

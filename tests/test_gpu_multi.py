@@ -85,3 +85,33 @@ def test_two_ranks_match_single_gpu(tmp_path):
         torch.testing.assert_close(o["loss"], o["single"], rtol=1e-6, atol=1e-6)
         assert o["rows_equal"] and o["gemm_equal"] and o["block_equal"] and o["grads_ok"]
     assert torch.equal(outs[0]["loss"], outs[1]["loss"])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_one_process_drives_two_devices():
+    """A single process that uses the library on cuda:0 and then on cuda:1: every launch runs
+    on the device that owns its tensors (kernel attributes such as the dynamic shared memory
+    limit are per device), and both devices give the same bits."""
+    from custom_cuda_kernals_b200 import _native
+    from custom_cuda_kernals_b200.kernels.autograd import rmsnorm_residual_backward
+    from custom_cuda_kernals_b200.kernels.fp8_quant import fp8_quant
+    from custom_cuda_kernals_b200.kernels.linear_cross_entropy import linear_cross_entropy
+    from custom_cuda_kernals_b200.kernels.matmul_add_bias import matmul_add_bias
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(512, 1024, generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(2048, 1024, generator=g)).to(torch.bfloat16)
+    small = torch.randn(64, 1024, generator=g).to(torch.bfloat16)
+    t = torch.randint(0, 2048, (512,), generator=g)
+    outs = []
+    for d in (0, 1):
+        dev = torch.device("cuda", d)
+        xd, wd, sd, td = x.to(dev), w.to(dev), small.to(dev), t.to(dev)
+        y = matmul_add_bias(xd, wd)                       # CTA-pair kernel
+        ys = matmul_add_bias(sd, wd)                      # narrow-tile kernel
+        codes, scale = fp8_quant(xd, "e4m3", "block")     # TMA-staged kernel (dynamic shared memory)
+        loss = linear_cross_entropy(xd, wd, td)
+        dx, dw = rmsnorm_residual_backward(xd, None, xd, torch.ones(1024, dtype=torch.bfloat16, device=dev), 1e-5)
+        assert y.device == dev and _native.take_device_status(y) == 0
+        outs.append([o.cpu() for o in (y, ys, codes.view(torch.uint8), scale, loss, dx, dw)])
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
