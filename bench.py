@@ -633,7 +633,8 @@ def run_ours(args, rank, world, local):
         emit(line)
 
 
-PROFILE_CASES = ("gemm", "gemm_fp8", "lce", "lce_dlogits", "swiglu", "rmsnorm", "rope", "fp8_token", "fp8_block")
+PROFILE_CASES = ("gemm", "gemm_fp8", "lce", "lce_dlogits", "swiglu", "rmsnorm", "rope", "fp8_token", "fp8_block",
+                 "swiglu_bwd", "rmsnorm_bwd", "moe_router", "token_gather", "token_combine")
 
 
 def run_profile_case(name, launches=3):
@@ -671,6 +672,27 @@ def run_profile_case(name, launches=3):
         lse = torch.logsumexp(lg, dim=1)
         dl, dl_t = torch.empty(2048, 32064, dtype=bf, device=dev), torch.empty(32064, 2048, dtype=bf, device=dev)
         fn = lambda: _native.lce_dlogits_from_logits(lg, t, lse, -100, 1.0 / 2048, dl, dl_t)
+    elif name == "swiglu_bwd":   # 5 x 59 MB
+        from custom_cuda_kernals_b200.kernels.autograd import swiglu_backward
+        a, b, c = rn(2048, 14336), rn(2048, 14336), rn(2048, 14336)
+        fn = lambda: swiglu_backward(a, b, c)
+    elif name == "rmsnorm_bwd":  # 16384 x 4096 bf16: 4 x 134 MB
+        from custom_cuda_kernals_b200.kernels.autograd import rmsnorm_residual_backward
+        dy, dro, ro, w = rn(16384, 4096), rn(16384, 4096), rn(16384, 4096), rn(4096)
+        fn = lambda: rmsnorm_residual_backward(dy, dro, ro, w, 1e-5)
+    elif name == "moe_router":   # 262144 tokens x 256 experts bf16: 134 MB of logits
+        from custom_cuda_kernals_b200.kernels.moe_router import moe_router
+        lg = rn(262144, 256)
+        fn = lambda: moe_router(lg, 8)
+    elif name in ("token_gather", "token_combine"):   # 32768 rows x 4096 bf16 from 16384 tokens (top-2)
+        from custom_cuda_kernals_b200.kernels.token_permute import compute_permutation, token_combine, token_gather
+        x = rn(16384, 4096)
+        perm, unperm = compute_permutation(torch.randint(0, 8, (16384, 2), device=dev))
+        if name == "token_gather":
+            fn = lambda: token_gather(x, perm)
+        else:
+            rows, wts = token_gather(x, perm), torch.rand(16384, 2, device=dev)
+            fn = lambda: token_combine(rows, unperm, wts)
     elif name == "swiglu":      # config 2a at 1/4 of the rows: 3 x 59 MB
         a, b = rn(2048, 14336), rn(2048, 14336)
         fn = lambda: swiglu(a, b)
