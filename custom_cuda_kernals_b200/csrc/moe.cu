@@ -8,7 +8,8 @@
 //     8 * L >= experts, each lane holding 8 logits in registers - 8 experts is one THREAD per
 //     token with a single 16-byte load, 256 experts a full warp.  Softmax statistics run on
 //     xor-shuffles inside the group; each of the k arg-max rounds is one integer max-reduction
-//     (redux.sync) + ballot + shuffle when the group is a whole warp, a shuffle butterfly
+//     (redux.sync) when the group is a whole warp - on a packed (value, expert) key for 16-bit
+//     logits, on the value followed by a ballot and a shuffle for fp32 - and a shuffle butterfly
 //     otherwise; ties go to the lower expert id.
 //   * gather: warps walk destination rows; a lane keeps four 16-byte vectors in flight and the
 //     next row's index is fetched while the current row streams.
@@ -25,6 +26,19 @@ namespace {
 // ------------------------------------------------------------------ router
 constexpr int kRouterVals = 8;       // logits per lane
 constexpr int kRouterThreads = 256;
+
+// The 16 bits a 16-bit storage type holds for `f` (exact: `f` was read from that type), and back.
+template <typename T> struct Bits16;
+template <> struct Bits16<__nv_bfloat16> {
+    __device__ static __forceinline__ uint32_t of(float f) { return __float_as_uint(f) >> 16; }
+    __device__ static __forceinline__ float to_float(uint32_t b) { return __uint_as_float(b << 16); }
+};
+template <> struct Bits16<__half> {
+    __device__ static __forceinline__ uint32_t of(float f) { return __half_as_ushort(__float2half_rn(f)); }
+    __device__ static __forceinline__ float to_float(uint32_t b) {
+        return __half2float(__ushort_as_half(static_cast<unsigned short>(b)));
+    }
+};
 
 template <typename T, int L>
 __global__ void __launch_bounds__(kRouterThreads)
@@ -71,52 +85,83 @@ moe_router_kernel(const T* __restrict__ logits, float* __restrict__ topk_w, int6
     for (int o = L / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float inv_sum = 1.0f / sum;
 
-    // k rounds of arg-max; a selected logit is replaced by -inf in its owner's registers.
-    // Equal logits go to the lower expert id: strict '>' keeps the first of a lane's values,
-    // and across lanes the lower lane (= lower ids) wins.
     float picked = 0.0f;                        // sum of the selected probabilities
-    for (int j = 0; j < k; ++j) {
-        float best = v[0];
-        int best_i = 0;
+    if constexpr (L == 32 && sizeof(T) == 2) {
+        // 16-bit logits, whole warp per token: value and expert id fit one 32-bit key - the value's
+        // bits made order-preserving in the high half, 255 - expert in the low byte, so that a
+        // plain unsigned max picks the largest logit and, among equals, the lowest expert.  A
+        // round is then 7 max ops, one redux.sync and 8 compare-and-clear ops; keys are unique.
+        uint32_t key[kRouterVals];
 #pragma unroll
-        for (int i = 1; i < kRouterVals; ++i)
-            if (v[i] > best) {
-                best = v[i];
-                best_i = i;
+        for (int i = 0; i < kRouterVals; ++i) {
+            const int e = sub * kRouterVals + i;
+            const uint32_t b = Bits16<T>::of(v[i]);
+            const uint32_t ord = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
+            key[i] = e < experts ? ((ord << 16) | static_cast<uint32_t>(255 - e)) : 0u;
+        }
+        for (int j = 0; j < k; ++j) {
+            uint32_t local = key[0];
+#pragma unroll
+            for (int i = 1; i < kRouterVals; ++i) local = max(local, key[i]);
+            const uint32_t top = __reduce_max_sync(0xffffffffu, local);
+#pragma unroll
+            for (int i = 0; i < kRouterVals; ++i) key[i] = key[i] == top ? 0u : key[i];
+            const uint32_t ord = top >> 16;
+            const float best = Bits16<T>::to_float((ord & 0x8000u) ? (ord & 0x7fffu) : (~ord & 0xffffu));
+            const float p = __expf(best - mx) * inv_sum;
+            picked += p;
+            if (live && sub == j % L) {
+                topk_w[token * k + j] = p;
+                topk_i[token * k + j] = 255 - static_cast<int>(top & 0xffu);
             }
-        int best_e;
-        if constexpr (L == 32) {
-            // whole warp: one integer max-reduction on an order-preserving key, one ballot for
-            // the owner, one shuffle for the owner's slot - instead of ten shuffles.  (Sub-warp
-            // groups keep the butterfly: redux.sync with one mask per group measured slower.)
-            const uint32_t bits = __float_as_uint(best);
-            const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
-            const uint32_t top = __reduce_max_sync(0xffffffffu, key);
-            const int owner = __ffs(__ballot_sync(0xffffffffu, key == top)) - 1;
-            best_e = owner * kRouterVals + __shfl_sync(0xffffffffu, best_i, owner);
-            best = __uint_as_float((top & 0x80000000u) ? (top & 0x7fffffffu) : ~top);
-        } else {
-            best_e = sub * kRouterVals + best_i;
-#pragma unroll
-            for (int o = L / 2; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                if (ov > best || (ov == best && oe < best_e)) {
-                    best = ov;
-                    best_e = oe;
+        }
+    } else {
+        // k rounds of arg-max; a selected logit is replaced by -inf in its owner's registers.
+        // Equal logits go to the lower expert id: strict '>' keeps the first of a lane's values,
+        // and across lanes the lower lane (= lower ids) wins.
+        for (int j = 0; j < k; ++j) {
+            float best = v[0];
+            int best_i = 0;
+    #pragma unroll
+            for (int i = 1; i < kRouterVals; ++i)
+                if (v[i] > best) {
+                    best = v[i];
+                    best_i = i;
+                }
+            int best_e;
+            if constexpr (L == 32) {
+                // whole warp: one integer max-reduction on an order-preserving key, one ballot for
+                // the owner, one shuffle for the owner's slot - instead of ten shuffles.  (Sub-warp
+                // groups keep the butterfly: redux.sync with one mask per group measured slower.)
+                const uint32_t bits = __float_as_uint(best);
+                const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+                const uint32_t top = __reduce_max_sync(0xffffffffu, key);
+                const int owner = __ffs(__ballot_sync(0xffffffffu, key == top)) - 1;
+                best_e = owner * kRouterVals + __shfl_sync(0xffffffffu, best_i, owner);
+                best = __uint_as_float((top & 0x80000000u) ? (top & 0x7fffffffu) : ~top);
+            } else {
+                best_e = sub * kRouterVals + best_i;
+    #pragma unroll
+                for (int o = L / 2; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                    if (ov > best || (ov == best && oe < best_e)) {
+                        best = ov;
+                        best_e = oe;
+                    }
                 }
             }
-        }
-        if (best_e / kRouterVals == sub) {
-#pragma unroll
-            for (int i = 0; i < kRouterVals; ++i)
-                if (i == best_e % kRouterVals) v[i] = -INFINITY;
-        }
-        const float p = __expf(best - mx) * inv_sum;
-        picked += p;
-        if (live && sub == j % L) {
-            topk_w[token * k + j] = p;
-            topk_i[token * k + j] = best_e;
+            if (best_e / kRouterVals == sub) {
+    #pragma unroll
+                for (int i = 0; i < kRouterVals; ++i)
+                    if (i == best_e % kRouterVals) v[i] = -INFINITY;
+            }
+            const float p = __expf(best - mx) * inv_sum;
+            picked += p;
+            if (live && sub == j % L) {
+                topk_w[token * k + j] = p;
+                topk_i[token * k + j] = best_e;
+            }
         }
     }
     if (renormalize && live) {
