@@ -82,6 +82,26 @@ def test_row_and_column_shards_are_bitwise_slices_of_the_whole_at_small_sizes():
     assert torch.equal(matmul_add_bias(x, w[512:1024].contiguous()), whole[:, 512:1024])
 
 
+def test_large_problem_rows_do_not_depend_on_how_many_rows_are_computed_together():
+    """8192 x 512 x 1792 (224 CTA-pair tiles, a ragged last wave) equals, bit for bit, the same
+    rows computed as two 4096-row problems, and matches the oracle; ragged edges included."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(8192, 512, generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(1792, 512, generator=g)).to(torch.bfloat16)
+    b = (0.05 * torch.randn(1792, generator=g)).to(torch.bfloat16)
+    xd, wd, bd = to_dev(x, w, b)
+    y = matmul_add_bias(xd, wd, bd)
+    halves = torch.cat([matmul_add_bias(xd[:4096].contiguous(), wd, bd), matmul_add_bias(xd[4096:].contiguous(), wd, bd)])
+    assert torch.equal(y, halves)
+    check(y[:1024], ops.matmul_add_bias(x[:1024], w, b), torch.bfloat16, ops.TOLERANCE_GEMM)
+    check(y[-512:], ops.matmul_add_bias(x[-512:], w, b), torch.bfloat16, ops.TOLERANCE_GEMM)
+    # ragged edges: 8000 rows, 1800 columns
+    y2 = matmul_add_bias(xd[:8000].contiguous(), torch.cat([wd, wd[:8]]), torch.cat([bd, bd[:8]]))
+    assert torch.equal(y2[:, :1792], y[:8000]) and torch.equal(y2[:, 1792:], y[:8000, :8])
+    assert device_status_clean(y)
+
+
 _SPLITK_CHILD = r"""
 import torch
 from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
