@@ -20,6 +20,8 @@
 // baselines/token_permute.py:196-226.
 #include "common.cuh"
 
+namespace cck { namespace tc { unsigned int* status_word(); } }   // matmul_add_bias.cu: the per-device status word
+
 namespace cck {
 namespace {
 
@@ -356,6 +358,85 @@ cudaError_t run_combine(const void* expert_out, const int64_t* uidx, const float
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ expert-parallel row exchange
+// The same two row movers with one level of indirection: the destination (dispatch) or the
+// source (combine) of a row is (rank, row) - a base pointer out of a table of `world` buffers,
+// which in a multi-GPU run are the ranks' receive buffers mapped into this process (peer
+// memory over NVLink), plus a row index.  The kernels only push or pull: nothing in them waits
+// for another GPU; the caller separates the phases with stream-ordered barriers.  Every
+// (rank, row) is checked against the table size and the buffers' capacity; a row that fails the
+// check is skipped and bit 2 of the status word is set, so a wrong plan cannot fault a GPU.
+constexpr unsigned int kStatusBadRoute = 4u;
+
+__global__ void __launch_bounds__(kGatherThreads)
+token_dispatch_kernel(const Vec16* __restrict__ src, const int64_t* __restrict__ src_row,
+                      const int64_t* __restrict__ dst_rank, const int64_t* __restrict__ dst_row,
+                      const int64_t* __restrict__ dst_bases, int world, int64_t capacity_rows, int64_t n_src_rows,
+                      int64_t n, int64_t n_vec, unsigned int* status) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (kGatherThreads / 32);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * (kGatherThreads / 32) + (threadIdx.x >> 5); i < n; i += warps) {
+        const int64_t from = src_row[i], rank = dst_rank[i], to = dst_row[i];
+        if (from < 0 || from >= n_src_rows || rank < 0 || rank >= world || to < 0 || to >= capacity_rows) {
+            if (lane == 0) atomicOr(status, kStatusBadRoute);
+            continue;
+        }
+        const Vec16* s = src + from * n_vec;
+        Vec16* d = reinterpret_cast<Vec16*>(static_cast<uintptr_t>(dst_bases[rank])) + to * n_vec;
+        for (int64_t i0 = lane; i0 < n_vec; i0 += 32 * kGatherUnroll) {
+            Vec16 x[kGatherUnroll];
+#pragma unroll
+            for (int u = 0; u < kGatherUnroll; ++u)
+                if (i0 + 32 * u < n_vec) x[u] = ld_stream(s + i0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < kGatherUnroll; ++u)
+                if (i0 + 32 * u < n_vec) *(d + i0 + 32 * u) = x[u];      // plain store: the target may be peer memory
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kCombineMaxThreads)
+token_combine_remote_kernel(const int64_t* __restrict__ src_bases, int world, int64_t capacity_rows,
+                            const int64_t* __restrict__ src_rank, const int64_t* __restrict__ src_row,
+                            const float* __restrict__ weights, T* __restrict__ combined, int64_t n_tokens, int k,
+                            int64_t n_vec, unsigned int* status) {
+    constexpr int kPer = Store<T>::kPerVec;
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (kCombineMaxThreads / 32);
+    for (int64_t token = static_cast<int64_t>(blockIdx.x) * (kCombineMaxThreads / 32) + (threadIdx.x >> 5);
+         token < n_tokens; token += warps) {
+        Vec16* out = reinterpret_cast<Vec16*>(combined) + token * n_vec;
+        for (int64_t slab = 0; slab < n_vec; slab += 32 * kCombineVpt) {
+            const int64_t i0 = slab + lane;
+            float acc[kCombineVpt][kPer];
+#pragma unroll
+            for (int u = 0; u < kCombineVpt; ++u)
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) acc[u][e] = 0.0f;
+            for (int j = 0; j < k; ++j) {                                  // warp-uniform loads
+                const int64_t rank = __ldg(src_rank + token * k + j), row = __ldg(src_row + token * k + j);
+                const float w = __ldg(weights + token * k + j);
+                if (rank < 0 || rank >= world || row < 0 || row >= capacity_rows) {
+                    if (lane == 0 && slab == 0) atomicOr(status, kStatusBadRoute);
+                    continue;
+                }
+                const Vec16* r = reinterpret_cast<const Vec16*>(static_cast<uintptr_t>(src_bases[rank])) + row * n_vec;
+                Vec16 a[kCombineVpt];
+#pragma unroll
+                for (int u = 0; u < kCombineVpt; ++u)
+                    if (i0 + 32 * u < n_vec) a[u] = *(r + i0 + 32 * u);      // plain load: the source may be peer memory
+#pragma unroll
+                for (int u = 0; u < kCombineVpt; ++u)
+                    if (i0 + 32 * u < n_vec) fma_vec<T>(acc[u], a[u], w);
+            }
+#pragma unroll
+            for (int u = 0; u < kCombineVpt; ++u)
+                if (i0 + 32 * u < n_vec) st_stream(out + i0 + 32 * u, pack<T>(acc[u]));
+        }
+    }
+}
+
 }  // namespace
 }  // namespace cck
 
@@ -414,4 +495,64 @@ extern "C" int32_t launch_token_combine_fwd(const void* expert_output, const int
         case cck::kBF16: return cck::run_combine<__nv_bfloat16>(expert_output, unpermute_index, weights, combined, n_tokens, k, hidden_dim, s);
         default:         return cudaErrorInvalidValue;
     }
+}
+
+// Expert-parallel dispatch: row src[src_row[i]] goes to row dst_row[i] of buffer dst_rank[i] of
+// `dst_bases` (a device array of `world` base addresses - this rank's own receive buffer and its
+// peers' mapped ones), for i < n.  Rows are `hidden_dim` elements of `dtype`; hidden_dim *
+// element size must be a multiple of 16 and every buffer 16-byte aligned.  Routes outside
+// [0, world) x [0, capacity_rows) or source rows outside [0, n_src_rows) are skipped and set bit
+// 2 of the word `cck_take_device_status` returns.  No reference counterpart.
+extern "C" int32_t launch_token_dispatch_fwd(const void* src, const int64_t* src_row, const int64_t* dst_rank,
+                                             const int64_t* dst_row, const int64_t* dst_bases, int64_t world,
+                                             int64_t capacity_rows, int64_t n_src_rows, int64_t n, int64_t hidden_dim,
+                                             int32_t dtype, void* stream) {
+    using namespace cck;
+    if (n <= 0 || hidden_dim <= 0) return cudaSuccess;
+    const int64_t elem = dtype == kF32 ? 4 : ((dtype == kF16 || dtype == kBF16) ? 2 : 0);
+    if (elem == 0 || world <= 0 || world > 1024 || (hidden_dim * elem) % 16 != 0 || !aligned16(src)) return cudaErrorInvalidValue;
+    unsigned int* st = cck::tc::status_word();
+    if (!st) return cudaErrorMemoryAllocation;
+    token_dispatch_kernel<<<warp_grid(n), kGatherThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const Vec16*>(src), src_row, dst_rank, dst_row, dst_bases, static_cast<int>(world), capacity_rows,
+        n_src_rows, n, hidden_dim * elem / 16, st);
+    return cudaGetLastError();
+}
+
+// Expert-parallel combine: combined[t] = sum_j weights[t, j] * row src_row[t, j] of buffer
+// src_rank[t, j] of `src_bases`, fp32 accumulation, one rounding.  Same checks as the dispatch.
+extern "C" int32_t launch_token_combine_remote_fwd(const int64_t* src_bases, int64_t world, int64_t capacity_rows,
+                                                   const int64_t* src_rank, const int64_t* src_row, const float* weights,
+                                                   void* combined, int64_t n_tokens, int64_t k, int64_t hidden_dim,
+                                                   int32_t dtype, void* stream) {
+    using namespace cck;
+    if (n_tokens <= 0 || k <= 0 || hidden_dim <= 0) return cudaSuccess;
+    if (world <= 0 || world > 1024 || k > 0x7fffffffLL || !aligned16(combined)) return cudaErrorInvalidValue;
+    unsigned int* st = cck::tc::status_word();
+    if (!st) return cudaErrorMemoryAllocation;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned grid = warp_grid(n_tokens);
+    switch (dtype) {
+        case kF32:
+            if (hidden_dim % 4) return cudaErrorInvalidValue;
+            token_combine_remote_kernel<float><<<grid, kCombineMaxThreads, 0, s>>>(
+                src_bases, static_cast<int>(world), capacity_rows, src_rank, src_row, weights, static_cast<float*>(combined),
+                n_tokens, static_cast<int>(k), hidden_dim / 4, st);
+            break;
+        case kF16:
+            if (hidden_dim % 8) return cudaErrorInvalidValue;
+            token_combine_remote_kernel<__half><<<grid, kCombineMaxThreads, 0, s>>>(
+                src_bases, static_cast<int>(world), capacity_rows, src_rank, src_row, weights, static_cast<__half*>(combined),
+                n_tokens, static_cast<int>(k), hidden_dim / 8, st);
+            break;
+        case kBF16:
+            if (hidden_dim % 8) return cudaErrorInvalidValue;
+            token_combine_remote_kernel<__nv_bfloat16><<<grid, kCombineMaxThreads, 0, s>>>(
+                src_bases, static_cast<int>(world), capacity_rows, src_rank, src_row, weights,
+                static_cast<__nv_bfloat16*>(combined), n_tokens, static_cast<int>(k), hidden_dim / 8, st);
+            break;
+        default:
+            return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
 }

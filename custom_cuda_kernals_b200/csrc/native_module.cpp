@@ -259,6 +259,56 @@ void token_combine_fwd(const at::Tensor& expert_output, const at::Tensor& unperm
                                           l.stream));
 }
 
+// expert-parallel row exchange (no counterpart in the reference)
+void token_dispatch_fwd(const at::Tensor& src, const at::Tensor& src_row, const at::Tensor& dst_rank,
+                        const at::Tensor& dst_row, const at::Tensor& dst_bases, int64_t capacity_rows) {
+    const int32_t dt = tag_of("src", src);
+    expect_float_input("src", dt);
+    expect_int("src_row", src_row, at::kLong, "int64");
+    expect_int("dst_rank", dst_rank, at::kLong, "int64");
+    expect_int("dst_row", dst_row, at::kLong, "int64");
+    expect_int("dst_bases", dst_bases, at::kLong, "int64");
+    if (src.dim() != 2) value_error("shape mismatch: src must be 2-D [rows, hidden], got " + shape_str(src));
+    const int64_t n = src_row.numel();
+    if (dst_rank.numel() != n || dst_row.numel() != n)
+        value_error("shape mismatch: src_row, dst_rank and dst_row must have the same number of elements");
+    if (dst_bases.dim() != 1 || dst_bases.numel() < 1) value_error("shape mismatch: dst_bases must be a 1-D table of addresses");
+    if ((src.size(1) * src.element_size()) % 16 != 0) value_error("shape mismatch: a row must be a multiple of 16 bytes");
+    if (capacity_rows < 0) value_error("capacity_rows must not be negative");
+    Launch l(src, {&src_row, &dst_rank, &dst_row, &dst_bases});
+    check_launch("launch_token_dispatch_fwd",
+                 launch_token_dispatch_fwd(src.data_ptr(), static_cast<const int64_t*>(src_row.data_ptr()),
+                                           static_cast<const int64_t*>(dst_rank.data_ptr()),
+                                           static_cast<const int64_t*>(dst_row.data_ptr()),
+                                           static_cast<const int64_t*>(dst_bases.data_ptr()), dst_bases.numel(),
+                                           capacity_rows, src.size(0), n, src.size(1), dt, l.stream));
+}
+
+void token_combine_remote_fwd(const at::Tensor& src_bases, int64_t capacity_rows, const at::Tensor& src_rank,
+                              const at::Tensor& src_row, const at::Tensor& weights, const at::Tensor& combined) {
+    const int32_t dt = tag_of("combined", combined);
+    expect_float_input("combined", dt);
+    expect_int("src_bases", src_bases, at::kLong, "int64");
+    expect_int("src_rank", src_rank, at::kLong, "int64");
+    expect_int("src_row", src_row, at::kLong, "int64");
+    expect_f32("weights", tag_of("weights", weights));
+    if (combined.dim() != 2) value_error("shape mismatch: combined must be 2-D [T, hidden], got " + shape_str(combined));
+    if (src_rank.dim() != 2 || src_rank.size(0) != combined.size(0) || src_row.sizes() != src_rank.sizes() ||
+        weights.sizes() != src_rank.sizes())
+        value_error("shape mismatch: src_rank, src_row and weights must be [T, k] with T = combined's rows; got " +
+                    shape_str(src_rank) + ", " + shape_str(src_row) + ", " + shape_str(weights));
+    const int64_t per_vec = dt == CCK_F32 ? 4 : 8;
+    if (combined.size(1) % per_vec != 0) value_error("shape mismatch: hidden must be a multiple of " + std::to_string(per_vec));
+    if (src_bases.dim() != 1 || src_bases.numel() < 1) value_error("shape mismatch: src_bases must be a 1-D table of addresses");
+    Launch l(combined, {&src_bases, &src_rank, &src_row, &weights});
+    check_launch("launch_token_combine_remote_fwd",
+                 launch_token_combine_remote_fwd(static_cast<const int64_t*>(src_bases.data_ptr()), src_bases.numel(),
+                                                 capacity_rows, static_cast<const int64_t*>(src_rank.data_ptr()),
+                                                 static_cast<const int64_t*>(src_row.data_ptr()),
+                                                 static_cast<const float*>(weights.data_ptr()), combined.data_ptr(),
+                                                 combined.size(0), src_rank.size(1), combined.size(1), dt, l.stream));
+}
+
 // gradients of the two ops above (no counterpart in the reference)
 void swiglu_bwd(const at::Tensor& gate, const at::Tensor& up, const at::Tensor& dy, const at::Tensor& dgate,
                 const at::Tensor& dup) {
@@ -826,6 +876,10 @@ PYBIND11_MODULE(_native, m) {
     m.def("token_gather_fwd", &token_gather_fwd, py::arg("src"), py::arg("indices"), py::arg("dst"));
     m.def("token_combine_fwd", &token_combine_fwd, py::arg("expert_output"), py::arg("unpermute_index"),
           py::arg("weights"), py::arg("combined"));
+    m.def("token_dispatch_fwd", &token_dispatch_fwd, py::arg("src"), py::arg("src_row"), py::arg("dst_rank"),
+          py::arg("dst_row"), py::arg("dst_bases"), py::arg("capacity_rows"));
+    m.def("token_combine_remote_fwd", &token_combine_remote_fwd, py::arg("src_bases"), py::arg("capacity_rows"),
+          py::arg("src_rank"), py::arg("src_row"), py::arg("weights"), py::arg("combined"));
     m.def("swiglu_bwd", &swiglu_bwd, py::arg("gate"), py::arg("up"), py::arg("dy"), py::arg("dgate"), py::arg("dup"));
     m.def("rmsnorm_residual_bwd", &rmsnorm_residual_bwd, py::arg("dy"), py::arg("d_residual_out"),
           py::arg("residual_out"), py::arg("weight"), py::arg("dx"), py::arg("dweight"), py::arg("workspace"),

@@ -1,0 +1,122 @@
+"""Expert-parallel token exchange: the all-to-all around the expert FFNs of a mixture-of-experts
+layer, done by the row movers themselves over peer memory.
+
+The reference stops at one GPU (its token_permute kernels gather and combine rows locally:
+csrc/kernels/token_permute.cu, baselines/token_permute.py:58-72).  With the experts spread over
+the ranks of one NVLink/NVSwitch box, the same two steps become the dispatch and combine
+all-to-all - and instead of packing rows, calling a collective and unpacking, the dispatch kernel
+writes each token row straight into the owning rank's receive buffer (peer memory), and the
+combine kernel reads each token's k expert outputs straight out of the ranks that produced them,
+weighting and summing as it goes.  The kernels only push or pull; the phases are separated by
+stream-ordered barriers of the symmetric-memory handle, and the only other communication is one
+all-gather of per-expert counts (world x experts integers).
+
+Receive layout on rank r: blocks in source-rank order; inside a block the rows are sorted by
+expert (ascending) and inside an expert keep the sender's token order - so every sender can
+compute where its rows land from the count matrix alone.
+
+``plan_dispatch`` / ``plan_receive`` are pure index arithmetic (any device, testable without
+a GPU); ``ExpertParallel`` owns the symmetric buffers and runs the phases.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+
+__all__ = ["DispatchPlan", "plan_dispatch", "plan_receive", "ExpertParallel"]
+
+
+@dataclass
+class DispatchPlan:
+    src_row: torch.Tensor        # [T*k] source token of every slot of the expert-sorted order
+    dst_rank: torch.Tensor       # [T*k] rank that owns the slot's expert
+    dst_row: torch.Tensor        # [T*k] row in that rank's receive buffer
+    slot_of: torch.Tensor        # [T, k] slot of every (token, choice): the combine reads rank/row there
+
+
+def plan_dispatch(topk_indices: torch.Tensor, counts: torch.Tensor, rank: int, experts_per_rank: int) -> DispatchPlan:
+    """Where this rank's rows go.  ``topk_indices``: ``[T, k]`` expert ids of the local tokens;
+    ``counts``: ``[world, experts]``, ``counts[s, e]`` = number of (token, choice) pairs of rank
+    ``s`` routed to expert ``e`` (the all-gathered bincounts)."""
+    t, k = topk_indices.shape
+    world = counts.shape[0]
+    flat = topk_indices.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    experts_sorted = flat[order]
+    dst_rank = torch.div(experts_sorted, experts_per_rank, rounding_mode="floor")
+    per_rank = counts.reshape(world, world, experts_per_rank).sum(-1)           # [source, destination]
+    seg_start = per_rank[:rank].sum(0)                                          # rows of lower sources, per destination
+    first = torch.cumsum(per_rank[rank], 0) - per_rank[rank]                    # start of each destination in my sorted order
+    slots = torch.arange(t * k, device=flat.device)
+    dst_row = seg_start[dst_rank] + (slots - first[dst_rank])
+    slot_of = torch.empty_like(order)
+    slot_of[order] = slots
+    return DispatchPlan(torch.div(order, k, rounding_mode="floor"), dst_rank, dst_row, slot_of.reshape(t, k))
+
+
+def plan_receive(counts: torch.Tensor, rank: int, experts_per_rank: int) -> tuple[int, torch.Tensor]:
+    """What arrives at ``rank``: the number of rows and the expert id of every row, in buffer order."""
+    mine = counts[:, rank * experts_per_rank:(rank + 1) * experts_per_rank]     # [source, my experts]
+    ids = torch.arange(rank * experts_per_rank, (rank + 1) * experts_per_rank, device=counts.device)
+    expert_of_row = torch.repeat_interleave(ids.repeat(counts.shape[0]), mine.reshape(-1))
+    return int(mine.sum().item()), expert_of_row
+
+
+class ExpertParallel:
+    """Dispatch / expert / combine over the ranks of one process group (one process per GPU).
+
+    ``capacity_rows`` bounds the rows one rank can receive per call (its experts' share of
+    ``world * T * k`` in the worst case); a call that would exceed it raises ``ValueError`` on
+    every rank before anything is sent.  Buffers are symmetric memory: allocated once, mapped
+    into every peer."""
+
+    def __init__(self, n_experts: int, hidden: int, capacity_rows: int, dtype: torch.dtype = torch.bfloat16,
+                 device: torch.device | None = None, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if n_experts % self.world:
+            raise ValueError(f"n_experts ({n_experts}) must be divisible by the world size ({self.world})")
+        self.n_experts, self.experts_per_rank = n_experts, n_experts // self.world
+        self.hidden, self.capacity, self.dtype = hidden, capacity_rows, dtype
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.recv = symm_mem.empty((capacity_rows, hidden), dtype=dtype, device=self.device)
+        self.out = symm_mem.empty((capacity_rows, hidden), dtype=dtype, device=self.device)
+        self._recv_h = symm_mem.rendezvous(self.recv, self.group.group_name)
+        self._out_h = symm_mem.rendezvous(self.out, self.group.group_name)
+        self.recv_bases = torch.tensor(list(self._recv_h.buffer_ptrs), dtype=torch.int64, device=self.device)
+        self.out_bases = torch.tensor(list(self._out_h.buffer_ptrs), dtype=torch.int64, device=self.device)
+
+    def exchange_counts(self, topk_indices: torch.Tensor) -> torch.Tensor:
+        mine = torch.bincount(topk_indices.reshape(-1), minlength=self.n_experts).to(torch.int64)
+        counts = torch.empty(self.world, self.n_experts, dtype=torch.int64, device=mine.device)
+        dist.all_gather_into_tensor(counts, mine, group=self.group)
+        return counts
+
+    def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_indices: torch.Tensor, expert_fn) -> torch.Tensor:
+        """``combined[t] = sum_j topk_weights[t, j] * expert_fn(x[t], expert topk_indices[t, j])``
+        with the experts evaluated on the ranks that own them.  ``expert_fn(rows, expert_ids)``
+        maps this rank's received rows ``[R, hidden]`` (with the expert id of every row) to
+        ``[R, hidden]``."""
+        counts = self.exchange_counts(topk_indices)
+        per_rank = counts.reshape(self.world, self.world, self.experts_per_rank).sum(-1)
+        worst = int(per_rank.sum(0).max().item())
+        if worst > self.capacity:
+            raise ValueError(f"a rank would receive {worst} rows, more than capacity_rows = {self.capacity}")
+        plan = plan_dispatch(topk_indices, counts, self.rank, self.experts_per_rank)
+        _native.token_dispatch_fwd(x, plan.src_row, plan.dst_rank, plan.dst_row, self.recv_bases, self.capacity)
+        self._recv_h.barrier()                               # every rank's pushes have landed
+        n_rows, expert_of_row = plan_receive(counts, self.rank, self.experts_per_rank)
+        if n_rows:
+            self.out[:n_rows].copy_(expert_fn(self.recv[:n_rows], expert_of_row))
+        self._out_h.barrier()                                # every rank's expert outputs are in place
+        combined = torch.empty(x.shape[0], self.hidden, dtype=self.dtype, device=self.device)
+        _native.token_combine_remote_fwd(self.out_bases, self.capacity, plan.dst_rank[plan.slot_of].contiguous(),
+                                         plan.dst_row[plan.slot_of].contiguous(), topk_weights, combined)
+        self._out_h.barrier()                                # nobody still reads the buffers the next call overwrites
+        return combined

@@ -197,6 +197,22 @@ int32_t launch_token_combine_fwd(const void* expert_output, const int64_t* unper
                                  void* combined, int64_t n_tokens, int64_t k, int64_t hidden_dim, int32_t dtype,
                                  void* stream);
 
+/* Expert-parallel forms of the two row movers (no reference counterpart): the destination /
+ * source of a row is (rank, row) - an entry of a device array of `world` buffer base addresses
+ * (this GPU's own receive buffer and its peers' buffers mapped into this process) and a row
+ * index.  Push / pull only: nothing waits on another GPU inside the kernels; separate the
+ * phases with stream-ordered barriers.  hidden_dim * element size must be a multiple of 16,
+ * every buffer 16-byte aligned.  A route outside [0, world) x [0, capacity_rows) (or a source
+ * row outside [0, n_src_rows)) is skipped and sets bit 2 of cck_take_device_status(). */
+int32_t launch_token_dispatch_fwd(const void* src, const int64_t* src_row, const int64_t* dst_rank,
+                                  const int64_t* dst_row, const int64_t* dst_bases, int64_t world,
+                                  int64_t capacity_rows, int64_t n_src_rows, int64_t n, int64_t hidden_dim,
+                                  int32_t dtype, void* stream);
+int32_t launch_token_combine_remote_fwd(const int64_t* src_bases, int64_t world, int64_t capacity_rows,
+                                        const int64_t* src_rank, const int64_t* src_row, const float* weights,
+                                        void* combined, int64_t n_tokens, int64_t k, int64_t hidden_dim, int32_t dtype,
+                                        void* stream);
+
 /* Gradients of launch_swiglu_fwd for an upstream gradient dy: dgate = dy * up * silu'(gate),
  * dup = dy * silu(gate), flat over n elements, fp32 arithmetic, one rounding.  No reference
  * counterpart (the reference is forward-only). */
