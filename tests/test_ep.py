@@ -55,6 +55,12 @@ def test_plans_fill_every_receive_buffer_exactly_and_in_order(world, experts, k)
         assert (keys.diff() >= 0).all()                                                # source-major, expert-minor
         assert torch.div(expert_of_row, epr, rounding_mode="floor").eq(r).all()
         outs.append(_expert(recv[r][:n_rows], expert_of_row))
+        # the way back: every received row returns to its source rank, into the slot it was sent from
+        home, slot = ep.plan_return(counts, r, epr)
+        assert torch.equal(home, tag[r][:n_rows, 0])
+        for i in range(n_rows):
+            p = plans[int(home[i])]
+            assert int(p.dst_rank[slot[i]]) == r and int(p.dst_row[slot[i]]) == i
     for r, p in enumerate(plans):
         got = torch.zeros_like(xs[r])
         for j in range(k):
@@ -119,12 +125,15 @@ def _ep_rank(rank, world, port, out_dir):
     experts, k, hidden, t = 8, 2, 1024, 300
     xs, idx, w, counts = _setup(world, experts, t, k, hidden, seed=5, device="cpu", dtype=torch.bfloat16)
     x, i, wt = xs[rank].to(dev), idx[rank].to(dev), w[rank].to(dev)
-    layer = ep.ExpertParallel(experts, hidden, capacity_rows=2 * world * (t + world) * k // world + 64, device=dev)
+    cap = 2 * world * (t + world) * k // world + 64
+    layer = ep.ExpertParallel(experts, hidden, capacity_rows=cap, device=dev)
     got = layer.forward(x, wt, i, _expert)
     again = layer.forward(x, wt, i, _expert)                    # buffers are reusable call after call
+    pushed = ep.ExpertParallel(experts, hidden, capacity_rows=cap, max_local_rows=(t + world) * k, device=dev,
+                               return_mode="push").forward(x, wt, i, _expert)
     torch.cuda.synchronize()
     ok = bool(torch.allclose(got.float(), _expected(x, i, wt), rtol=1.6e-2, atol=1.6e-2) and torch.equal(got, again)
-              and _native.take_device_status(x) == 0)
+              and torch.equal(got, pushed) and _native.take_device_status(x) == 0)
     try:
         tiny = ep.ExpertParallel(experts, hidden, capacity_rows=8, device=dev)
         tiny.forward(x, wt, i, _expert)
