@@ -202,7 +202,7 @@ def wrapper_call_stats(fn, arg_sets, flush, iters=100):
                       "CUDA events around the Python wrapper call"}
 
 
-def bench_ops(dev, rank, world, peaks, src):
+def bench_ops(dev, rank, world, peaks, src, with_reference_kernels=False):
     """Each fused op alone at the configuration sizes, sharded over the ranks; inputs rotate
     through sets whose total size exceeds the 126 MB L2."""
     from custom_cuda_kernals_b200 import dist
@@ -237,7 +237,7 @@ def bench_ops(dev, rank, world, peaks, src):
     # (oracle/_ref, built by oracle/build_ref.py where a reference checkout exists), timed the
     # same way on the same inputs.  A baseline leg like cpu_baseline: measured, never shipped.
     ref = None
-    if cpu_on:
+    if cpu_on and with_reference_kernels:
         from oracle import ref_kernels
         ref = ref_kernels if ref_kernels.available() else None
 
@@ -622,7 +622,7 @@ def run_ours(args, rank, world, local):
     line["clocks"] = clocks.summary()
     line["parity"] = parity
     if not args.skip_ops:
-        line["ops"] = bench_ops(dev, rank, world, peaks, src)
+        line["ops"] = bench_ops(dev, rank, world, peaks, src, args.with_reference_kernels)
     if rank == 0 and world == 1:
         w_cpu = {k: v.cpu() for k, v in weights.items()}
         tps, dt = cpu_sample_tokens_per_s(w_cpu, 4, 1, batch=BATCH)
@@ -724,6 +724,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-ops", action="store_true", help="only the block step, not the per-op table")
+    ap.add_argument("--with-reference-kernels", action="store_true",
+                    help="N=1: also time the reference project's own kernels (oracle/_ref, if built) beside each op")
     ap.add_argument("--profile-case", default=None, help=f"run one small kernel case and exit: {PROFILE_CASES}")
     args = ap.parse_args()
     if args.profile_case:
