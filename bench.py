@@ -271,7 +271,9 @@ def bench_ops(dev, rank, world, peaks, src, with_reference_kernels=False):
                                      "cores": torch.get_num_threads(), "kind": "port", "sample": sample,
                                      "seconds": round(dt, 4)}
 
-    from oracle import ops as O
+    O = None
+    if cpu_on:                    # the CPU baseline legs are the only users of the oracle here
+        from oracle import ops as O
 
     # config 1: rmsnorm+residual fp32 [2048, 4096], rows sharded
     r0, r1 = dist.row_range(2048, rank, world)
