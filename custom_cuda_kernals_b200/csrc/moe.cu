@@ -437,6 +437,106 @@ token_combine_remote_kernel(const int64_t* __restrict__ src_bases, int world, in
     }
 }
 
+// ---- the plan of one expert-parallel call, in one launch.
+// From this rank's flattened top-k expert ids and the all-gathered count matrix
+// counts[source][expert]: a STABLE counting sort of the (token, choice) pairs by expert (pairs
+// of one expert keep their order), and for every pair the rank that owns its expert and the row
+// it takes in that rank's receive buffer - blocks in source-rank order, inside a block sorted by
+// expert.  One CTA walks the pairs 1024 at a time: a pair's position among the equal-expert
+// pairs of its warp comes from match_any, the warps' counts are prefix-summed per expert in
+// shared memory (32 x experts 16-bit cells), and a running per-expert base carries over to the
+// next 1024.  meta[0] = rows this rank receives, meta[1] = the most any rank receives.
+constexpr int kPlanThreads = 1024;
+constexpr int kPlanMaxExperts = 256;   // the router's own limit
+constexpr int kPlanMaxWorld = 32;
+
+__global__ void __launch_bounds__(kPlanThreads)
+ep_plan_kernel(const int64_t* __restrict__ topk, const int64_t* __restrict__ counts, int64_t n, int k, int world,
+               int experts, int rank, int64_t* __restrict__ src_row, int64_t* __restrict__ dst_rank,
+               int64_t* __restrict__ dst_row, int64_t* __restrict__ pull_rank, int64_t* __restrict__ pull_row,
+               int64_t* __restrict__ meta, unsigned int* status) {
+    __shared__ int64_t per_rank[kPlanMaxWorld * kPlanMaxWorld];      // [source][destination]
+    __shared__ int64_t seg_start[kPlanMaxWorld], first[kPlanMaxWorld];
+    __shared__ int64_t expert_start[kPlanMaxExperts], base[kPlanMaxExperts];
+    __shared__ uint16_t hist[32 * kPlanMaxExperts];                  // [warp][expert]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int epr = experts / world;
+    for (int i = tid; i < world * world; i += kPlanThreads) {
+        const int s = i / world, r = i - s * world;
+        int64_t sum = 0;
+        for (int e = 0; e < epr; ++e) sum += counts[static_cast<int64_t>(s) * experts + r * epr + e];
+        per_rank[i] = sum;
+    }
+    __syncthreads();
+    if (tid < world) {
+        int64_t before = 0, mine_before = 0, total = 0;
+        for (int s = 0; s < world; ++s) {
+            if (s < rank) before += per_rank[s * world + tid];
+            total += per_rank[s * world + tid];
+        }
+        for (int r = 0; r < tid; ++r) mine_before += per_rank[rank * world + r];
+        seg_start[tid] = before;
+        first[tid] = mine_before;
+        base[tid] = total;                      // borrowed for the max below
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int64_t worst = 0;
+        for (int r = 0; r < world; ++r) worst = base[r] > worst ? base[r] : worst;
+        meta[0] = base[rank];
+        meta[1] = worst;
+        int64_t run = 0;
+        for (int e = 0; e < experts; ++e) {
+            expert_start[e] = run;
+            run += counts[static_cast<int64_t>(rank) * experts + e];
+        }
+    }
+    __syncthreads();
+    if (tid < experts) base[tid] = 0;
+    for (int64_t p0 = 0; p0 < n; p0 += kPlanThreads) {
+        for (int i = tid; i < 32 * experts; i += kPlanThreads) hist[i] = 0;
+        const int64_t p = p0 + tid;
+        int e = experts;                                             // sentinel: no pair / bad id
+        if (p < n) {
+            const int64_t v = topk[p];
+            if (v >= 0 && v < experts) e = static_cast<int>(v);
+            else atomicOr(status, kStatusBadRoute);
+        }
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const int ahead = __popc(peers & ((1u << lane) - 1u));
+        __syncthreads();
+        if (e < experts && ahead == 0) hist[warp * experts + e] = static_cast<uint16_t>(__popc(peers));
+        __syncthreads();
+        int64_t chunk_total = 0;
+        if (tid < experts) {
+            uint16_t run = 0;
+            for (int w = 0; w < 32; ++w) {
+                const uint16_t c = hist[w * experts + tid];
+                hist[w * experts + tid] = run;
+                run = static_cast<uint16_t>(run + c);
+            }
+            chunk_total = run;
+        }
+        __syncthreads();
+        if (e < experts) {
+            const int64_t slot = expert_start[e] + base[e] + hist[warp * experts + e] + ahead;
+            const int r = e / epr;
+            const int64_t row = seg_start[r] + (slot - first[r]);
+            src_row[slot] = p / k;
+            dst_rank[slot] = r;
+            dst_row[slot] = row;
+            pull_rank[p] = r;
+            pull_row[p] = row;
+        } else if (p < n) {
+            pull_rank[p] = -1;                                       // the combine skips and reports it
+            pull_row[p] = -1;
+        }
+        __syncthreads();
+        if (tid < experts) base[tid] += chunk_total;
+        __syncthreads();
+    }
+}
+
 }  // namespace
 }  // namespace cck
 
@@ -554,5 +654,28 @@ extern "C" int32_t launch_token_combine_remote_fwd(const int64_t* src_bases, int
         default:
             return cudaErrorInvalidValue;
     }
+    return cudaGetLastError();
+}
+
+// The plan of one expert-parallel call (see ep_plan_kernel): topk = this rank's [n] flattened
+// expert ids (n = tokens x k), counts = [world, experts] all-gathered per-expert counts.
+// Outputs, all int64: src_row / dst_rank / dst_row [n] in expert-sorted slot order (the
+// arguments of launch_token_dispatch_fwd), pull_rank / pull_row [n] in (token, choice) order
+// (the arguments of launch_token_combine_remote_fwd), meta[2] = {rows this rank receives, most
+// rows any rank receives}.  experts <= 256, world <= 32, experts % world == 0.  An id outside
+// [0, experts) sets bit 2 of the status word and gets the route (-1, -1), which the movers skip;
+// src_row / dst_* are then not fully written (zero them first if that can happen).
+extern "C" int32_t launch_ep_plan(const int64_t* topk, const int64_t* counts, int64_t n, int64_t k, int64_t world,
+                                  int64_t experts, int64_t rank, int64_t* src_row, int64_t* dst_rank, int64_t* dst_row,
+                                  int64_t* pull_rank, int64_t* pull_row, int64_t* meta, void* stream) {
+    using namespace cck;
+    if (n < 0 || k <= 0 || world <= 0 || world > kPlanMaxWorld || experts <= 0 || experts > kPlanMaxExperts ||
+        experts % world != 0 || rank < 0 || rank >= world)
+        return cudaErrorInvalidValue;
+    unsigned int* st = cck::tc::status_word();
+    if (!st) return cudaErrorMemoryAllocation;
+    ep_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        topk, counts, n, static_cast<int>(k), static_cast<int>(world), static_cast<int>(experts), static_cast<int>(rank),
+        src_row, dst_rank, dst_row, pull_rank, pull_row, meta, st);
     return cudaGetLastError();
 }

@@ -284,6 +284,32 @@ void token_dispatch_fwd(const at::Tensor& src, const at::Tensor& src_row, const 
                                            capacity_rows, src.size(0), n, src.size(1), dt, l.stream));
 }
 
+void ep_plan(const at::Tensor& topk, const at::Tensor& counts, int64_t rank, const at::Tensor& src_row,
+             const at::Tensor& dst_rank, const at::Tensor& dst_row, const at::Tensor& pull_rank,
+             const at::Tensor& pull_row, const at::Tensor& meta) {
+    expect_int("topk", topk, at::kLong, "int64");
+    expect_int("counts", counts, at::kLong, "int64");
+    for (const auto& named : {std::make_pair("src_row", &src_row), std::make_pair("dst_rank", &dst_rank),
+                              std::make_pair("dst_row", &dst_row), std::make_pair("pull_rank", &pull_rank),
+                              std::make_pair("pull_row", &pull_row), std::make_pair("meta", &meta)})
+        expect_int(named.first, *named.second, at::kLong, "int64");
+    if (topk.dim() != 2 || counts.dim() != 2) value_error("shape mismatch: topk must be [T, k] and counts [world, experts]");
+    const int64_t n = topk.numel(), k = topk.size(1), world = counts.size(0), experts = counts.size(1);
+    if (src_row.numel() != n || dst_rank.numel() != n || dst_row.numel() != n || pull_rank.numel() != n ||
+        pull_row.numel() != n || meta.numel() != 2)
+        value_error("shape mismatch: the five route outputs need T * k elements each, meta 2");
+    if (experts > 256 || world > 32 || world < 1 || experts % world != 0 || k < 1)
+        value_error("shape mismatch: at most 256 experts and 32 ranks, experts divisible by the ranks");
+    if (rank < 0 || rank >= world) value_error("rank must lie in [0, world)");
+    Launch l(topk, {&counts, &src_row, &dst_rank, &dst_row, &pull_rank, &pull_row, &meta});
+    check_launch("launch_ep_plan",
+                 launch_ep_plan(static_cast<const int64_t*>(topk.data_ptr()), static_cast<const int64_t*>(counts.data_ptr()),
+                                n, k, world, experts, rank, static_cast<int64_t*>(src_row.data_ptr()),
+                                static_cast<int64_t*>(dst_rank.data_ptr()), static_cast<int64_t*>(dst_row.data_ptr()),
+                                static_cast<int64_t*>(pull_rank.data_ptr()), static_cast<int64_t*>(pull_row.data_ptr()),
+                                static_cast<int64_t*>(meta.data_ptr()), l.stream));
+}
+
 void token_combine_remote_fwd(const at::Tensor& src_bases, int64_t capacity_rows, const at::Tensor& src_rank,
                               const at::Tensor& src_row, const at::Tensor& weights, const at::Tensor& combined) {
     const int32_t dt = tag_of("combined", combined);
@@ -878,6 +904,8 @@ PYBIND11_MODULE(_native, m) {
           py::arg("weights"), py::arg("combined"));
     m.def("token_dispatch_fwd", &token_dispatch_fwd, py::arg("src"), py::arg("src_row"), py::arg("dst_rank"),
           py::arg("dst_row"), py::arg("dst_bases"), py::arg("capacity_rows"));
+    m.def("ep_plan", &ep_plan, py::arg("topk"), py::arg("counts"), py::arg("rank"), py::arg("src_row"), py::arg("dst_rank"),
+          py::arg("dst_row"), py::arg("pull_rank"), py::arg("pull_row"), py::arg("meta"));
     m.def("token_combine_remote_fwd", &token_combine_remote_fwd, py::arg("src_bases"), py::arg("capacity_rows"),
           py::arg("src_rank"), py::arg("src_row"), py::arg("weights"), py::arg("combined"));
     m.def("swiglu_bwd", &swiglu_bwd, py::arg("gate"), py::arg("up"), py::arg("dy"), py::arg("dgate"), py::arg("dup"));

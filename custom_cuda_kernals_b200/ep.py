@@ -31,7 +31,7 @@ import torch.distributed as dist
 
 from . import _native
 
-__all__ = ["DispatchPlan", "plan_dispatch", "plan_receive", "plan_return", "ExpertParallel"]
+__all__ = ["DispatchPlan", "plan_dispatch", "plan_receive", "plan_return", "plan_on_device", "ExpertParallel"]
 
 
 @dataclass
@@ -82,6 +82,19 @@ def plan_return(counts: torch.Tensor, rank: int, experts_per_rank: int) -> tuple
     n_rows = int(rows_from.sum().item())
     slot = first_in_source[home] + (torch.arange(n_rows, device=counts.device) - block_start[home])
     return home, slot
+
+
+def plan_on_device(topk_indices: torch.Tensor, counts: torch.Tensor, rank: int):
+    """``plan_dispatch`` and the combine's routes by ONE kernel launch instead of ~25 small
+    PyTorch ops (at most 256 experts, 32 ranks).  Returns ``(src_row, dst_rank, dst_row,
+    pull_rank [T, k], pull_row [T, k], meta)``; ``meta`` is a device tensor ``[rows this rank
+    receives, most rows any rank receives]``."""
+    t, k = topk_indices.shape
+    dev = topk_indices.device
+    routes = torch.empty(5, t * k, dtype=torch.int64, device=dev)
+    meta = torch.empty(2, dtype=torch.int64, device=dev)
+    _native.ep_plan(topk_indices, counts, rank, routes[0], routes[1], routes[2], routes[3], routes[4], meta)
+    return routes[0], routes[1], routes[2], routes[3].view(t, k), routes[4].view(t, k), meta
 
 
 class ExpertParallel:
@@ -136,14 +149,26 @@ class ExpertParallel:
         if push and t * k > self.max_local:
             raise ValueError(f"T * k = {t * k} exceeds max_local_rows = {self.max_local}")
         counts = self.exchange_counts(topk_indices)
-        per_rank = counts.reshape(self.world, self.world, self.experts_per_rank).sum(-1)
-        worst = int(per_rank.sum(0).max().item())
+        on_device = self.n_experts <= 256 and self.world <= 32 and not push
+        if on_device:
+            src_row, dst_rank, dst_row, pull_rank, pull_row, meta = plan_on_device(topk_indices, counts, self.rank)
+            n_rows, worst = meta.tolist()                    # the call's one host read
+        else:
+            per_rank = counts.reshape(self.world, self.world, self.experts_per_rank).sum(-1)
+            worst = int(per_rank.sum(0).max().item())
         if worst > self.capacity:
             raise ValueError(f"a rank would receive {worst} rows, more than capacity_rows = {self.capacity}")
-        plan = plan_dispatch(topk_indices, counts, self.rank, self.experts_per_rank)
-        _native.token_dispatch_fwd(x, plan.src_row, plan.dst_rank, plan.dst_row, self.recv_bases, self.capacity)
+        if not on_device:
+            plan = plan_dispatch(topk_indices, counts, self.rank, self.experts_per_rank)
+            src_row, dst_rank, dst_row = plan.src_row, plan.dst_rank, plan.dst_row
+        _native.token_dispatch_fwd(x, src_row, dst_rank, dst_row, self.recv_bases, self.capacity)
         self._recv_h.barrier()                               # every rank's pushes have landed
-        n_rows, expert_of_row = plan_receive(counts, self.rank, self.experts_per_rank)
+        if on_device:
+            mine = counts[:, self.rank * self.experts_per_rank:(self.rank + 1) * self.experts_per_rank]
+            ids = torch.arange(self.rank * self.experts_per_rank, (self.rank + 1) * self.experts_per_rank, device=self.device)
+            expert_of_row = torch.repeat_interleave(ids.repeat(self.world), mine.reshape(-1), output_size=n_rows)
+        else:
+            n_rows, expert_of_row = plan_receive(counts, self.rank, self.experts_per_rank)
         if n_rows:
             y = expert_fn(self.recv[:n_rows], expert_of_row)
             if push:
@@ -157,7 +182,8 @@ class ExpertParallel:
             # the next call's first barrier keeps peers from overwriting `ret` before this combine ran
             return token_combine(self.ret[:t * k], plan.slot_of, topk_weights)
         combined = torch.empty(t, self.hidden, dtype=self.dtype, device=self.device)
-        _native.token_combine_remote_fwd(self.ret_bases, self.capacity, plan.dst_rank[plan.slot_of].contiguous(),
-                                         plan.dst_row[plan.slot_of].contiguous(), topk_weights, combined)
+        if not on_device:
+            pull_rank, pull_row = plan.dst_rank[plan.slot_of].contiguous(), plan.dst_row[plan.slot_of].contiguous()
+        _native.token_combine_remote_fwd(self.ret_bases, self.capacity, pull_rank, pull_row, topk_weights, combined)
         self._ret_h.barrier()                                # nobody still reads the buffers the next call overwrites
         return combined

@@ -208,6 +208,16 @@ int32_t launch_token_dispatch_fwd(const void* src, const int64_t* src_row, const
                                   const int64_t* dst_row, const int64_t* dst_bases, int64_t world,
                                   int64_t capacity_rows, int64_t n_src_rows, int64_t n, int64_t hidden_dim,
                                   int32_t dtype, void* stream);
+/* The routes of one expert-parallel call in one launch: topk = this rank's n = tokens x k flattened
+ * expert ids, counts = [world, experts] all-gathered per-expert counts (int64).  Writes, all int64:
+ * src_row / dst_rank / dst_row [n] in expert-sorted slot order (a stable sort: pairs of one expert keep
+ * their order) - the arguments of launch_token_dispatch_fwd; pull_rank / pull_row [n] in (token, choice)
+ * order - the arguments of launch_token_combine_remote_fwd; meta[0] = rows this rank receives, meta[1] =
+ * the most rows any rank receives.  A rank's receive buffer holds blocks in source-rank order, each
+ * sorted by expert.  experts <= 256, world <= 32, experts % world == 0, else cudaErrorInvalidValue. */
+int32_t launch_ep_plan(const int64_t* topk, const int64_t* counts, int64_t n, int64_t k, int64_t world,
+                       int64_t experts, int64_t rank, int64_t* src_row, int64_t* dst_rank, int64_t* dst_row,
+                       int64_t* pull_rank, int64_t* pull_row, int64_t* meta, void* stream);
 int32_t launch_token_combine_remote_fwd(const int64_t* src_bases, int64_t world, int64_t capacity_rows,
                                         const int64_t* src_rank, const int64_t* src_row, const float* weights,
                                         void* combined, int64_t n_tokens, int64_t k, int64_t hidden_dim, int32_t dtype,

@@ -108,6 +108,31 @@ def test_kernels_with_the_ranks_side_by_side_on_one_gpu(world, experts, k, hidde
     assert _native.take_device_status(xs[0]) == 0
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,experts,k,tokens", [(1, 4, 2, 50), (2, 8, 2, 1000), (4, 8, 3, 700), (8, 256, 8, 513),
+                                                    (8, 64, 6, 4096), (3, 6, 1, 1), (32, 256, 2, 300)])
+def test_planning_kernel_equals_the_index_arithmetic(world, experts, k, tokens):
+    """One launch gives exactly the routes of plan_dispatch (a stable sort by expert) for every
+    emulated rank: 1024-pair chunks that end mid-way, 256 experts, one thread per expert."""
+    from custom_cuda_kernals_b200 import _native
+    dev = torch.device("cuda", 0)
+    epr = experts // world
+    _, idx, _, counts = _setup(world, experts, tokens, k, 8, seed=world + experts + tokens, device=dev)
+    per_rank = counts.reshape(world, world, epr).sum(-1)
+    for r in range(world):
+        want = ep.plan_dispatch(idx[r], counts, r, epr)
+        src_row, dst_rank, dst_row, pull_rank, pull_row, meta = ep.plan_on_device(idx[r], counts, r)
+        assert torch.equal(src_row, want.src_row) and torch.equal(dst_rank, want.dst_rank) and torch.equal(dst_row, want.dst_row)
+        assert torch.equal(pull_rank, want.dst_rank[want.slot_of]) and torch.equal(pull_row, want.dst_row[want.slot_of])
+        assert meta.tolist() == [int(per_rank[:, r].sum()), int(per_rank.sum(0).max())]
+    assert _native.take_device_status(counts) == 0
+    bad = idx[0].clone()
+    bad[0, 0] = experts                                          # an expert id that does not exist
+    out = ep.plan_on_device(bad, counts, 0)
+    torch.cuda.synchronize()
+    assert _native.take_device_status(counts) & 4 and out[3][0, 0] == -1 and out[4][0, 0] == -1
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
