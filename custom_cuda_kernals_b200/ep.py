@@ -18,8 +18,9 @@ Receive layout on rank r: blocks in source-rank order; inside a block the rows a
 expert (ascending) and inside an expert keep the sender's token order - so every sender can
 compute where its rows land from the count matrix alone.
 
-``plan_dispatch`` / ``plan_receive`` / ``plan_return`` are pure index arithmetic (any device, testable without
-a GPU); ``ExpertParallel`` owns the symmetric buffers and runs the phases.
+``plan_dispatch`` / ``plan_receive`` / ``plan_return`` are pure index arithmetic (any device,
+testable without a GPU); ``plan_on_device`` gets the same routes from one kernel launch;
+``ExpertParallel`` owns the symmetric buffers and runs the phases.
 """
 
 from __future__ import annotations
