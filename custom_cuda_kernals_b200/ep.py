@@ -188,3 +188,79 @@ class ExpertParallel:
         _native.token_combine_remote_fwd(self.ret_bases, self.capacity, pull_rank, pull_row, topk_weights, combined)
         self._ret_h.barrier()                                # nobody still reads the buffers the next call overwrites
         return combined
+
+
+def _benchmark(tokens: int = 8192, k: int = 2, hidden: int = 4096, iters: int = 10) -> None:
+    """One process per GPU (launch with ``python -m torch.distributed.run --nproc-per-node N -m
+    custom_cuda_kernals_b200.ep``): a layer call with identity experts through ``ExpertParallel``
+    against the same exchange through local gather + two ``all_to_all_single`` + local combine,
+    CUDA events, max over ranks; rank 0 prints one JSON line."""
+    import json
+    import os
+
+    from .kernels.token_permute import token_combine, token_gather
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    experts = 8 * world
+    epr = experts // world
+    g = torch.Generator(device=dev).manual_seed(rank)
+    x = torch.randn(tokens, hidden, device=dev, generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(experts, device=dev, generator=g)[:k] for _ in range(64)]).repeat(tokens // 64, 1)
+    w = torch.rand(tokens, k, device=dev, generator=g)
+    layer = ExpertParallel(experts, hidden, capacity_rows=3 * tokens * k, device=dev)
+
+    def fused():
+        return layer.forward(x, w, idx, lambda rows, ids: rows)
+
+    def nccl_path():
+        counts = layer.exchange_counts(idx)
+        per_rank = counts.reshape(world, world, epr).sum(-1)
+        order = torch.argsort(idx.reshape(-1), stable=True)
+        send = token_gather(x, torch.div(order, k, rounding_mode="floor"))
+        to_peers, from_peers = per_rank[rank].tolist(), per_rank[:, rank].tolist()
+        recv = torch.empty(sum(from_peers), hidden, dtype=x.dtype, device=dev)
+        dist.all_to_all_single(recv, send, from_peers, to_peers)
+        back = torch.empty_like(send)
+        dist.all_to_all_single(back, recv, to_peers, from_peers)
+        inverse = torch.empty_like(order)
+        inverse[order] = torch.arange(order.numel(), device=dev)
+        return token_combine(back, inverse.reshape(tokens, k), w)
+
+    same = bool(torch.equal(fused(), nccl_path()))
+    counts = layer.exchange_counts(idx)
+    src_row, dst_rank, dst_row, pull_rank, pull_row, _ = plan_on_device(idx, counts, rank)
+    out = torch.empty(tokens, hidden, dtype=x.dtype, device=dev)
+
+    def kernels_only():
+        _native.token_dispatch_fwd(x, src_row, dst_rank, dst_row, layer.recv_bases, layer.capacity)
+        layer._recv_h.barrier()
+        _native.token_combine_remote_fwd(layer.recv_bases, layer.capacity, pull_rank, pull_row, w, out)
+        layer._recv_h.barrier()
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return round(ms.item(), 3)
+
+    line = {"world": world, "tokens_per_rank": tokens, "k": k, "hidden": hidden, "same_as_nccl_path": same,
+            "layer_call_ms": timed(fused), "nccl_path_ms": timed(nccl_path), "kernels_and_barriers_ms": timed(kernels_only),
+            "row_bytes_per_rank_each_way": tokens * k * hidden * 2, "remote_fraction": round(1 - 1 / world, 3)}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    _benchmark()
