@@ -198,7 +198,7 @@ def wrapper_call_stats(fn, arg_sets, flush, iters=100):
     times.sort()
     return {"median_us": round(statistics.median(times), 2),
             "iqr_us": round(times[int(0.75 * iters)] - times[int(0.25 * iters)], 2),
-            "method": "reference harness: 512 MB L2 flush + synchronize before each of 100 single calls, "
+            "method": f"reference harness: 512 MB L2 flush + synchronize before each of {iters} single calls, "
                       "CUDA events around the Python wrapper call"}
 
 
@@ -251,9 +251,9 @@ def bench_ops(dev, rank, world, peaks, src, with_reference_kernels=False):
             "speedup": round(secs / (out[name]["us_per_launch"] * 1e-6), 2),
             "what": "the reference's own CUDA kernel recompiled for sm_100a (-O3 --use_fast_math), same inputs, same timing"}
 
-    def wrapper(name, fn, arg_sets):
+    def wrapper(name, fn, arg_sets, iters=100):
         if flush is not None:
-            out[name]["wrapper_call"] = wrapper_call_stats(fn, arg_sets, flush)
+            out[name]["wrapper_call"] = wrapper_call_stats(fn, arg_sets, flush, iters)
 
     def cpu(name, work, fn, sample):
         """The oracle's CPU op chain on a bounded sample of the same inputs (all host cores)."""
@@ -391,6 +391,7 @@ def bench_ops(dev, rank, world, peaks, src, with_reference_kernels=False):
     a, w, bias = rn(8192, 4096), rn(n1 - n0, 4096, scale=0.02), rn(n1 - n0, scale=0.02)
     record("matmul_add_bias_bf16", "tensor", 2 * 8192 * 4096 * (n1 - n0),
            timed_loop(matmul_add_bias, [(a, w, bias)], 20), f"columns {n1 - n0} of 14336")
+    wrapper("matmul_add_bias_bf16", matmul_add_bias, [(a, w, bias)], 60)
     if ref:      # the reference GEMM is a CUDA-core kernel: tens of milliseconds per launch, timed eagerly
         reference_kernel("matmul_add_bias_bf16", ref.matmul_add_bias, [(a, w, bias)], 2 * 8192 * 4096 * (n1 - n0), 3,
                          graph=False)
@@ -421,6 +422,7 @@ def bench_ops(dev, rank, world, peaks, src, with_reference_kernels=False):
 
     record("linear_cross_entropy_bf16", "tensor", 2 * 16384 * 4096 * (v1 - v0),
            timed_loop(lce, [(h, wv, t)], 4 if world == 1 else 8, warm=2), f"vocab rows {v1 - v0} of 128256")
+    wrapper("linear_cross_entropy_bf16", lce, [(h, wv, t)], 20)
     if ref:      # the reference path: 32 cuBLAS chunk GEMMs + its chunk-update kernel (logits chunks materialised)
         reference_kernel("linear_cross_entropy_bf16", ref.linear_cross_entropy, [(h, wv, t)],
                          2 * 16384 * 4096 * (v1 - v0), 3, graph=False)
