@@ -52,7 +52,8 @@ def test_tensor_core_path_ragged_shapes(shape, dtype):
 
 
 @pytest.mark.parametrize("shape", [(128, 4096, 4096), (16, 4096, 11008), (256, 1024, 4096), (100, 512, 1000),
-                                   (512, 4096, 4096), (128, 4096, 72), (1, 8192, 4096)])
+                                   (512, 4096, 4096), (128, 4096, 72), (1, 8192, 4096), (16, 4096, 4096),
+                                   (17, 1024, 2048), (64, 4096, 4096), (5, 256, 520), (33, 11008, 4096)])
 def test_small_m_narrow_tiles_match_oracle(shape):
     """Decode-sized batches (few 128 x 256 tiles) run on 128 x 64 tiles: same results as the
     oracle's bf16 chain and as an fp32 evaluation, ragged column counts included."""
@@ -79,6 +80,7 @@ def test_row_and_column_shards_are_bitwise_slices_of_the_whole_at_small_sizes():
     whole = matmul_add_bias(x, w)
     assert torch.equal(matmul_add_bias(x[:128].contiguous(), w), whole[:128])
     assert torch.equal(matmul_add_bias(x[300:316].contiguous(), w), whole[300:316])
+    assert torch.equal(matmul_add_bias(x[700:749].contiguous(), w), whole[700:749])
     assert torch.equal(matmul_add_bias(x, w[512:1024].contiguous()), whole[:, 512:1024])
 
 
