@@ -1,4 +1,13 @@
-"""Fused residual add + RMSNorm (custom_cuda/kernels/rmsnorm_residual.py:17-28)."""
+"""Fused residual add + RMSNorm behind the reference's entry point
+(custom_cuda/kernels/rmsnorm_residual.py:17-28), and the norm alone.
+
+Rounding follows the PyTorch baseline (baselines/rmsnorm_residual.py:130-136): the sum ``x +
+residual`` is rounded to the storage type, the mean of squares is taken from that rounded sum in
+fp32, the normalised value is rounded to the storage type and then multiplied by ``weight``.
+One CTA owns a row and keeps it in registers between the reduction and the store
+(csrc/rmsnorm_residual.cu), so each input is read from memory once.  The gradient is in
+``kernels.autograd.rmsnorm_residual_trainable``.
+"""
 
 from __future__ import annotations
 
@@ -11,16 +20,13 @@ __all__ = ["rmsnorm_residual", "rmsnorm"]
 
 def rmsnorm_residual(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
                      eps: float = 1e-6) -> tuple[torch.Tensor, torch.Tensor]:
-    """``residual_out = x + residual``; ``y = RMSNorm(residual_out) * weight``.
-
-    x, residual: ``[..., hidden]`` contiguous CUDA tensors of one dtype
-    (float32/float16/bfloat16); weight: ``[hidden]`` of the same dtype.
-    Returns ``(y, residual_out)``.
-    """
-    y = torch.empty_like(x)
-    residual_out = torch.empty_like(x)
-    _native.rmsnorm_residual_fwd(x, residual, weight, y, residual_out, eps)
-    return y, residual_out
+    """``(y, residual_out)`` with ``residual_out = x + residual`` and ``y = residual_out *
+    rsqrt(mean(residual_out ** 2) + eps) * weight`` over the last dimension.  ``x`` and
+    ``residual`` share shape ``[..., hidden]`` and dtype (float32 / float16 / bfloat16) and are
+    contiguous CUDA tensors; ``weight`` is ``[hidden]`` of that dtype."""
+    outputs = torch.empty((2, *x.shape), dtype=x.dtype, device=x.device)      # y and residual_out, one allocation
+    _native.rmsnorm_residual_fwd(x, residual, weight, outputs[0], outputs[1], eps)
+    return outputs[0], outputs[1]
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
