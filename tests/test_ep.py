@@ -179,3 +179,37 @@ def test_two_ranks_exchange_rows_over_peer_memory(tmp_path):
     for r in range(world):
         res = torch.load(tmp_path / f"ep{r}.pt")
         assert res["ok"] and res["refused"]
+
+
+def test_plans_are_a_bijection_onto_dense_buffers_for_random_routings():
+    """Property check over random (world, experts per rank, k, tokens): every (source, slot) maps
+    to a distinct (rank, row), the rows of a rank are exactly 0..n_rows-1, the receiver's expert
+    ids match what was sent, and plan_return inverts plan_dispatch."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=40, deadline=None)
+    @given(st.integers(1, 8), st.integers(1, 5), st.integers(1, 4), st.integers(0, 60), st.integers(0, 10 ** 6))
+    def check(world, epr, k, tokens, seed):
+        experts = world * epr
+        k = min(k, experts)
+        g = torch.Generator().manual_seed(seed)
+        idx = [torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(tokens + r % 3)]).reshape(-1, k)
+               if tokens + r % 3 else torch.empty(0, k, dtype=torch.long) for r in range(world)]
+        counts = torch.stack([torch.bincount(i.reshape(-1), minlength=experts) for i in idx])
+        plans = [ep.plan_dispatch(idx[r], counts, r, epr) for r in range(world)]
+        for d in range(world):
+            n_rows, expert_of_row = ep.plan_receive(counts, d, epr)
+            rows, sent_experts, sources, slots = [], [], [], []
+            for r, p in enumerate(plans):
+                mask = p.dst_rank == d
+                rows.append(p.dst_row[mask])
+                sent_experts.append(idx[r].reshape(-1)[torch.argsort(idx[r].reshape(-1), stable=True)][mask])
+                sources.append(torch.full((int(mask.sum()),), r))
+                slots.append(mask.nonzero().squeeze(1))
+            rows, sent_experts = torch.cat(rows), torch.cat(sent_experts)
+            assert rows.numel() == n_rows and torch.equal(torch.sort(rows)[0], torch.arange(n_rows))
+            assert torch.equal(expert_of_row[rows], sent_experts)
+            home, slot = ep.plan_return(counts, d, epr)
+            assert torch.equal(home[rows], torch.cat(sources)) and torch.equal(slot[rows], torch.cat(slots))
+
+    check()
