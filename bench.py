@@ -497,15 +497,60 @@ def run_reference(args, rank, world):
         return
     steps, warm = max(1, args.steps), max(0, args.warmup)
     w = cpu_weights()
-    tps, dt = cpu_sample_tokens_per_s(w, steps, warm, batch=2)
+    tps, dt = cpu_sample_tokens_per_s(w, steps, warm, batch=BATCH)
     line = base_line(args, world, tps, dt * 1e3)
     line.update({"impl": "reference", "scaling": "strong",
                  "cpu_baseline": {"value": tps, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                                  "sample": f"oracle block (eager baselines' op chain) on batch 2 x seq {SEQ} (1/4 of a "
-                                            f"step), {steps} timed step(s) after {warm} warm-up; tokens/s = {2 * SEQ} / step time"},
+                                  "sample": f"oracle block (the eager baselines' op chain, pinned bit for bit to the "
+                                            f"reference's BaselineLlamaBlock) on the full step, batch {BATCH} x seq {SEQ}: "
+                                            f"{steps} timed step(s) after {warm} warm-up"},
                  "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                  })
     emit(line)
+
+
+def multi_gpu_parity(dev, rank, world):
+    """Before timing at N > 1: the three sharded paths of the per-op table on a small shape, each
+    against the single-GPU result computed on this rank - the vocabulary-sharded loss (one
+    all-gather), this rank's column shard of matmul_add_bias, and the vocabulary-parallel
+    gradients (all-reduced d_hidden, own d_weight rows).  Every rank takes part in the collectives;
+    the verdict is the AND over ranks."""
+    from custom_cuda_kernals_b200 import dist
+    from custom_cuda_kernals_b200.kernels.linear_cross_entropy import linear_cross_entropy, linear_cross_entropy_fwd_bwd
+    from custom_cuda_kernals_b200.kernels.matmul_add_bias import matmul_add_bias
+    n, hid, v, ncol = 1024, 512, 16384, 4096
+    g = torch.Generator(device=dev).manual_seed(99)              # the same tensors on every rank
+    h = torch.randn(n, hid, device=dev, generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(v, hid, device=dev, generator=g)).to(torch.bfloat16)
+    bias = (0.05 * torch.randn(ncol, device=dev, generator=g)).to(torch.bfloat16)
+    t = torch.randint(0, v, (n,), device=dev, generator=g)
+    t[::7] = -100
+    v0, v1 = dist.vocab_range(v, rank, world)
+    c0, c1 = dist.column_range(ncol, rank, world)
+    loss_1, dh_1, dw_1 = linear_cross_entropy_fwd_bwd(h, w, t)
+    assert abs(float(loss_1) - float(linear_cross_entropy(h, w, t))) <= 1e-6 * abs(float(loss_1))
+    y_1 = matmul_add_bias(h, w[:ncol], bias)
+    loss_n = dist.vocab_parallel_linear_cross_entropy(h, w[v0:v1].contiguous(), t, v0)
+    loss_g, dh_n, dw_n = dist.vocab_parallel_linear_cross_entropy_fwd_bwd(h, w[v0:v1].contiguous(), t, v0)
+    y_n = matmul_add_bias(h, w[c0:c1].contiguous(), bias[c0:c1].contiguous())
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-30))
+
+    out = {"shape": f"N {n} x H {hid} x V {v}; matmul columns {ncol}",
+           "loss_rel_err": abs(float(loss_n) - float(loss_1)) / abs(float(loss_1)),
+           "fwd_bwd_loss_rel_err": abs(float(loss_g) - float(loss_1)) / abs(float(loss_1)),
+           "column_shard_bit_equal": bool(torch.equal(y_n, y_1[:, c0:c1])),
+           "d_hidden_max_err_over_max": rel(dh_n, dh_1),
+           "d_weight_rows_max_err_over_max": rel(dw_n, dw_1[v0:v1])}
+    # d_hidden is a sum of bf16 per-shard contributions (one rounding per shard and one per
+    # all-reduce step) against a single bf16 rounding on one GPU: 2 % of the largest element
+    ok = (out["loss_rel_err"] <= 1e-5 and out["fwd_bwd_loss_rel_err"] <= 1e-5 and out["column_shard_bit_equal"]
+          and out["d_hidden_max_err_over_max"] <= 2e-2 and out["d_weight_rows_max_err_over_max"] <= 1e-2)
+    flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+    torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+    out["ok"] = bool(flag.item() == 1.0)
+    return out
 
 
 # --------------------------------------------------------------------------- our arm
@@ -526,26 +571,37 @@ def run_ours(args, rank, world, local):
     out_host = torch.empty_like(x_host).pin_memory()
     x_dev = x_host.to(dev)
 
-    # parity gate on a slice (rank 0): the GPU block against the CPU oracle with the same weights.
-    # A seven-GEMM bf16 chain is compared through a common fp32 evaluation: the GPU result must
-    # be as close to it as the oracle's own bf16 result is, and close to the oracle elementwise
-    # (torch's eager bf16 block on GPU vs on CPU already differs on ~3 % of the elements at
-    # rtol 1e-2 / atol 2e-2, so that bound carries a 5 % budget here).
+    # parity gate on the timed shape (rank 0): one full 2048-token sequence of the timed input
+    # through the GPU block against the CPU oracle (pinned bit for bit to the reference's
+    # BaselineLlamaBlock) with the same weights.  A seven-GEMM bf16 chain is compared through a
+    # common fp32 evaluation: the GPU result must be as close to it as the oracle's own bf16
+    # result is; elementwise against the oracle at the reference's block tolerance (rtol 1e-2,
+    # atol 2e-2) the bar is the measured value plus a margin - two bf16 evaluations of this
+    # chain on different machines (torch's own ops on GPU vs on CPU included) differ on 5.9-6.0 %
+    # of the elements at 2048 tokens, so the budget is 7.5 %.
     parity = None
     if rank == 0:
         w_cpu = {k: v.cpu() for k, v in weights.items()}
-        xs = x_all[:1, :256]
+        xs = x_all[b0:b0 + 1]
         want = cpu_block_step(xs, w_cpu).float()
         truth = cpu_block_step(xs.float(), {k: v.float() for k, v in w_cpu.items()})
         got = block(xs.to(dev)).cpu().float()
         rms = lambda t: float(t.pow(2).mean().sqrt())
         e_gpu, e_cpu = rms(got - truth), rms(want - truth)
         bad = float(((got - want).abs() > 2e-2 + 1e-2 * want.abs()).float().mean())
-        parity = {"sample": "batch 1 x seq 256 vs CPU oracle (bf16) and its fp32 evaluation",
+        parity = {"sample": f"batch 1 x seq {SEQ} (the first timed sequence) vs CPU oracle (bf16) and its fp32 evaluation",
                   "rms_err_vs_fp32": {"gpu": e_gpu, "oracle_bf16": e_cpu},
-                  "outside_rtol1e-2_atol2e-2_vs_oracle": bad, "ok": bool(e_gpu <= 1.25 * e_cpu and bad <= 0.05)}
+                  "outside_rtol1e-2_atol2e-2_vs_oracle": bad, "budget": 0.075,
+                  "ok": bool(e_gpu <= 1.25 * e_cpu and bad <= 0.075)}
         log("parity", parity)
         del w_cpu
+
+    if world > 1:
+        multi = multi_gpu_parity(dev, rank, world)
+        if rank == 0:
+            parity["multi_gpu"] = multi
+            parity["ok"] = bool(parity["ok"] and multi["ok"])
+            log("multi-GPU parity", multi)
 
     with torch.no_grad():
         for _ in range(max(3, args.warmup)):
@@ -633,6 +689,75 @@ def run_ours(args, rank, world, local):
         line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                                 "sample": f"CPU oracle block on the full step (batch {BATCH} x seq {SEQ}), 4 timed steps "
                                           f"of {dt:.2f} s after 1 warm-up"}
+    if rank == 0:
+        emit(line)
+
+
+def run_ep_exchange(rank, world, tokens=8192, k=2, hidden=4096, iters=10):
+    """`--ep-exchange` (N >= 2 ranks): one mixture-of-experts layer call with identity experts through
+    ExpertParallel (dispatch and combine kernels over peer memory) against the same exchange through
+    local gather + two all_to_all_single + local combine; CUDA events, max over ranks; rank 0 prints
+    one JSON line."""
+    import torch.distributed as td
+
+    from custom_cuda_kernals_b200 import _native, ep
+    from custom_cuda_kernals_b200.kernels.token_permute import token_combine, token_gather
+    dev = torch.device("cuda", torch.cuda.current_device())
+    experts = 8 * world
+    epr = experts // world
+    g = torch.Generator(device=dev).manual_seed(rank)
+    x = torch.randn(tokens, hidden, device=dev, generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(experts, device=dev, generator=g)[:k] for _ in range(64)]).repeat(tokens // 64, 1)
+    w = torch.rand(tokens, k, device=dev, generator=g)
+    layer = ep.ExpertParallel(experts, hidden, capacity_rows=3 * tokens * k, device=dev)
+
+    def fused():
+        return layer.forward(x, w, idx, lambda rows, ids: rows)
+
+    def nccl_path():
+        counts = layer.exchange_counts(idx)
+        per_rank = counts.reshape(world, world, epr).sum(-1)
+        order = torch.argsort(idx.reshape(-1), stable=True)
+        send = token_gather(x, torch.div(order, k, rounding_mode="floor"))
+        to_peers, from_peers = per_rank[rank].tolist(), per_rank[:, rank].tolist()
+        recv = torch.empty(sum(from_peers), hidden, dtype=x.dtype, device=dev)
+        td.all_to_all_single(recv, send, from_peers, to_peers)
+        back = torch.empty_like(send)
+        td.all_to_all_single(back, recv, to_peers, from_peers)
+        inverse = torch.empty_like(order)
+        inverse[order] = torch.arange(order.numel(), device=dev)
+        return token_combine(back, inverse.reshape(tokens, k), w)
+
+    same = bool(torch.equal(fused(), nccl_path()))
+    counts = layer.exchange_counts(idx)
+    src_row, dst_rank, dst_row, pull_rank, pull_row, _ = ep.plan_on_device(idx, counts, rank)
+    out = torch.empty(tokens, hidden, dtype=x.dtype, device=dev)
+
+    def kernels_only():
+        _native.token_dispatch_fwd(x, src_row, dst_rank, dst_row, layer.recv_bases, layer.capacity)
+        layer.barrier()
+        _native.token_combine_remote_fwd(layer.recv_bases, layer.capacity, pull_rank, pull_row, w, out)
+        layer.barrier()
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        td.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        td.all_reduce(ms, op=td.ReduceOp.MAX)
+        return round(ms.item(), 3)
+
+    line = {"world": world, "tokens_per_rank": tokens, "k": k, "hidden": hidden, "same_as_nccl_path": same,
+            "layer_call_ms": timed(fused), "nccl_path_ms": timed(nccl_path), "kernels_and_barriers_ms": timed(kernels_only),
+            "row_bytes_per_rank_each_way": tokens * k * hidden * 2, "remote_fraction": round(1 - 1 / world, 3),
+            "device_status": int(_native.take_device_status(out))}
     if rank == 0:
         emit(line)
 
@@ -730,6 +855,8 @@ def main():
     ap.add_argument("--skip-ops", action="store_true", help="only the block step, not the per-op table")
     ap.add_argument("--with-reference-kernels", action="store_true",
                     help="N=1: also time the reference project's own kernels (oracle/_ref, if built) beside each op")
+    ap.add_argument("--ep-exchange", action="store_true",
+                    help="N >= 2: time the expert-parallel token exchange against the all_to_all path and exit")
     ap.add_argument("--profile-case", default=None, help=f"run one small kernel case and exit: {PROFILE_CASES}")
     args = ap.parse_args()
     if args.profile_case:
@@ -744,7 +871,12 @@ def main():
     if world != args.gpus and rank == 0:
         log(f"note: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE")
     try:
-        run_ours(args, rank, world, local)
+        if args.ep_exchange:
+            if world < 2:
+                raise SystemExit("--ep-exchange needs at least two ranks (torch.distributed.run --nproc-per-node N)")
+            run_ep_exchange(rank, world)
+        else:
+            run_ours(args, rank, world, local)
     finally:
         if torch.distributed.is_initialized():
             torch.distributed.destroy_process_group()

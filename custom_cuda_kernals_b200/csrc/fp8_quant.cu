@@ -276,7 +276,7 @@ fp8_block_tma_kernel(const __grid_constant__ CUtensorMap map, uint8_t* __restric
         ptx::tma_load_2d(ptx::smem_addr(tile), &map, bar, static_cast<int32_t>(c0), static_cast<int32_t>(r0));
     }
     __syncthreads();
-    const bool ok = ptx::mbar_wait(bar, 0, &abort_flag);
+    const bool ok = ptx::mbar_wait(bar, 0, &abort_flag, status);
     if (!__syncthreads_and(ok)) {
         if (threadIdx.x == 0) atomicOr(status, 2u);
         return;

@@ -11,6 +11,8 @@
 //
 // Waits: the mbarrier waits are the bounded ones of ptx.cuh; the two cluster barriers are
 // reached by every thread of every CTA on every path (a role that gave up still arrives).
+// If any CTA of the cluster gave up, the leader stores nothing for that tile and bit 0 of the
+// status word is set.
 #pragma once
 
 #include "gemm_tcgen05.cuh"
@@ -28,6 +30,11 @@ __device__ __forceinline__ uint32_t cluster_nctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
     return r;
+}
+__device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t cluster_addr) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+    return v;
 }
 __device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
     float4 v;
@@ -89,7 +96,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int stage = 0;
             uint32_t phase = 0;
             for (int kb = kb0; kb < kb1; ++kb) {
-                if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
+                if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status)) break;
                 ptx::mbar_arrive_expect_tx(full_bar(stage), kSkStageBytes);
                 const uint32_t a_dst = base + stage * kSkStageBytes;
                 ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * 64, m_tile * kBM);
@@ -103,7 +110,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             uint32_t phase = 0;
             bool ok = true;
             for (int kb = kb0; kb < kb1; ++kb) {
-                if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, status)) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 const uint32_t a_src = base + stage * kSkStageBytes;
                 const uint64_t da = ptx::smem_desc_k_sw128(a_src);
@@ -119,7 +126,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     } else {
         // ---- epilogue, part 1: this CTA's partial out of tensor memory
         const int quarter = warp & 3;
-        const bool got = ptx::mbar_wait(tfull_bar, 0u, abort_flag);
+        const bool got = ptx::mbar_wait(tfull_bar, 0u, abort_flag, status);
         if (__all_sync(0xffffffffu, got)) {
             ptx::tc_fence_after_sync();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -145,7 +152,15 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     ptx::cluster_arrive();
     ptx::cluster_wait();
 
-    if (rank == 0 && warp >= 2 && have_acc && !*abort_flag) {
+    // a peer whose wait ran out parked nothing: its abort flag (raised before it arrived at the
+    // barrier above) tells the leader to leave the tile unwritten and report instead
+    bool peers_ok = true;
+    if (rank == 0 && warp >= 2) {
+        const uint32_t flag_local = ptx::smem_addr(const_cast<int*>(abort_flag));
+        for (uint32_t r = 1; r < splits; ++r) peers_ok = peers_ok && ld_cluster_u32(ptx::map_to_cta(flag_local, r)) == 0u;
+        if (!peers_ok && threadIdx.x == 64) atomicOr(status, 1u);
+    }
+    if (rank == 0 && warp >= 2 && have_acc && !*abort_flag && peers_ok) {
         // ---- epilogue, part 2 (leader): add the peers' partials in rank order, bias, round, store
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;

@@ -192,7 +192,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             while (ok && it.next(w)) {
                 const int m0 = w.m_tile * kBM, n0 = w.n_tile * BN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
                     const uint32_t a_dst = base + stage * kStageBytes;
                     ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kElemsPerSlab, m0);
@@ -213,11 +213,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             while (ok && it.next(w)) {
                 const int buf = acc_iter & 1;
                 const uint32_t acc_phase = (acc_iter >> 1) & 1;
-                if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag)) break;
+                if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, status)) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t d = tmem_base + buf * BN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, status)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
                     const uint32_t a_src = base + stage * kStageBytes;
                     const uint64_t da = ptx::smem_desc_k_sw128(a_src);
@@ -251,7 +251,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             __syncwarp();
             Epi::tile_begin(ep, th, w, my_scratch, lane, row_in_tile);
             __syncwarp();
-            const bool got = ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag);
+            const bool got = ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, status);
             if (!__all_sync(0xffffffffu, got)) break;
             ptx::tc_fence_after_sync();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
@@ -360,7 +360,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int m0 = (w.m_tile * 2 + static_cast<int>(rank)) * kBM;
                 const int n0 = w.n_tile * kBN + static_cast<int>(rank) * 128;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status)) { ok = false; break; }
                     const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
                     if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * kPairStageBytes);
                     const uint32_t a_dst = base + stage * kPairStageBytes;
@@ -382,11 +382,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             while (ok && it.next(w)) {
                 const int buf = acc_iter & 1;
                 const uint32_t acc_phase = (acc_iter >> 1) & 1;
-                if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag)) break;
+                if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, status)) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t d = tmem_base + buf * kBN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, status)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
                     const uint32_t a_src = base + stage * kPairStageBytes;
                     const uint64_t da = ptx::smem_desc_k_sw128(a_src);
@@ -425,7 +425,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             __syncwarp();
             Epi::tile_begin(ep, th, w, my_scratch, lane, row_in_tile);
             __syncwarp();
-            const bool got = ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag);
+            const bool got = ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, status);
             if (!__all_sync(0xffffffffu, got)) break;
             ptx::tc_fence_after_sync();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
@@ -503,12 +503,14 @@ inline bool splitk_enabled() {
 }
 
 inline int sm_count() {
-    static int n = [] {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return kNumSMs;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return kNumSMs;
-        return v;
-    }();
+    static int cached_per_device[kMaxDevices] = {};
+    const int slot = current_device_slot();
+    if (slot < 0) return kNumSMs;
+    int& n = cached_per_device[slot];
+    if (n <= 0) {
+        int v = 0;
+        n = (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, slot) == cudaSuccess && v > 0) ? v : kNumSMs;
+    }
     return n;
 }
 

@@ -582,7 +582,9 @@ constexpr int64_t kNoAllocScratchBytes = 6ll << 20;   // 6 MiB: e.g. 8192 rows x
 static __device__ __align__(256) float g_lce_noalloc_scratch[kNoAllocScratchBytes / sizeof(float)];
 
 // In host code the array's name only stands for the symbol; its device address has
-// to be asked for, once per device, with that device current.
+// to be asked for, once per device, with that device current.  The per-device cache is
+// filled without a lock: host threads that make the first call on one device at the same
+// time each look the address up and store the same value, so no thread reads a wrong one.
 float* noalloc_scratch_ptr(cudaError_t* err) {
     static float* ptr[64] = {};
     int dev = 0;

@@ -18,15 +18,19 @@
 namespace cck {
 namespace tc {
 
-__device__ unsigned int g_status_word = 0;
+// Per-device status block (layout in ptx.cuh): error bits in the first word, the wait limit
+// of the bounded mbarrier waits in bytes 8..15.
+__device__ __align__(16) unsigned long long g_status_block[2] = {0ull, ptx::kDefaultWaitLimitNs};
 
+// Address of the current device's status block.  The per-device cache is filled without a lock:
+// two host threads making the first call on one device both store the same address.
 unsigned int* status_word() {
     static unsigned int* ptr[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     if (!ptr[dev]) {
         void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_block) != cudaSuccess) return nullptr;
         ptr[dev] = static_cast<unsigned int*>(p);
     }
     return ptr[dev];
@@ -264,4 +268,60 @@ extern "C" int32_t cck_take_device_status(uint32_t* out) {
     if (e != cudaSuccess) return e;
     *out = v;
     return cudaMemcpy(st, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+}
+
+// Sets the limit of every bounded device-side wait on the current device (nanoseconds, clamped
+// to [1 us, 10 s]; the library starts with 2 s) and returns the previous one in *previous_ns
+// (may be null).  Synchronises the device: kernels in flight keep the limit they started with.
+extern "C" int32_t cck_set_wait_limit_ns(uint64_t limit_ns, uint64_t* previous_ns) {
+    unsigned int* st = cck::tc::status_word();
+    if (!st) return cudaErrorInvalidValue;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    unsigned long long old = 0, now = limit_ns < 1000ull ? 1000ull : (limit_ns > 10000000000ull ? 10000000000ull : limit_ns);
+    e = cudaMemcpy(&old, st + 2, sizeof(old), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    if (previous_ns) *previous_ns = old;
+    return cudaMemcpy(st + 2, &now, sizeof(now), cudaMemcpyHostToDevice);
+}
+
+// Self-test of the give-up path of the tensor-core kernels: one launch of a real GEMM kernel on
+// ONE tile whose A tensor map is built with a 64-row box where the kernel counts on 128 rows of
+// bytes, so the "stage full" mbarrier never completes and no MMA is ever issued.  The waiting
+// roles run into the wait limit, raise the CTA's abort flag, the CTA waits for its copies in
+// flight, frees its tensor memory, sets bit 0 of the status word and returns - no fault, no
+// hang, the context stays usable.  Set a short limit (cck_set_wait_limit_ns, ~1 ms) first.
+//   a [256, 64], b [256, 64] bf16 (row-major), y [256, 256] bf16 (left unwritten)
+//   variant 0: gemm_kernel (one CTA)   1: gemm_pair_kernel (one CTA pair)   2: gemm_splitk_kernel (cluster of 2)
+extern "C" int32_t launch_wait_limit_selftest(const void* a, const void* b, void* y, int32_t variant, void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    using T = __nv_bfloat16;
+    if (!a || !b || !y || !aligned16(a) || !aligned16(b) || !aligned16(y)) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const int64_t rows = 256, k = variant == 2 ? 128 : 64;
+    CUtensorMap ta, tb;
+    cudaError_t e = make_tmap(&ta, dt, 2, a, variant == 2 ? 128 : rows, k, 64 /* the kernels expect kBM = 128 */);
+    if (e != cudaSuccess) return e;
+    EpiBias<T>::Params ep{nullptr, static_cast<T*>(y), rows, 256, 1};
+    SchedGemm::Params sp{1, 1, 1};
+    switch (variant) {
+        case 0:
+            e = make_tmap(&tb, dt, 2, b, rows, k, kBN);
+            if (e != cudaSuccess) return e;
+            return launch<false, SchedGemm, EpiBias<T>>(ta, tb, sp, ep, k, ptx::instr_desc(1u, 1u, kBM, kBN), 1, s);
+        case 1:
+            if (max_pairs<false, SchedGemm, EpiBias<T>>() <= 0) return cudaErrorNotSupported;
+            e = make_tmap(&tb, dt, 2, b, rows, k, 128);
+            if (e != cudaSuccess) return e;
+            return launch_pair<false, SchedGemm, EpiBias<T>>(ta, tb, sp, ep, k, ptx::instr_desc(1u, 1u, 2 * kBM, kBN), 1, s);
+        case 2:
+            e = make_tmap(&tb, dt, 2, b, 128, k, 64);
+            if (e != cudaSuccess) return e;
+            return launch_splitk<T>(ta, tb, nullptr, static_cast<T*>(y), 128, 64, 1, 1, k, ptx::instr_desc(1u, 1u, kBM, 64),
+                                    1, 2, s);
+        default:
+            return cudaErrorInvalidValue;
+    }
 }

@@ -862,6 +862,25 @@ uint32_t take_device_status(const at::Tensor& like) {
     return v;
 }
 
+uint64_t set_wait_limit_ns(const at::Tensor& like, uint64_t limit_ns) {
+    c10::cuda::CUDAGuard guard(like.device());
+    uint64_t previous = 0;
+    check_launch("cck_set_wait_limit_ns", cck_set_wait_limit_ns(limit_ns, &previous));
+    return previous;
+}
+
+void wait_limit_selftest(const at::Tensor& a, const at::Tensor& b, const at::Tensor& y, int64_t variant) {
+    for (const auto& named : {std::make_pair("a", &a), std::make_pair("b", &b), std::make_pair("y", &y)})
+        if (tag_of(named.first, *named.second) != CCK_BF16)
+            value_error(std::string("unsupported dtype '") + named.first + " must be bfloat16'");
+    if (a.numel() < 256 * 64 || b.numel() < 256 * 64 || y.numel() < 256 * 256)
+        value_error("shape mismatch: a and b need 256 x 64 elements, y 256 x 256");
+    if (variant < 0 || variant > 2) value_error("variant must be 0 (single CTA), 1 (CTA pair) or 2 (split-K cluster)");
+    Launch l(a, {&b, &y});
+    check_launch("launch_wait_limit_selftest",
+                 launch_wait_limit_selftest(a.data_ptr(), b.data_ptr(), y.data_ptr(), static_cast<int32_t>(variant), l.stream));
+}
+
 }  // namespace
 
 PYBIND11_MODULE(_native, m) {
@@ -919,4 +938,6 @@ PYBIND11_MODULE(_native, m) {
     m.def("lce_finalize", &lce_finalize, py::arg("stats"), py::arg("targets"), py::arg("ignore_index"),
           py::arg("loss_rows").none(true), py::arg("reduce_out"));
     m.def("take_device_status", &take_device_status, py::arg("like"));
+    m.def("set_wait_limit_ns", &set_wait_limit_ns, py::arg("like"), py::arg("limit_ns"));
+    m.def("wait_limit_selftest", &wait_limit_selftest, py::arg("a"), py::arg("b"), py::arg("y"), py::arg("variant"));
 }

@@ -1,7 +1,8 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) features the tensor-core
 // kernels use: mbarrier, TMA tile loads (never multicast), tcgen05 MMA / TMEM.
-// Every wait is bounded: it gives up after kWaitTimeoutNs and reports failure so
-// the kernel can record an error word and leave instead of hanging the GPU.
+// Every wait is bounded: it gives up after the device's wait limit (2 s unless the host
+// changed it, see wait_limit_ns) and reports failure so the kernel can record an error
+// word and leave instead of hanging the GPU.
 #pragma once
 
 #include <cuda.h>
@@ -11,7 +12,14 @@
 namespace cck {
 namespace ptx {
 
-constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kDefaultWaitLimitNs = 2000000000ull;  // 2 s
+
+// The per-device status block every waiting kernel gets a pointer to:
+//   word 0 (32 bit)   error bits, set with atomicOr, read and cleared by cck_take_device_status
+//   bytes 8..15       the wait limit in nanoseconds of %globaltimer (cck_set_wait_limit_ns)
+__device__ __forceinline__ unsigned long long wait_limit_ns(const unsigned int* status_block) {
+    return *reinterpret_cast<const volatile unsigned long long*>(status_block + 2);
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -44,15 +52,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when another thread raised *abort_flag or when
-// the timeout ran out (in which case it raises the flag itself).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// the wait limit ran out (in which case it raises the flag itself).  The limit is
+// read from the status block only on the slow path, after 64 failed polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          const unsigned int* status_block) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer() - t0 > kWaitTimeoutNs) {
+            if (globaltimer() - t0 > wait_limit_ns(status_block)) {
                 *abort_flag = 1;
                 return false;
             }

@@ -11,8 +11,11 @@ produced them, weighting and summing as it goes ("pull", the default: one pass, 
 device time per layer call at 8 GPUs for 8192 tokens x top-2 x 4096 bf16 per rank).  The other
 way back ("push": the dispatch kernel writes every output row into its token's home rank, then
 the local combine runs) is there for comparison; it measured slower (0.72 ms).  The kernels only
-push or pull; the phases are separated by stream-ordered barriers of the symmetric-memory handle,
-and the only other communication is one all-gather of per-expert counts (world x experts ints).
+push or pull and never wait on another GPU; the phases are separated by ``PhaseBarrier``, a
+stream-ordered one-element all-reduce of the process group, so a peer that left or raised between
+two phases surfaces on the others as an exception within the group's timeout instead of a GPU
+spinning on a flag.  The only other communication is one all-gather of per-expert counts (world x
+experts ints).
 
 Receive layout on rank r: blocks in source-rank order; inside a block the rows are sorted by
 expert (ascending) and inside an expert keep the sender's token order - so every sender can
@@ -32,7 +35,28 @@ import torch.distributed as dist
 
 from . import _native
 
-__all__ = ["DispatchPlan", "plan_dispatch", "plan_receive", "plan_return", "plan_on_device", "ExpertParallel"]
+__all__ = ["DispatchPlan", "plan_dispatch", "plan_receive", "plan_return", "plan_on_device", "PhaseBarrier",
+           "ExpertParallel"]
+
+
+class PhaseBarrier:
+    """Separates two phases of the exchange on the current stream: a one-element all-reduce of the
+    process group.  When it completes on a rank, every rank's kernels launched before its own call
+    have finished (their peer-memory stores are visible: a kernel's writes are released at its
+    end, and the collective cannot finish without every rank's contribution, which each rank
+    sends only after its earlier work on the stream).  Unlike a spin on a peer's flag it is
+    covered by the process group's timeout and watchdog: a rank that never arrives turns into an
+    exception (or an aborted communicator) on the others, not a kernel that waits forever.
+    Works on any backend (NCCL on GPUs, gloo on CPU for the tests)."""
+
+    def __init__(self, device, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+        self.passed = 0
+
+    def __call__(self) -> None:
+        dist.all_reduce(self.token, group=self.group)
+        self.passed += 1
 
 
 @dataclass
@@ -129,6 +153,7 @@ class ExpertParallel:
             handle = symm_mem.rendezvous(buf, self.group.group_name)
             return buf, handle, torch.tensor(list(handle.buffer_ptrs), dtype=torch.int64, device=self.device)
 
+        self.barrier = PhaseBarrier(self.device, self.group)
         self.recv, self._recv_h, self.recv_bases = symmetric(capacity_rows)
         # the second buffer: expert outputs where they were computed (pull), or returned rows at home (push)
         self.ret, self._ret_h, self.ret_bases = symmetric(capacity_rows if return_mode == "pull" else max(1, max_local_rows))
@@ -145,7 +170,15 @@ class ExpertParallel:
         maps this rank's received rows ``[R, hidden]`` (with the expert id of every row) to
         ``[R, hidden]``."""
         from .kernels.token_permute import token_combine
+        if topk_indices.dim() != 2:
+            raise ValueError(f"topk_indices must be [T, k], got {tuple(topk_indices.shape)}")
         t, k = topk_indices.shape
+        self._check_rows("x", x, t)
+        if tuple(topk_weights.shape) != (t, k):
+            raise ValueError(f"topk_weights shape {tuple(topk_weights.shape)} must match topk_indices' {(t, k)}")
+        for name, tensor in (("topk_weights", topk_weights), ("topk_indices", topk_indices)):
+            if tensor.device != self.device:
+                raise ValueError(f"{name} is on {tensor.device}, the exchange buffers on {self.device}")
         push = self.return_mode == "push"
         if push and t * k > self.max_local:
             raise ValueError(f"T * k = {t * k} exceeds max_local_rows = {self.max_local}")
@@ -163,7 +196,7 @@ class ExpertParallel:
             plan = plan_dispatch(topk_indices, counts, self.rank, self.experts_per_rank)
             src_row, dst_rank, dst_row = plan.src_row, plan.dst_rank, plan.dst_row
         _native.token_dispatch_fwd(x, src_row, dst_rank, dst_row, self.recv_bases, self.capacity)
-        self._recv_h.barrier()                               # every rank's pushes have landed
+        self.barrier()                                       # every rank's pushes have landed
         if on_device:
             mine = counts[:, self.rank * self.experts_per_rank:(self.rank + 1) * self.experts_per_rank]
             ids = torch.arange(self.rank * self.experts_per_rank, (self.rank + 1) * self.experts_per_rank, device=self.device)
@@ -172,13 +205,14 @@ class ExpertParallel:
             n_rows, expert_of_row = plan_receive(counts, self.rank, self.experts_per_rank)
         if n_rows:
             y = expert_fn(self.recv[:n_rows], expert_of_row)
+            self._check_rows("expert_fn's output", y, n_rows, contiguous=False)
             if push:
                 home, slot = plan_return(counts, self.rank, self.experts_per_rank)
                 _native.token_dispatch_fwd(y.contiguous(), torch.arange(n_rows, device=self.device), home, slot,
                                            self.ret_bases, self.max_local)
             else:
                 self.ret[:n_rows].copy_(y)
-        self._ret_h.barrier()                                # outputs are where the combine looks for them
+        self.barrier()                                       # outputs are where the combine looks for them
         if push:
             # the next call's first barrier keeps peers from overwriting `ret` before this combine ran
             return token_combine(self.ret[:t * k], plan.slot_of, topk_weights)
@@ -186,81 +220,18 @@ class ExpertParallel:
         if not on_device:
             pull_rank, pull_row = plan.dst_rank[plan.slot_of].contiguous(), plan.dst_row[plan.slot_of].contiguous()
         _native.token_combine_remote_fwd(self.ret_bases, self.capacity, pull_rank, pull_row, topk_weights, combined)
-        self._ret_h.barrier()                                # nobody still reads the buffers the next call overwrites
+        self.barrier()                                       # nobody still reads the buffers the next call overwrites
         return combined
 
-
-def _benchmark(tokens: int = 8192, k: int = 2, hidden: int = 4096, iters: int = 10) -> None:
-    """One process per GPU (launch with ``python -m torch.distributed.run --nproc-per-node N -m
-    custom_cuda_kernals_b200.ep``): a layer call with identity experts through ``ExpertParallel``
-    against the same exchange through local gather + two ``all_to_all_single`` + local combine,
-    CUDA events, max over ranks; rank 0 prints one JSON line."""
-    import json
-    import os
-
-    from .kernels.token_permute import token_combine, token_gather
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-    dev = torch.device("cuda", torch.cuda.current_device())
-    dist.init_process_group("nccl", device_id=dev)
-    experts = 8 * world
-    epr = experts // world
-    g = torch.Generator(device=dev).manual_seed(rank)
-    x = torch.randn(tokens, hidden, device=dev, generator=g).to(torch.bfloat16)
-    idx = torch.stack([torch.randperm(experts, device=dev, generator=g)[:k] for _ in range(64)]).repeat(tokens // 64, 1)
-    w = torch.rand(tokens, k, device=dev, generator=g)
-    layer = ExpertParallel(experts, hidden, capacity_rows=3 * tokens * k, device=dev)
-
-    def fused():
-        return layer.forward(x, w, idx, lambda rows, ids: rows)
-
-    def nccl_path():
-        counts = layer.exchange_counts(idx)
-        per_rank = counts.reshape(world, world, epr).sum(-1)
-        order = torch.argsort(idx.reshape(-1), stable=True)
-        send = token_gather(x, torch.div(order, k, rounding_mode="floor"))
-        to_peers, from_peers = per_rank[rank].tolist(), per_rank[:, rank].tolist()
-        recv = torch.empty(sum(from_peers), hidden, dtype=x.dtype, device=dev)
-        dist.all_to_all_single(recv, send, from_peers, to_peers)
-        back = torch.empty_like(send)
-        dist.all_to_all_single(back, recv, to_peers, from_peers)
-        inverse = torch.empty_like(order)
-        inverse[order] = torch.arange(order.numel(), device=dev)
-        return token_combine(back, inverse.reshape(tokens, k), w)
-
-    same = bool(torch.equal(fused(), nccl_path()))
-    counts = layer.exchange_counts(idx)
-    src_row, dst_rank, dst_row, pull_rank, pull_row, _ = plan_on_device(idx, counts, rank)
-    out = torch.empty(tokens, hidden, dtype=x.dtype, device=dev)
-
-    def kernels_only():
-        _native.token_dispatch_fwd(x, src_row, dst_rank, dst_row, layer.recv_bases, layer.capacity)
-        layer._recv_h.barrier()
-        _native.token_combine_remote_fwd(layer.recv_bases, layer.capacity, pull_rank, pull_row, w, out)
-        layer._recv_h.barrier()
-
-    def timed(fn):
-        for _ in range(3):
-            fn()
-        dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        ms = torch.tensor([a.elapsed_time(b) / iters], device=dev)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return round(ms.item(), 3)
-
-    line = {"world": world, "tokens_per_rank": tokens, "k": k, "hidden": hidden, "same_as_nccl_path": same,
-            "layer_call_ms": timed(fused), "nccl_path_ms": timed(nccl_path), "kernels_and_barriers_ms": timed(kernels_only),
-            "row_bytes_per_rank_each_way": tokens * k * hidden * 2, "remote_fraction": round(1 - 1 / world, 3)}
-    if rank == 0:
-        print(json.dumps(line), flush=True)
-    dist.destroy_process_group()
-
-
-if __name__ == "__main__":
-    _benchmark()
+    def _check_rows(self, name, rows, n_rows, contiguous=True):
+        """The exchange kernels take the row pitch from the tensor they are given, while the
+        receive buffers' capacity is counted in rows of ``hidden`` elements of ``dtype``: a wider
+        or differently typed row would be written past a peer's buffer, so refuse it here."""
+        if rows.dim() != 2 or tuple(rows.shape) != (n_rows, self.hidden):
+            raise ValueError(f"{name} must be [{n_rows}, {self.hidden}], got {tuple(rows.shape)}")
+        if rows.dtype != self.dtype:
+            raise ValueError(f"{name} is {rows.dtype}, the exchange buffers are {self.dtype}")
+        if rows.device != self.device:
+            raise ValueError(f"{name} is on {rows.device}, the exchange buffers on {self.device}")
+        if contiguous and not rows.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")

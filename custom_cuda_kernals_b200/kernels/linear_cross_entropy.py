@@ -102,15 +102,20 @@ def lce_lse_from_stats(stats: torch.Tensor) -> torch.Tensor:
     return (m + torch.log(total)).contiguous()
 
 
-def _local_targets(targets: torch.Tensor, v_start: int, v: int, ignore_index: int) -> torch.Tensor:
-    """Targets as column indices of a vocabulary shard: ignored rows keep ``ignore_index``, rows
-    whose target lies in another shard get a value that matches no column."""
+_IGNORED, _ELSEWHERE = -1, -2
+
+
+def _local_targets(targets: torch.Tensor, v_start: int, v: int, ignore_index: int) -> tuple[torch.Tensor, int]:
+    """Targets as column indices of a vocabulary shard, and the value that marks an ignored row
+    in them.  "Ignored" is decided on the GLOBAL ids: with ``ignore_index >= 0`` (a pad id, say 0)
+    a real target whose local index happens to equal ``ignore_index`` must not be dropped on the
+    shard that starts ``ignore_index`` columns below it.  So on a shard with ``v_start > 0``
+    ignored rows become -1 and rows whose target lies in another shard -2 (matches no column)."""
     if v_start == 0:
-        return targets       # out-of-range targets match no column already
-    outside = -1 if ignore_index != -1 else -2
+        return targets, ignore_index       # local == global; out-of-range targets match no column already
     local = targets - v_start
-    local = torch.where((local >= 0) & (local < v), local, torch.full_like(local, outside))
-    return torch.where(targets == ignore_index, targets, local).contiguous()
+    local = torch.where((local >= 0) & (local < v), local, torch.full_like(local, _ELSEWHERE))
+    return torch.where(targets == ignore_index, torch.full_like(local, _IGNORED), local).contiguous(), _IGNORED
 
 
 def lce_grad_scale(targets: torch.Tensor, ignore_index: int, reduction: str) -> float:
@@ -163,7 +168,7 @@ def lce_stats_and_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets:
     if not (_fused_ok(hidden, weight) and hidden.is_cuda) or v % 8 != 0:
         raise ValueError("the gradient path needs float16/bfloat16 CUDA inputs with H and V multiples of 8")
     dev, dt = hidden.device, hidden.dtype
-    local = _local_targets(targets, v_start, v, ignore_index)
+    local, local_ignore = _local_targets(targets, v_start, v, ignore_index)
     w_t = weight_t if weight_t is not None else _padded_transpose(weight)             # [H, V]
     d_hidden = torch.empty_like(hidden)
     one_chunk = n <= rows_per_chunk
@@ -194,14 +199,14 @@ def lce_stats_and_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets:
         stats_parts.append(stats)
         lse = lce_lse_from_stats(stats)
         if recompute:
-            _native.lce_dlogits_fwd(hc, weight, local[r0:r1], lse, ignore_index, grad_scale, dl)
+            _native.lce_dlogits_fwd(hc, weight, local[r0:r1], lse, local_ignore, grad_scale, dl)
             dl_t = _padded_transpose(dl, width)
         else:
             if side_by_side:
                 dl_t = dl_t_all[:, r0:r0 + width]
             else:
                 dl_t = (torch.empty if width == rows else torch.zeros)(v, width, dtype=dt, device=dev)
-            _native.lce_dlogits_from_logits(logits[:rows], local[r0:r1], lse, ignore_index, grad_scale, dl, dl_t)
+            _native.lce_dlogits_from_logits(logits[:rows], local[r0:r1], lse, local_ignore, grad_scale, dl, dl_t)
         _native.matmul_add_bias_fwd(dl, w_t, None, d_hidden[r0:r1])                # [r, V] x [H, V]^T
         if side_by_side:
             continue

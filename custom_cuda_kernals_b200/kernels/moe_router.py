@@ -16,14 +16,17 @@ __all__ = ["moe_router"]
 
 
 def moe_router(logits: torch.Tensor, k: int, renormalize: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
-    """``topk_weights, topk_indices = topk(softmax(logits, dim=-1), k)``, optionally renormalised.
+    """Routes every token to its ``k`` most probable experts.
 
-    logits: ``[T, E]`` contiguous CUDA tensor, ``E <= 256``.  Returns ``topk_weights: [T, k]``
-    (float32, descending) and ``topk_indices: [T, k]`` (int64; equal probabilities go to the
-    lower expert id).  ``k > E`` raises ``RuntimeError`` as ``torch.topk`` does.
+    ``logits`` holds one row of ``E`` gate scores per token (2-D, contiguous, on the GPU; at most
+    256 experts).  Each row goes through a softmax evaluated in fp32; the ``k`` largest
+    probabilities come back in descending order as ``[T, k]`` float32 together with their expert
+    ids as ``[T, k]`` int64, ties going to the lower id.  With ``renormalize`` the kept
+    probabilities are divided by their sum.  Asking for more experts than there are raises
+    ``RuntimeError``, like ``torch.topk``.
     """
-    n_tokens = logits.shape[0]
-    topk_weights = torch.empty((n_tokens, k), dtype=torch.float32, device=logits.device)
-    topk_indices = torch.empty((n_tokens, k), dtype=torch.long, device=logits.device)
-    _native.moe_router_fwd(logits, topk_weights, topk_indices, renormalize)
-    return topk_weights, topk_indices
+    shape = (logits.shape[0], k)
+    weights = torch.empty(shape, dtype=torch.float32, device=logits.device)
+    experts = torch.empty(shape, dtype=torch.long, device=logits.device)
+    _native.moe_router_fwd(logits, weights, experts, renormalize)
+    return weights, experts

@@ -105,8 +105,9 @@ int64_t cck_lce_num_splits(int64_t n, int64_t v_count);
  * held by every GPU that loads it.  No allocation or free is made.  Returns
  * cudaErrorInvalidValue, launching nothing, when cck_lce_workspace_bytes(n, v_count) exceeds
  * cck_lce_noalloc_max_workspace_bytes().  The first call on a device looks up the array's
- * address and should be made outside stream capture.  Calls share the array: calls that overlap
- * on the GPU race and must be serialised by the caller. */
+ * address and should be made outside stream capture (host threads may make it concurrently: each
+ * caches the same address).  Calls share the array: calls that overlap on the GPU race and must
+ * be serialised by the caller. */
 int32_t launch_linear_cross_entropy_fwd_noalloc(const void* hidden, const void* weight, const int64_t* targets,
                                                 int64_t v_start, int64_t n, int64_t h, int64_t v_count,
                                                 float* row_stats, int32_t dtype, void* stream);
@@ -261,6 +262,24 @@ int32_t cck_gemm_pair_capacity(void);
 /* Reads and clears the error word of the tensor-core kernels on the current device (bit 0: a
  * bounded wait inside a kernel ran out and the kernel gave up).  Synchronises the device. */
 int32_t cck_take_device_status(uint32_t* out);
+
+/* Limit, in nanoseconds of the GPU's global timer, of every bounded wait inside this library's
+ * kernels on the current device (mbarrier waits of the tensor-core GEMMs and of the TMA-staged
+ * FP8 block quantiser).  The library starts with 2 s; values are clamped to [1 us, 10 s].  The
+ * previous limit is returned in *previous_ns (may be NULL).  Synchronises the device.  No
+ * reference counterpart: the reference's kernels never wait. */
+int32_t cck_set_wait_limit_ns(uint64_t limit_ns, uint64_t* previous_ns);
+
+/* Self-test of the give-up path: launches ONE tile of a real GEMM kernel whose A tensor map
+ * delivers half the bytes the kernel's "stage full" barrier counts on, so that barrier never
+ * completes, no MMA is issued, and the waiting roles run into the wait limit.  Expected outcome:
+ * the kernel returns by itself, y is left unwritten, cck_take_device_status() reports bit 0, and
+ * the next launch works (tensor memory was freed).  Nothing faults.  Call cck_set_wait_limit_ns
+ * with about a millisecond first and restore the limit afterwards.
+ *   a, b: [256, 64] bfloat16 each (16-byte aligned), y: [256, 256] bfloat16
+ *   variant 0: single-CTA kernel, 1: CTA-pair kernel (cta_group::2), 2: cluster split-K kernel
+ * No reference counterpart. */
+int32_t launch_wait_limit_selftest(const void* a, const void* b, void* y, int32_t variant, void* stream);
 
 #ifdef __cplusplus
 }

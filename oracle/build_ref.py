@@ -12,11 +12,15 @@ B200 beside ours.  The reference's Rust/PyO3 layer is not needed for either and 
 here (no Rust toolchain).
 
     python oracle/build_ref.py --reference /path/to/reference
+
+Without ``--reference`` the checkout is looked for in ``$CUSTOM_CUDA_REFERENCE`` and then in a
+directory named ``reference`` beside this repository; if neither exists nothing is built.
 """
 
 from __future__ import annotations
 
 import argparse
+import os
 import pathlib
 import shutil
 import subprocess
@@ -27,6 +31,15 @@ OUT = HERE / "_ref"
 LIB = OUT / "libcustom_cuda_ref.so"
 KERNELS = ["rmsnorm_residual", "swiglu", "rope", "fp8_quant", "matmul_add_bias", "linear_cross_entropy",
            "moe_router", "token_permute"]
+
+
+def find_reference() -> pathlib.Path | None:
+    """A checkout of the reference project: ``$CUSTOM_CUDA_REFERENCE``, else a ``reference``
+    directory beside this repository.  None when neither holds ``csrc/kernels``."""
+    for cand in (os.environ.get("CUSTOM_CUDA_REFERENCE"), HERE.parent.parent / "reference"):
+        if cand and (pathlib.Path(cand) / "csrc" / "kernels").is_dir():
+            return pathlib.Path(cand)
+    return None
 
 
 def build(reference: str | pathlib.Path, verbose: bool = False) -> pathlib.Path | None:
@@ -55,11 +68,12 @@ def build(reference: str | pathlib.Path, verbose: bool = False) -> pathlib.Path 
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None)
     ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args()
-    lib = build(a.reference, a.verbose)
-    print(f"built {lib}" if lib else f"no reference checkout at {a.reference}; nothing built")
+    reference = a.reference or find_reference()
+    lib = build(reference, a.verbose) if reference else None
+    print(f"built {lib}" if lib else f"no reference checkout ({reference}); nothing built")
     return 0
 
 

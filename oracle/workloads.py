@@ -92,6 +92,26 @@ def block_input(batch=8, seq=2048, hidden=4096, salt=0, dtype=torch.bfloat16):
     return (0.02 * torch.randn(batch, seq, hidden, generator=g)).to(dtype)
 
 
+# decoder-block pins: name -> (architecture overrides of LLAMA3_8B, batch, seq)
+BLOCK_PINS = {
+    "small_gqa": (dict(hidden=256, ffn=512, n_heads=8, n_kv_heads=2, head_dim=32), 2, 48),
+    "small_mha": (dict(hidden=128, ffn=384, n_heads=4, n_kv_heads=4, head_dim=32), 3, 17),
+    "llama3_8b_seq64": (dict(), 1, 64),
+}
+
+
+def block_pin_inputs(name):
+    """Weights and input of one decoder-block pin: the benchmark's seeded generators, with
+    norm weights 1 + 0.1 N(0,1) instead of ones so that the norm-weight multiply is exercised."""
+    over, batch, seq = BLOCK_PINS[name]
+    cfg = dict(LLAMA3_8B, **over)
+    w = block_weights(cfg)
+    g = torch.Generator().manual_seed(4242)
+    for key in ("input_layernorm_weight", "post_attention_layernorm_weight"):
+        w[key] = (1.0 + 0.1 * torch.randn(cfg["hidden"], generator=g)).to(torch.bfloat16)
+    return cfg, w, block_input(batch, seq, cfg["hidden"])
+
+
 def lce_bf16(tokens=16384, hidden=4096, vocab=128256, ignore_fraction=0.05, salt=0):
     """Config 5: hidden ~ N(0,1), LM-head W[V,H] ~ N(0,0.02), labels uniform
     with 5 % replaced by -100.

@@ -13,6 +13,14 @@ the reference's ``ALL_CASES`` tables (on CPU, seed 0):
   2. checks that ``oracle.ops.*`` reproduces the reference's ``eager_*``
      (and ``reference_fp64``) outputs bit for bit;
 
+  3. builds the reference's own decoder block (``BaselineLlamaBlock`` of
+     ``examples/llama_block.py:83-189``, ``device="cpu"``) on a small and on a
+     Llama-3-8B-shaped configuration, loads the oracle's seeded weights into
+     it and checks that ``oracle.ops.llama_block`` reproduces its output bit
+     for bit (the example imports ``custom_cuda.kernels``; this repository's
+     alias package of that name is imported first, so the built ``_native``
+     module must exist, no GPU is needed);
+
 then stores, for a set of small cases, the reference's outputs in
 ``golden_small.pt`` and, for every FP8 case, a SHA-256 of the reference's code
 bytes and scale bytes in ``fp8_digests.json``.  ``pin_report.json`` records
@@ -35,7 +43,7 @@ HERE = pathlib.Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
 
-from oracle import cases, ops  # noqa: E402
+from oracle import cases, ops, workloads  # noqa: E402
 
 SMALL = {
     "rmsnorm": ["npot_hidden", "single_elem"],
@@ -78,6 +86,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
     args = ap.parse_args()
+    # this repository's alias package, before the reference checkout goes first on sys.path:
+    # the reference's decoder-block example imports the same names
+    import custom_cuda.kernels.rmsnorm_residual  # noqa: F401
+    import custom_cuda.kernels.rope  # noqa: F401
+    import custom_cuda.kernels.swiglu  # noqa: F401
     sys.path.insert(0, args.reference)
     ref = {k: importlib.import_module(f"baselines.{m}") for k, m in {
         "rmsnorm": "rmsnorm_residual", "swiglu": "swiglu", "rope": "rope", "fp8": "fp8_quant",
@@ -231,6 +244,24 @@ def main():
     rp, mp = ref["permute"].compute_permutation(topk), ops.compute_permutation(topk)
     note("combine", True, all(same(a, b) for a, b in zip(rp, mp)), "compute_permutation")
     golden["combine/compute_permutation"] = {"topk": topk, "permute_index": rp[0], "unpermute_index": rp[1]}
+
+    # ---- the decoder block (examples/llama_block.py:83-189; acceptance check :271-283)
+    example = importlib.import_module("examples.llama_block")
+    for name in workloads.BLOCK_PINS:
+        cfg, w, x = workloads.block_pin_inputs(name)
+        blk = example.BaselineLlamaBlock(
+            hidden_size=cfg["hidden"], intermediate_size=cfg["ffn"], num_heads=cfg["n_heads"],
+            num_kv_heads=cfg["n_kv_heads"], seq_len=x.shape[1], rms_eps=cfg["eps"], rope_theta=cfg["theta"],
+            dtype=torch.bfloat16, device="cpu")
+        with torch.no_grad():
+            for key, t in w.items():
+                target = getattr(blk, key)
+                (target.weight if isinstance(target, torch.nn.Linear) else target).copy_(t)
+            ro = blk(x)
+            mo = ops.llama_block(x, w, n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"], eps=cfg["eps"],
+                                 theta=cfg["theta"])
+        note("block", True, same(ro, mo), name)
+        golden[f"block/{name}"] = {"y": ro}
 
     torch.save(golden, HERE / "golden_small.pt")
     (HERE / "fp8_digests.json").write_text(json.dumps(digests, indent=0, sort_keys=True))

@@ -78,7 +78,7 @@ def test_vocab_parallel_exchange_two_gloo_ranks(tmp_path):
     assert outs[0]["range"][1] == outs[1]["range"][0]
 
 
-def _grad_rank_main(rank, world, port, out_dir, scatter):
+def _grad_rank_main(rank, world, port, out_dir, scatter, ignore_index=-100):
     """The vocabulary-parallel gradient path on two gloo ranks.  The three GPU kernels it
     calls are replaced by fp32 torch stand-ins; the target localisation, the log-sum-exp
     merge, the gradient scale and both collectives are the library's own."""
@@ -97,11 +97,14 @@ def _grad_rank_main(rank, world, port, out_dir, scatter):
                             gather=None, recompute=False):
         stats = gather(torch.stack(ops.lce_partials(h, w, t, v_start)).float())
         lse = lce.lce_lse_from_stats(stats)
-        local = lce._local_targets(t, v_start, w.shape[0], ignore_index)
+        # like the dlogits kernels: a row is ignored when its LOCAL target equals the marker the
+        # library passes along with the local targets - nothing here looks at the global ids
+        local, local_ignore = lce._local_targets(t, v_start, w.shape[0], ignore_index)
+        keep = local != local_ignore
         dl = torch.exp(h.float() @ w.float().T - lse[:, None])
-        hit = (local >= 0) & (local < w.shape[0]) & (t != ignore_index)
+        hit = (local >= 0) & (local < w.shape[0]) & keep
         dl[hit.nonzero().squeeze(1), local[hit]] -= 1.0
-        dl = dl * scale * (t != ignore_index)[:, None]
+        dl = dl * scale * keep[:, None]
         return stats, dl @ w.float(), dl.T @ h.float()
 
     lce.lce_loss_from_stats, lce.lce_stats_and_gradients = loss_from_stats, stats_and_gradients
@@ -110,25 +113,30 @@ def _grad_rank_main(rank, world, port, out_dir, scatter):
     h = torch.randn(n, hd, generator=g)
     w = 0.2 * torch.randn(v, hd, generator=g)
     t = torch.randint(0, v, (n,), generator=g)
-    t[::7] = -100
-    t[1] = dist.vocab_range(v, 1, world)[0] - 100   # its index within shard 1 equals ignore_index: must not be ignored
+    t[::7] = ignore_index
+    # a real target whose index WITHIN shard 1 equals ignore_index: must not be ignored there
+    t[1] = dist.vocab_range(v, 1, world)[0] + ignore_index
     v0, v1 = dist.vocab_range(v, rank, world)
-    loss, dh, dw = dist.vocab_parallel_linear_cross_entropy_fwd_bwd(h, w[v0:v1], t, v0, scatter_rows=scatter)
+    loss, dh, dw = dist.vocab_parallel_linear_cross_entropy_fwd_bwd(h, w[v0:v1], t, v0, ignore_index=ignore_index,
+                                                                    scatter_rows=scatter)
     torch.save({"loss": loss, "dh": dh, "dw": dw, "range": (v0, v1)}, os.path.join(out_dir, f"g{rank}.pt"))
     td.destroy_process_group()
 
 
-def test_vocab_parallel_gradients_two_gloo_ranks(tmp_path):
+@pytest.mark.parametrize("ignore_index", [-100, 0])
+def test_vocab_parallel_gradients_two_gloo_ranks(tmp_path, ignore_index):
+    """``ignore_index`` 0 is a pad id inside the vocabulary: the first column of shard 1 has local
+    index 0 and is a real target there."""
     world = 2
-    mp.spawn(_grad_rank_main, args=(world, _free_port(), str(tmp_path), False), nprocs=world, join=True)
+    mp.spawn(_grad_rank_main, args=(world, _free_port(), str(tmp_path), False, ignore_index), nprocs=world, join=True)
     g = torch.Generator().manual_seed(5)
     n, hd, v = 64, 32, 384
     h = torch.randn(n, hd, generator=g).requires_grad_(True)
     w = (0.2 * torch.randn(v, hd, generator=g)).requires_grad_(True)
     t = torch.randint(0, v, (n,), generator=g)
-    t[::7] = -100
-    t[1] = dist.vocab_range(v, 1, world)[0] - 100
-    want = torch.nn.functional.cross_entropy(h @ w.T, t, ignore_index=-100)
+    t[::7] = ignore_index
+    t[1] = dist.vocab_range(v, 1, world)[0] + ignore_index
+    want = torch.nn.functional.cross_entropy(h @ w.T, t, ignore_index=ignore_index)
     want.backward()
     outs = [torch.load(tmp_path / f"g{r}.pt") for r in range(world)]
     for o in outs:
@@ -158,6 +166,46 @@ def test_a_rank_that_never_joins_surfaces_as_an_error_on_the_survivor(tmp_path):
     all-gather ends with an exception within the process-group timeout instead of waiting forever."""
     mp.spawn(_rank_that_loses_its_peer, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     assert (tmp_path / "r0.txt").read_text() != "completed"
+
+
+def test_local_targets_decide_ignored_on_global_ids():
+    from custom_cuda_kernals_b200.kernels.linear_cross_entropy import _local_targets
+    t = torch.tensor([0, 5, 128, 133, 300, 0])
+    local, marker = _local_targets(t, 128, 128, 0)            # shard [128, 256), pad id 0
+    assert marker == -1 and local.tolist() == [-1, -2, 0, 5, -2, -1]
+    local, marker = _local_targets(t, 0, 128, 0)              # first shard: local ids are the global ids
+    assert marker == 0 and local is t
+    local, marker = _local_targets(torch.tensor([-100, 28, 200]), 128, 128, -100)
+    assert marker == -1 and local.tolist() == [-1, -2, 72]
+
+
+def _phase_rank(rank, world, port, out_dir, leaver):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_from_env(timeout_s=8)
+    from custom_cuda_kernals_b200.ep import PhaseBarrier
+    barrier = PhaseBarrier("cpu")
+    outcome = "completed"
+    try:
+        barrier()                   # after "dispatch": every rank is there
+        if rank == leaver:
+            return                  # raises / leaves between the phases, nothing in flight
+        barrier()                   # after "expert outputs": the leaver never arrives
+    except Exception as e:
+        outcome = type(e).__name__
+    with open(os.path.join(out_dir, f"phase{rank}.txt"), "w") as f:
+        f.write(f"{outcome} {barrier.passed}")
+
+
+def test_phase_barrier_completes_and_surfaces_a_rank_that_left_between_phases(tmp_path):
+    """The expert-parallel exchange separates its phases with PhaseBarrier.  Two healthy ranks
+    pass both barriers; when one rank leaves after the first phase, the survivor's second barrier
+    ends with an exception inside the process-group timeout - it does not wait forever."""
+    mp.spawn(_phase_rank, args=(2, _free_port(), str(tmp_path), -1), nprocs=2, join=True)
+    assert [(tmp_path / f"phase{r}.txt").read_text() for r in range(2)] == ["completed 2", "completed 2"]
+    mp.spawn(_phase_rank, args=(2, _free_port(), str(tmp_path), 1), nprocs=2, join=True)
+    outcome, passed = (tmp_path / "phase0.txt").read_text().split()
+    assert outcome != "completed" and passed == "1"
 
 
 def test_single_process_needs_no_group():

@@ -213,3 +213,29 @@ def test_plans_are_a_bijection_onto_dense_buffers_for_random_routings():
             assert torch.equal(home[rows], torch.cat(sources)) and torch.equal(slot[rows], torch.cat(slots))
 
     check()
+
+
+def test_forward_refuses_rows_that_do_not_match_the_exchange_buffers():
+    """The exchange kernels take the row pitch from the tensor they are handed while capacity is
+    counted in buffer rows, so a wider, differently typed or strided ``x`` (or expert output) must
+    be refused on the host before any row is sent.  Checked on a layer object without buffers:
+    the checks run before anything touches them."""
+    layer = object.__new__(ep.ExpertParallel)
+    layer.hidden, layer.dtype, layer.device = 64, torch.bfloat16, torch.device("cpu")
+    layer.return_mode, layer.max_local = "pull", 0
+    idx = torch.zeros(10, 2, dtype=torch.long)
+    w = torch.rand(10, 2)
+    good = torch.zeros(10, 64, dtype=torch.bfloat16)
+    for bad, what in [(torch.zeros(10, 128, dtype=torch.bfloat16), r"must be \[10, 64\]"),
+                      (torch.zeros(9, 64, dtype=torch.bfloat16), r"must be \[10, 64\]"),
+                      (torch.zeros(10, 64, dtype=torch.float16), "exchange buffers are"),
+                      (torch.zeros(10, 128, dtype=torch.bfloat16)[:, ::2], "contiguous"),
+                      (torch.zeros(640, dtype=torch.bfloat16), r"must be \[10, 64\]")]:
+        with pytest.raises(ValueError, match=what):
+            layer.forward(bad, w, idx, _expert)
+    with pytest.raises(ValueError, match="topk_weights shape"):
+        layer.forward(good, torch.rand(10, 3), idx, _expert)
+    with pytest.raises(ValueError, match=r"topk_indices must be \[T, k\]"):
+        layer.forward(good, w, idx.reshape(-1), _expert)
+    with pytest.raises(ValueError, match="expert_fn's output"):
+        layer._check_rows("expert_fn's output", torch.zeros(7, 32, dtype=torch.bfloat16), 7, contiguous=False)

@@ -1,15 +1,23 @@
 """GPU parity: the Llama decoder block (examples/llama_block.py:158-173 structure) built
 from this library's ops, against the CPU oracle block with the same weights.
 
-A seven-GEMM bf16 chain cannot be compared bit for bit across machines: torch's own eager
-bf16 block on GPU and on CPU differ on about 3 % of the elements at the reference's block
-tolerance (rtol 1e-2, atol 2e-2; examples/llama_block.py:271-283 compares two blocks that
-share cuBLAS and SDPA, so only its three fused ops differ).  The bars here: (1) measured
-against an fp32 evaluation of the same block, the GPU result is as accurate as the oracle's
-bf16 result; (2) elementwise against the oracle within the reference's tolerance on >= 95 %
-of the elements; (3) against the same block written with torch's own GPU ops (F.linear,
-eager norm / rope / swiglu), where only accumulation order differs, within that tolerance
-on all but 2e-3 of the elements (measured: 3e-5 to 6e-4)."""
+The oracle block is pinned bit for bit to the reference's own BaselineLlamaBlock on CPU
+(tests/golden/make_golden.py, pin_report.json "block").  A seven-GEMM bf16 chain cannot be
+compared bit for bit across machines: torch's own eager bf16 block on GPU and on CPU differ on
+2.2 % (192-token sequences) to 5.9 % (2048-token sequences) of the elements at the reference's
+block tolerance (rtol 1e-2, atol 2e-2; examples/llama_block.py:271-283 compares two blocks that
+share cuBLAS and SDPA, so only its three fused ops differ).  The bars, each the value measured
+on B200 plus a stated margin:
+
+  (1) against an fp32 evaluation of the same block, the GPU result is as accurate as the
+      oracle's bf16 result (rms error ratio <= 1.25; at full size also against torch's own bf16
+      GPU ops, ratio <= 1.1);
+  (2) elementwise against the CPU oracle at the reference's tolerance: no further from it than
+      torch's own GPU ops are (<= 1.1 x their outlier fraction + 1e-3), and in absolute terms
+      <= 3 % at 192 tokens (measured 2.21 %), <= 7.5 % at 2048 tokens (measured 5.93-6.02 %);
+  (3) against the same block written with torch's own GPU ops (F.linear, SDPA, eager norm /
+      rope / swiglu), where only accumulation order differs: <= 2e-3 at 192 tokens (measured
+      4.5e-4 to 6.7e-4), <= 1.2e-2 at 2048 tokens (measured 5.8e-3 to 8.4e-3 per sequence)."""
 
 import pytest
 import torch
@@ -38,6 +46,11 @@ def _gpu_eager_block(x, w, n_heads, n_kv, eps, theta):
     return F.linear(ops.swiglu(F.linear(h2, w["gate_proj"]), F.linear(h2, w["up_proj"])), w["down_proj"]) + res2
 
 
+def _outside(a, b):
+    """Fraction of elements outside the reference's block tolerance (examples/llama_block.py:271-283)."""
+    return float(((a - b).abs() > 2e-2 + 1e-2 * b.abs()).float().mean())
+
+
 def _check(cfg, batch, seq):
     from custom_cuda_kernals_b200.llama_block import LlamaBlock
     w = workloads.block_weights(cfg)
@@ -59,9 +72,9 @@ def _check(cfg, batch, seq):
     got = got_dev.cpu().float()
     rms = lambda t: float(t.pow(2).mean().sqrt())
     assert rms(got - truth) <= 1.25 * rms(want - truth)
-    outside = lambda a, b: float(((a - b).abs() > 2e-2 + 1e-2 * b.abs()).float().mean())
-    assert outside(got, want) <= 0.05
-    assert outside(got, eager_dev.cpu().float()) <= 2e-3
+    eager = eager_dev.cpu().float()
+    assert _outside(got, want) <= min(0.03, 1.1 * _outside(eager, want) + 1e-3)
+    assert _outside(got, eager) <= 2e-3
     assert device_status_clean(got_dev)
 
 
@@ -99,28 +112,32 @@ def test_block_is_deterministic_and_batch_independent():
 
 
 def test_block_config4_full_size():
-    """Benchmark config 4 at full size (batch 8 x seq 2048): against the CPU oracle block on all
-    16384 tokens, against its fp32 evaluation on one sequence, and sequence independence (the
-    rows a rank would compute for sequences 6..7 are the same rows).  Two bf16 evaluations of
-    this chain drift further apart over 2048-token attention rows than over the 192-token ones
-    above (measured: 6 % of the elements beyond rtol 1e-2 / atol 2e-2), so the elementwise
-    budget here is 10 %; the accuracy bar is the comparison with the fp32 evaluation."""
+    """Benchmark config 4 at full size (batch 8 x seq 2048), all 16384 tokens: against the CPU
+    oracle block, against the same block on torch's own GPU ops (bf16, and fp32 as the common
+    truth), and sequence independence (the rows a rank would compute for sequences 6..7 are the
+    same rows).  Bars as listed at the top of this file."""
     from custom_cuda_kernals_b200.llama_block import LlamaBlock
     cfg = dict(workloads.LLAMA3_8B)
     w = workloads.block_weights(cfg)
     x = workloads.block_input(8, 2048, cfg["hidden"])
     kw = dict(n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"], eps=cfg["eps"], theta=cfg["theta"])
+    arch = (cfg["n_heads"], cfg["n_kv_heads"], cfg["eps"], cfg["theta"])
     with torch.no_grad():
         want = ops.llama_block(x, w, **kw).float()
-        truth = ops.llama_block(x[:1].float(), {k: v.float() for k, v in w.items()}, **kw)
-        block = LlamaBlock({k: v.to(DEV) for k, v in w.items()}, cfg["n_heads"], cfg["n_kv_heads"], cfg["eps"],
-                           cfg["theta"], max_seq_len=2048)
+        wd = {k: v.to(DEV) for k, v in w.items()}
+        block = LlamaBlock(dict(wd), *arch, max_seq_len=2048)
         xd = x.to(DEV)
         got_dev = block(xd)
         part = block(xd[6:8].contiguous())
+        eager = _gpu_eager_block(xd, wd, *arch).cpu().float()
+        w32 = {k: v.float() for k, v in wd.items()}
+        truth = torch.cat([_gpu_eager_block(xd[i:i + 1].float(), w32, *arch).cpu() for i in range(8)])
     got = got_dev.cpu().float()
     rms = lambda t: float(t.pow(2).mean().sqrt())
-    assert rms(got[:1] - truth) <= 1.25 * rms(want[:1] - truth)
-    assert float(((got - want).abs() > 2e-2 + 1e-2 * want.abs()).float().mean()) <= 0.10
+    assert rms(got - truth) <= 1.1 * rms(eager - truth)             # as accurate as torch's bf16 GPU ops ...
+    assert rms(got - truth) <= 1.25 * rms(want - truth)             # ... and as the CPU oracle
+    assert _outside(got, want) <= min(0.075, 1.1 * _outside(eager, want) + 1e-3)
+    per_sequence = [_outside(got[i], eager[i]) for i in range(8)]
+    assert max(per_sequence) <= 1.2e-2, per_sequence
     assert torch.equal(part, got_dev[6:8])
     assert device_status_clean(got_dev)

@@ -193,6 +193,41 @@ def test_lce_gradients_match_autograd(shape, reduction, mode):
     assert device_status_clean(out)
 
 
+@pytest.mark.parametrize("ignore_index", [-100, 0, 5])
+@pytest.mark.parametrize("recompute", [False, True])
+def test_vocab_sharded_gradients_with_a_pad_id_inside_the_vocabulary(ignore_index, recompute):
+    """Two vocabulary shards emulated as consecutive calls on one GPU (the shards do not wait on
+    each other), against torch autograd.  With ``ignore_index`` 0 or 5 (a pad id) the shard that
+    starts at column 384 holds real targets whose local index equals ``ignore_index``; they must
+    get their gradient, and rows whose GLOBAL target is the pad id must get none."""
+    from custom_cuda_kernals_b200.kernels import linear_cross_entropy as lce
+    n, hdim, v, cut = 200, 128, 768, 384
+    g = torch.Generator().manual_seed(11 + ignore_index)
+    h = torch.randn(n, hdim, generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(v, hdim, generator=g)).to(torch.bfloat16)
+    t = torch.randint(0, v, (n,), generator=g)
+    t[::6] = ignore_index
+    t[1::9] = cut + ignore_index if ignore_index >= 0 else cut     # local index in shard 1 == ignore_index
+    h32, w32 = h.float().requires_grad_(True), w.float().requires_grad_(True)
+    want = torch.nn.functional.cross_entropy(h32 @ w32.T, t, ignore_index=ignore_index)
+    want.backward()
+    hd, wd, td_ = to_dev(h, w, t)
+    shards = [(0, cut), (cut, v)]
+    stats_all = torch.stack([lce.lce_row_stats(hd, wd[a:b].contiguous(), td_, a) for a, b in shards])
+    scale = lce.lce_grad_scale(td_, ignore_index, "mean")
+    dh, dws = torch.zeros(n, hdim, device=DEV), []
+    for a, b in shards:
+        _, dh_part, dw_part = lce.lce_stats_and_gradients(hd, wd[a:b].contiguous(), td_, scale, a, ignore_index,
+                                                          gather=lambda st: stats_all, recompute=recompute)
+        dh += dh_part.float()
+        dws.append(dw_part)
+    loss = lce.lce_loss_from_stats(stats_all, td_, ignore_index, "mean")
+    torch.testing.assert_close(loss.cpu(), want.detach(), rtol=1e-4, atol=1e-5)
+    _grad_close(dh, h32.grad, "d_hidden")
+    _grad_close(torch.cat(dws), w32.grad, "d_weight")
+    assert torch.all(dh[t == ignore_index] == 0) and torch.all(dh[1::9][t[1::9] != ignore_index].abs().sum(1) > 0)
+
+
 @pytest.mark.parametrize("n,v", [(64, 64), (200, 1000), (77, 332), (1, 8), (513, 4100)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_dlogits_from_logits_row_major_and_transposed(n, v, dtype):
