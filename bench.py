@@ -403,7 +403,33 @@ def bench_ops(dev, rank, world, peaks, src, with_reference_kernels=False):
     w8, w_s = fp8_quant(w, "e4m3", "token")
     record("matmul_add_bias_fp8", "tensor", 2 * 8192 * 4096 * (n1 - n0),
            timed_loop(matmul_add_bias_fp8, [(a8, a_s, w8, w_s, bias)], 20), f"columns {n1 - n0} of 14336")
-    out["matmul_add_bias_fp8"]["note"] = "fraction is against the bf16 dense peak"
+    # No FP8 peak is measured on this pool.  The fraction is stated against 2 x the measured bf16
+    # burst (the ratio of the nominal dense peaks, 4.5 : 2.25 PFLOP/s) - an assumption, named as
+    # such - and cuBLASLt's own FP8 GEMM (torch._scaled_mm) is timed on the same operands as a
+    # measured comparator.
+    fp8 = out["matmul_add_bias_fp8"]
+    fp8["peak"] = round(2 * peaks["bf16_tflops"] * world, 1)
+    fp8["frac"] = round(fp8["achieved"] / fp8["peak"], 4)
+    fp8["peak_source"] = f"assumed: 2 x {src} bf16 burst (no FP8 peak measured)"
+    if world == 1:
+        try:
+            w8_t, ws_t = w8.t(), w_s.reshape(1, -1).contiguous()
+            try:
+                lib_fn = lambda: torch._scaled_mm(a8, w8_t, scale_a=a_s.reshape(-1, 1), scale_b=ws_t, bias=bias,
+                                                  out_dtype=torch.bfloat16)
+                lib_fn()
+                kind = "row-wise scales"
+            except Exception:
+                one = torch.ones((), device=dev)
+                lib_fn = lambda: torch._scaled_mm(a8, w8_t, scale_a=one, scale_b=one, bias=bias, out_dtype=torch.bfloat16)
+                lib_fn()
+                kind = "per-tensor scales (row-wise refused)"
+            secs = timed_loop(lambda: lib_fn(), [()], 20)
+            fp8["library_fp8_gemm"] = {"achieved": round(2 * 8192 * 4096 * (n1 - n0) / secs / 1e12, 1), "unit": "TFLOP/s",
+                                       "us_per_launch": round(secs * 1e6, 2),
+                                       "what": f"torch._scaled_mm (cuBLASLt e4m3 GEMM, {kind}) on the same operands, same timing"}
+        except Exception as e:   # the comparator is optional; our own number stands without it
+            fp8["library_fp8_gemm"] = {"unavailable": repr(e)[:200]}
     if cpu_on:
         c8 = (a8[:256].cpu(), a_s[:256].cpu(), w8.cpu(), w_s.cpu(), bias.cpu())
         cpu("matmul_add_bias_fp8", 2 * 256 * 4096 * (n1 - n0), lambda: O.matmul_add_bias_fp8(*c8),

@@ -27,6 +27,11 @@ PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libcustom_cuda_b200.so"
+# --debug-bounds: the bandwidth-bound kernels compiled with -DCC_DEBUG_BOUNDS (csrc/common.cuh): every
+# global access through the shared load / store helpers is checked against host-registered ranges,
+# skipped and counted when outside.  A separate library, loaded only by the test that uses it.
+DEBUG_LIB = PKG / "libcustom_cuda_b200_dbg.so"
+DEBUG_SOURCES = ["swiglu.cu", "rmsnorm_residual.cu", "rope.cu"]
 
 CU_SOURCES = ["swiglu.cu", "rmsnorm_residual.cu", "rope.cu", "fp8_quant.cu", "linear_ce_chunk_update.cu",
               "matmul_add_bias.cu", "matmul_fused.cu", "linear_cross_entropy.cu", "backward_elementwise.cu", "moe.cu"]
@@ -86,6 +91,23 @@ def build_library(force=False, verbose=False) -> pathlib.Path:
     return LIB
 
 
+def build_debug_library(force=False, verbose=False) -> pathlib.Path:
+    """The -DCC_DEBUG_BOUNDS variant of the bandwidth-bound kernels, as its own shared library."""
+    OBJ.mkdir(exist_ok=True)
+    nvcc = _nvcc()
+    hdrs = [CSRC / h for h in HEADERS]
+    objs = []
+    for name in DEBUG_SOURCES:
+        src, obj = CSRC / name, OBJ / (pathlib.Path(name).stem + "_dbg.o")
+        if force or _stale(obj, [src, *hdrs]):
+            _run([nvcc, *NVCC_FLAGS, "-DCC_DEBUG_BOUNDS", "-I", PKG.parent / "include", "-c", src, "-o", obj], verbose)
+        objs.append(obj)
+    if force or _stale(DEBUG_LIB, objs):
+        _run([nvcc, "-shared", "-o", DEBUG_LIB, *objs, "-cudart", "static", "-Xlinker", "--no-undefined",
+              "-Xlinker", "-Bsymbolic"], verbose)
+    return DEBUG_LIB
+
+
 def build_native(force=False, verbose=False) -> pathlib.Path:
     """g++ the CPython module against the torch headers; links the kernel library by $ORIGIN."""
     import torch
@@ -109,9 +131,11 @@ def build_native(force=False, verbose=False) -> pathlib.Path:
     return out
 
 
-def build_all(force=False, verbose=False):
+def build_all(force=False, verbose=False, debug_bounds=True):
     lib = build_library(force, verbose)
     native = build_native(force, verbose)
+    if debug_bounds:
+        build_debug_library(force, verbose)
     return lib, native
 
 
@@ -119,9 +143,13 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--debug-bounds", action="store_true", help="only (re)build the -DCC_DEBUG_BOUNDS library")
     a = ap.parse_args(argv)
+    if a.debug_bounds:
+        print(f"built {build_debug_library(a.force, a.verbose)}")
+        return 0
     lib, native = build_all(a.force, a.verbose)
-    print(f"built {lib}\nbuilt {native}")
+    print(f"built {lib}\nbuilt {native}\nbuilt {DEBUG_LIB}")
 
 
 if __name__ == "__main__":

@@ -20,6 +20,66 @@ enum : int32_t { kF32 = 0, kF16 = 1, kBF16 = 2, kF8E4M3 = 3, kF8E5M2 = 4 };
 
 constexpr int kNumSMs = 148;  // B200
 
+// ---------------------------------------------------------------- debug bounds build
+// With -DCC_DEBUG_BOUNDS (python -m custom_cuda_kernals_b200._build --debug-bounds) every global
+// access that goes through the helpers below (16-byte vector loads / stores and the scalar
+// Store<T>::load1 / store1) is first checked against a table of address ranges the host
+// registered for the launch; an access outside every range is SKIPPED and counted, so a wrong
+// index shows up as a count instead of a fault.  Stands in for compute-sanitizer's memcheck on
+// machines where that tool is not available.  Each translation unit has its own table; the
+// CCK_DEBUG_BOUNDS_EXPORT(tag) macro at the end of a .cu file exports its two host calls:
+//   cck_dbg_set_ranges_<tag>(const void* const* base, const int64_t* bytes, int n)   (n <= 8; clears the count)
+//   cck_dbg_take_violations_<tag>(uint32_t* out)                                     (synchronises)
+#ifdef CC_DEBUG_BOUNDS
+namespace dbg {
+constexpr int kMaxRanges = 8;
+struct Table {
+    unsigned long long lo[kMaxRanges], hi[kMaxRanges];
+    int n;
+    unsigned int violations;
+};
+static __device__ Table g_table;
+__device__ __forceinline__ bool ok(const void* p, unsigned bytes) {
+    const unsigned long long a = reinterpret_cast<unsigned long long>(p);
+    for (int i = 0; i < g_table.n; ++i)
+        if (a >= g_table.lo[i] && a + bytes <= g_table.hi[i]) return true;
+    atomicAdd(&g_table.violations, 1u);
+    return false;
+}
+static inline int32_t set_ranges(const void* const* base, const int64_t* bytes, int n) {
+    if (n < 0 || n > kMaxRanges) return cudaErrorInvalidValue;
+    Table t = {};
+    t.n = n;
+    for (int i = 0; i < n; ++i) {
+        t.lo[i] = reinterpret_cast<unsigned long long>(base[i]);
+        t.hi[i] = t.lo[i] + static_cast<unsigned long long>(bytes[i]);
+    }
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    return cudaMemcpyToSymbol(g_table, &t, sizeof(t));
+}
+static inline int32_t take_violations(uint32_t* out) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    Table t;
+    e = cudaMemcpyFromSymbol(&t, g_table, sizeof(t));
+    if (e != cudaSuccess) return e;
+    *out = t.violations;
+    t.violations = 0;
+    return cudaMemcpyToSymbol(g_table, &t, sizeof(t));
+}
+}  // namespace dbg
+#define CCK_DBG_OK(p, bytes) (::cck::dbg::ok((p), (bytes)))
+#define CCK_DEBUG_BOUNDS_EXPORT(tag)                                                                              \
+    extern "C" int32_t cck_dbg_set_ranges_##tag(const void* const* base, const int64_t* bytes, int32_t n) {      \
+        return ::cck::dbg::set_ranges(base, bytes, n);                                                           \
+    }                                                                                                             \
+    extern "C" int32_t cck_dbg_take_violations_##tag(uint32_t* out) { return ::cck::dbg::take_violations(out); }
+#else
+#define CCK_DBG_OK(p, bytes) (true)
+#define CCK_DEBUG_BOUNDS_EXPORT(tag)
+#endif
+
 // ---------------------------------------------------------------- 16-byte vectors
 struct alignas(16) Vec16 {
     uint32_t w[4];
@@ -28,6 +88,7 @@ struct alignas(16) Vec16 {
 // Read-once data: non-coherent path, do not keep in L1.
 __device__ __forceinline__ Vec16 ld_stream(const void* p) {
     Vec16 v;
+    if (!CCK_DBG_OK(p, 16)) return Vec16{};
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
                  : "l"(p));
@@ -35,15 +96,18 @@ __device__ __forceinline__ Vec16 ld_stream(const void* p) {
 }
 // Re-used data (weights, tables): default caching.
 __device__ __forceinline__ Vec16 ld_cached(const void* p) {
+    if (!CCK_DBG_OK(p, 16)) return Vec16{};
     return *reinterpret_cast<const Vec16*>(p);
 }
 // Write-once data: streaming store (evict-first).
 __device__ __forceinline__ void st_stream(void* p, const Vec16& v) {
+    if (!CCK_DBG_OK(p, 16)) return;
     asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
                  :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3])
                  : "memory");
 }
 __device__ __forceinline__ void st_stream8(void* p, uint32_t a, uint32_t b) {
+    if (!CCK_DBG_OK(p, 8)) return;
     asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" :: "l"(p), "r"(a), "r"(b) : "memory");
 }
 
@@ -53,8 +117,8 @@ template <typename T> struct Store;
 template <> struct Store<float> {
     static constexpr int kPerVec = 4;
     __device__ static __forceinline__ float get(const Vec16& v, int i) { return __uint_as_float(v.w[i]); }
-    __device__ static __forceinline__ float load1(const float* p) { return *p; }
-    __device__ static __forceinline__ void store1(float* p, float f) { *p = f; }
+    __device__ static __forceinline__ float load1(const float* p) { return CCK_DBG_OK(p, 4) ? *p : 0.0f; }
+    __device__ static __forceinline__ void store1(float* p, float f) { if (CCK_DBG_OK(p, 4)) *p = f; }
     // value after one rounding to the storage type
     __device__ static __forceinline__ float round(float f) { return f; }
 };
@@ -65,8 +129,12 @@ template <> struct Store<__nv_bfloat16> {
         const uint32_t w = v.w[i >> 1];
         return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
     }
-    __device__ static __forceinline__ float load1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-    __device__ static __forceinline__ void store1(__nv_bfloat16* p, float f) { *p = __float2bfloat16_rn(f); }
+    __device__ static __forceinline__ float load1(const __nv_bfloat16* p) {
+        return CCK_DBG_OK(p, 2) ? __bfloat162float(*p) : 0.0f;
+    }
+    __device__ static __forceinline__ void store1(__nv_bfloat16* p, float f) {
+        if (CCK_DBG_OK(p, 2)) *p = __float2bfloat16_rn(f);
+    }
     __device__ static __forceinline__ float round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
     __device__ static __forceinline__ uint32_t pack2(float lo, float hi) {
         const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
@@ -81,8 +149,8 @@ template <> struct Store<__half> {
         const __half_raw r{static_cast<unsigned short>((i & 1) ? (w >> 16) : (w & 0xffffu))};
         return __half2float(__half(r));
     }
-    __device__ static __forceinline__ float load1(const __half* p) { return __half2float(*p); }
-    __device__ static __forceinline__ void store1(__half* p, float f) { *p = __float2half_rn(f); }
+    __device__ static __forceinline__ float load1(const __half* p) { return CCK_DBG_OK(p, 2) ? __half2float(*p) : 0.0f; }
+    __device__ static __forceinline__ void store1(__half* p, float f) { if (CCK_DBG_OK(p, 2)) *p = __float2half_rn(f); }
     __device__ static __forceinline__ float round(float f) { return __half2float(__float2half_rn(f)); }
     __device__ static __forceinline__ uint32_t pack2(float lo, float hi) {
         const __half2 h = __floats2half2_rn(lo, hi);

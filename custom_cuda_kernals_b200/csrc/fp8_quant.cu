@@ -192,6 +192,36 @@ fp8_token_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, float* __
     }
 }
 
+// The same quantiser for rows whose largest magnitude already exists as `n_tiles` partial maxima
+// per row ([n_tiles][rows], written by the producing GEMM's epilogue): no reduction, no barrier.
+// A maximum does not depend on the order it is taken in, so codes and scales are bit for bit
+// those of fp8_token_kernel.
+template <typename T, bool E5M2, int VPT>
+__global__ void __launch_bounds__(1024)
+fp8_token_from_amax_kernel(const T* __restrict__ x, const float* __restrict__ amax, int n_tiles, int64_t rows,
+                           uint8_t* __restrict__ codes, float* __restrict__ scale, int64_t n, int n_vec) {
+    constexpr int kPer = Store<T>::kPerVec;
+    const int64_t row = blockIdx.x;
+    const T* xr = x + row * n;
+    uint8_t* cr = codes + row * n;
+    Vec16 v[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) v[j] = ld_stream(xr + static_cast<int64_t>(i) * kPer);
+    }
+    float m = 0.0f;
+    for (int t = 0; t < n_tiles; ++t) m = fmaxf(m, amax[static_cast<int64_t>(t) * rows + row]);
+    const float sc = scale_of<E5M2>(m);
+    if (threadIdx.x == 0) scale[row] = sc;
+    const ExactDiv div = ExactDiv::make(sc);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) Chunk<T>::template quantise_store<E5M2>(v[j], div, cr + static_cast<int64_t>(i) * kPer);
+    }
+}
+
 // any n / alignment: scalar, the row is read twice (second time from L1/L2)
 template <typename T, bool E5M2>
 __global__ void __launch_bounds__(256)
@@ -397,6 +427,25 @@ cudaError_t run_token(const void* x, uint8_t* codes, float* scale, int64_t m, in
 }
 
 template <typename T, bool E5M2>
+cudaError_t run_token_from_amax(const void* x, const float* amax, int64_t n_tiles, uint8_t* codes, float* scale,
+                                int64_t m, int64_t n, cudaStream_t s) {
+    constexpr int kPer = Store<T>::kPerVec;
+    const int64_t n_vec = n / kPer;
+    if (m > 0x7fffffffLL || n_tiles <= 0 || n_tiles > 4096 || amax == nullptr || n % kPer != 0 || !aligned16(x) ||
+        (reinterpret_cast<uintptr_t>(codes) % kPer) != 0 || n_vec > 8 * 1024)
+        return cudaErrorInvalidValue;
+    const int vpt = n_vec <= 4 * 1024 ? 4 : 8;
+    int threads = static_cast<int>(ceil_div64(ceil_div64(n_vec, vpt), 32) * 32);
+    if (threads < 32) threads = 32;
+    const unsigned grid = static_cast<unsigned>(m);
+    const T* xp = static_cast<const T*>(x);
+    const int nt = static_cast<int>(n_tiles), nv = static_cast<int>(n_vec);
+    if (vpt == 4) fp8_token_from_amax_kernel<T, E5M2, 4><<<grid, threads, 0, s>>>(xp, amax, nt, m, codes, scale, n, nv);
+    else fp8_token_from_amax_kernel<T, E5M2, 8><<<grid, threads, 0, s>>>(xp, amax, nt, m, codes, scale, n, nv);
+    return cudaGetLastError();
+}
+
+template <typename T, bool E5M2>
 cudaError_t run_block(const void* x, uint8_t* codes, float* scale, int64_t m, int64_t n, cudaStream_t s) {
     const int64_t gx = ceil_div64(n, kTile), gy = ceil_div64(m, kTile);
     if (gy > 65535 || gx > 0x7fffffffLL) return cudaErrorInvalidValue;
@@ -506,4 +555,28 @@ extern "C" int32_t launch_fp8_quant_tensor_fwd(const void* x, uint8_t* x_fp8, fl
                                                void* stream) {
     if (amax_scratch == nullptr && m > 0 && n > 0) return cudaErrorInvalidValue;
     return cck::dispatch(cck::kTensor, x, x_fp8, scale, amax_scratch, m, n, dtype, fp8_format, stream);
+}
+
+// Per-token quantisation of a matrix whose row maxima the producing GEMM left as n_tiles partial
+// maxima per row (launch_matmul_add_bias_stats_fwd: row_amax [n_tiles, m]).  Codes and scales are
+// bit for bit those of launch_fp8_quant_token_fwd.  16-bit inputs, n a multiple of 8, 16-byte
+// aligned x, 8-byte aligned codes; otherwise cudaErrorInvalidValue.  No counterpart in the reference.
+extern "C" int32_t launch_fp8_quant_token_from_amax_fwd(const void* x, const float* row_amax, int64_t n_tiles,
+                                                        uint8_t* x_fp8, float* scale, int64_t m, int64_t n,
+                                                        int32_t dtype, int32_t fp8_format, void* stream) {
+    using namespace cck;
+    if (m <= 0 || n <= 0) return cudaSuccess;
+    if (fp8_format != kF8E4M3 && fp8_format != kF8E5M2) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool e5 = fp8_format == kF8E5M2;
+    switch (dtype) {
+        case kF16:
+            return e5 ? run_token_from_amax<__half, true>(x, row_amax, n_tiles, x_fp8, scale, m, n, s)
+                      : run_token_from_amax<__half, false>(x, row_amax, n_tiles, x_fp8, scale, m, n, s);
+        case kBF16:
+            return e5 ? run_token_from_amax<__nv_bfloat16, true>(x, row_amax, n_tiles, x_fp8, scale, m, n, s)
+                      : run_token_from_amax<__nv_bfloat16, false>(x, row_amax, n_tiles, x_fp8, scale, m, n, s);
+        default:
+            return cudaErrorInvalidValue;
+    }
 }

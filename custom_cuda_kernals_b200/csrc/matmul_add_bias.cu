@@ -92,7 +92,7 @@ struct EpiScaledBias {
     struct Thread { float a_scale; };
     __device__ static __forceinline__ void tile_begin(const Params& p, Thread& th, const TileWork& w, float* scratch,
                                                       int lane, int row_in_tile) {
-        const int64_t n0 = static_cast<int64_t>(w.n_tile) * kBN;
+        const int64_t n0 = w.n0;
 #pragma unroll
         for (int i = 0; i < kBN / 32; ++i) {
             const int64_t col = n0 + lane + 32 * i;
@@ -106,7 +106,7 @@ struct EpiScaledBias {
     __device__ static __forceinline__ void chunk(const Params& p, Thread& th, const TileWork& w, int row_in_tile,
                                                  int c0, float (&acc)[32], const float* scratch) {
         const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
-        const int64_t col = static_cast<int64_t>(w.n_tile) * kBN + c0;
+        const int64_t col = static_cast<int64_t>(w.n0) + c0;
         if (row >= p.m || col >= p.n) return;
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = fmaf(acc[j] * th.a_scale, scratch[c0 + j], scratch[kBN + c0 + j]);
@@ -207,45 +207,68 @@ extern "C" int32_t launch_matmul_add_bias_fwd(const void* x, const void* weight,
     }
 }
 
+namespace cck {
+namespace tc {
+
+// FP8 GEMM on the tensor cores for any M and N (K a multiple of 16, 16-byte aligned operands):
+// TMA zero-fills outside the matrices and the epilogue masks, so partial and undersized tiles
+// need nothing special; few full-width tiles (decode-sized M) run on 128 x 64 tiles like the
+// 16-bit path.
+template <typename T>
+cudaError_t gemm_fp8_tc(const uint8_t* a_codes, const float* a_scale, const uint8_t* w_codes, const float* w_scale,
+                        const void* bias, void* y, int64_t m, int64_t k, int64_t n, cudaStream_t s) {
+    const int m_tiles = static_cast<int>(ceil_div64(m, kBM)), n_tiles = static_cast<int>(ceil_div64(n, kBN));
+    typename EpiScaledBias<T>::Params ep{a_scale, w_scale, static_cast<const T*>(bias), static_cast<T*>(y), m, n,
+                                         (n % 8 == 0 && aligned16(y)) ? 1 : 0};
+    const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CUtensorMap ta, tb;
+    cudaError_t e = make_tmap(&ta, dt, 1, a_codes, m, k, kBM);
+    if (e != cudaSuccess) return e;
+    constexpr int kNarrow = 64;
+    const int64_t wide_tiles = static_cast<int64_t>(m_tiles) * n_tiles;
+    if (wide_tiles <= sm_count() / 4 && narrow_tiles_enabled()) {
+        e = make_tmap(&tb, dt, 1, w_codes, n, k, kNarrow);
+        if (e != cudaSuccess) return e;
+        SchedGemm::Params sp{m_tiles, static_cast<int>(ceil_div64(n, kNarrow)), m_tiles};
+        const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
+        return launch<true, SchedGemm, EpiScaledBias<T>, kNarrow>(ta, tb, sp, ep, k, ptx::instr_desc(0u, 0u, kBM, kNarrow),
+                                                                  static_cast<int>(tiles < sm_count() ? tiles : sm_count()), s);
+    }
+    const bool pair = m_tiles >= 2 && pair_kernels_enabled() && max_pairs<true, SchedGemm, EpiScaledBias<T>>() > 0;
+    e = make_tmap(&tb, dt, 1, w_codes, n, k, pair ? 128 : kBN);
+    if (e != cudaSuccess) return e;
+    const int m_units = pair ? (m_tiles + 1) / 2 : m_tiles;
+    SchedGemm::Params sp{m_units, n_tiles, raster_group(pair ? 2 * kBM : kBM, k, 1, m_units)};
+    const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
+    const uint32_t idesc = ptx::instr_desc(0u, 0u, pair ? 2 * kBM : kBM, kBN);   // e4m3 x e4m3
+    if (pair) return launch_pair<true, SchedGemm, EpiScaledBias<T>>(ta, tb, sp, ep, k, idesc, tiles, s);
+    return launch<true, SchedGemm, EpiScaledBias<T>>(ta, tb, sp, ep, k, idesc,
+                                                     static_cast<int>(tiles < sm_count() ? tiles : sm_count()), s);
+}
+
+}  // namespace tc
+}  // namespace cck
+
+// e4m3 operands with per-row scales.  Every shape runs, as with the 16-bit entry point (the
+// reference's launcher has a fallback for every shape: csrc/kernels/matmul_add_bias.cu:170-180):
+// K a multiple of 16 with 16-byte aligned operands and at least ~4 MFLOP go to the tensor
+// cores, everything else to the CUDA-core kernel.
 extern "C" int32_t launch_matmul_add_bias_fp8_fwd(const uint8_t* a_codes, const float* a_scale,
                                                   const uint8_t* w_codes, const float* w_scale, const void* bias,
                                                   void* y, int64_t m, int64_t k, int64_t n, int32_t out_dtype,
                                                   void* stream) {
     using namespace cck;
-    using namespace cck::tc;
     if (m <= 0 || n <= 0 || k <= 0) return cudaSuccess;
-    // e4m3 operands only; TMA needs 16-byte row strides and at least one full box per operand
-    if (k % 16 != 0 || k < 128 || m < kBM || n < kBN || !aligned16(a_codes) || !aligned16(w_codes) ||
-        m >= (1LL << 31) || n >= (1LL << 31) || k >= (1LL << 31))
-        return cudaErrorInvalidValue;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int m_tiles = static_cast<int>(ceil_div64(m, kBM)), n_tiles = static_cast<int>(ceil_div64(n, kBN));
-    const int vec_ok = (n % 8 == 0 && aligned16(y)) ? 1 : 0;
     if (out_dtype != kBF16 && out_dtype != kF16) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool bf = out_dtype == kBF16;
-    const bool pair = m_tiles >= 2 && pair_kernels_enabled() &&
-                      (bf ? max_pairs<true, SchedGemm, EpiScaledBias<__nv_bfloat16>>()
-                          : max_pairs<true, SchedGemm, EpiScaledBias<__half>>()) > 0;
-    CUtensorMap ta, tb;
-    cudaError_t e = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_codes, m, k, kBM);
-    if (e != cudaSuccess) return e;
-    e = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_codes, n, k, pair ? 128 : kBN);
-    if (e != cudaSuccess) return e;
-    const int m_units = pair ? (m_tiles + 1) / 2 : m_tiles;
-    SchedGemm::Params sp{m_units, n_tiles, raster_group(pair ? 2 * kBM : kBM, k, 1, m_units)};
-    const int64_t tiles = static_cast<int64_t>(sp.m_tiles) * sp.n_tiles;
-    const int ctas = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-    const uint32_t idesc = ptx::instr_desc(0u, 0u, pair ? 2 * kBM : kBM, kBN);   // e4m3 x e4m3
-    if (bf) {
-        EpiScaledBias<__nv_bfloat16>::Params ep{a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias),
-                                                static_cast<__nv_bfloat16*>(y), m, n, vec_ok};
-        return pair ? launch_pair<true, SchedGemm, EpiScaledBias<__nv_bfloat16>>(ta, tb, sp, ep, k, idesc, tiles, s)
-                    : launch<true, SchedGemm, EpiScaledBias<__nv_bfloat16>>(ta, tb, sp, ep, k, idesc, ctas, s);
-    }
-    EpiScaledBias<__half>::Params ep{a_scale, w_scale, static_cast<const __half*>(bias), static_cast<__half*>(y), m, n,
-                                     vec_ok};
-    return pair ? launch_pair<true, SchedGemm, EpiScaledBias<__half>>(ta, tb, sp, ep, k, idesc, tiles, s)
-                : launch<true, SchedGemm, EpiScaledBias<__half>>(ta, tb, sp, ep, k, idesc, ctas, s);
+    const bool tensor_cores = k % 16 == 0 && aligned16(a_codes) && aligned16(w_codes) && 2 * m * n * k >= (1LL << 22) &&
+                              m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31);
+    if (tensor_cores)
+        return bf ? tc::gemm_fp8_tc<__nv_bfloat16>(a_codes, a_scale, w_codes, w_scale, bias, y, m, k, n, s)
+                  : tc::gemm_fp8_tc<__half>(a_codes, a_scale, w_codes, w_scale, bias, y, m, k, n, s);
+    return bf ? gemm_fp8_simt<__nv_bfloat16>(a_codes, a_scale, w_codes, w_scale, bias, y, m, k, n, s)
+              : gemm_fp8_simt<__half>(a_codes, a_scale, w_codes, w_scale, bias, y, m, k, n, s);
 }
 
 // Number of CTA pairs the bf16 GEMM can keep resident on the current device (0: the pair

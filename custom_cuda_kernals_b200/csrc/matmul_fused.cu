@@ -109,6 +109,82 @@ struct EpiBiasResidual {
     __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
 };
 
+// ---- epilogue: y = round(acc + bias) (+ residual), and per (row, 256-column tile) statistics of
+// the STORED values: sum of squares and largest magnitude.  A row of y spans several tiles, which
+// different CTAs compute, so the row-wide reduction is left to the consumer: the statistics go to
+// [n_tiles][m] side buffers (tile-major: a warp's 32 rows are 128 contiguous bytes) and the
+// RMSNorm / per-token FP8 quantiser that follows reads n_tiles floats per row instead of reducing
+// the row itself (launch_rmsnorm_from_stats_fwd, launch_fp8_quant_token_from_amax_fwd).
+// Summation order is fixed - columns ascending inside a tile, one fp32 FMA chain per row - so the
+// statistics do not depend on the schedule.
+template <typename T>
+struct EpiBiasResidualStats {
+    struct Params {
+        const T* bias;       // [n] or null
+        const T* residual;   // [m, n] or null
+        T* y;
+        float* sumsq;        // [n_tiles, m] or null
+        float* amax;         // [n_tiles, m] or null
+        int64_t m, n;
+        int vec_ok;
+    };
+    struct Thread { float sumsq, amax; };
+    __device__ static __forceinline__ void tile_begin(const Params& p, Thread& th, const TileWork& w, float* scratch,
+                                                      int lane, int) {
+        const int64_t n0 = static_cast<int64_t>(w.n_tile) * kBN;
+#pragma unroll
+        for (int i = 0; i < kBN / 32; ++i) {
+            const int64_t col = n0 + lane + 32 * i;
+            scratch[lane + 32 * i] = (p.bias != nullptr && col < p.n) ? Store<T>::load1(p.bias + col) : 0.0f;
+        }
+        th.sumsq = 0.0f;
+        th.amax = 0.0f;
+    }
+    __device__ static __forceinline__ void chunk(const Params& p, Thread& th, const TileWork& w, int row_in_tile, int c0,
+                                                 float (&acc)[32], const float* scratch) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        const int64_t col = static_cast<int64_t>(w.n_tile) * kBN + c0;
+        if (row >= p.m || col >= p.n) return;
+        const bool whole = p.vec_ok && col + 32 <= p.n;
+        if (p.residual != nullptr) {
+            const T* res = p.residual + row * p.n + col;
+            if (whole) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float r[8];
+                    unpack<T>(ld_stream(res + 8 * q), r);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        acc[8 * q + i] = Store<T>::round(acc[8 * q + i] + scratch[c0 + 8 * q + i]) + r[i];
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col + j < p.n) acc[j] = Store<T>::round(acc[j] + scratch[c0 + j]) + Store<T>::load1(res + j);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] += scratch[c0 + j];
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            acc[j] = Store<T>::round(acc[j]);                  // what the store below writes
+            if (whole || col + j < p.n) {
+                th.sumsq = fmaf(acc[j], acc[j], th.sumsq);
+                th.amax = fmaxf(th.amax, fabsf(acc[j]));
+            }
+        }
+        store32<T>(p.y + row * p.n + col, acc, col, p.n, p.vec_ok);
+    }
+    __device__ static __forceinline__ void tile_end(const Params& p, Thread& th, const TileWork& w, int row_in_tile) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        if (row >= p.m) return;
+        const int64_t at = static_cast<int64_t>(w.n_tile) * p.m + row;
+        if (p.sumsq != nullptr) p.sumsq[at] = th.sumsq;
+        if (p.amax != nullptr) p.amax[at] = th.amax;
+    }
+};
+
 // ---- epilogue: y_f32 += acc   (fp32 accumulation across calls, e.g. a weight gradient
 // summed over row blocks)
 struct EpiAccumF32 {
@@ -214,6 +290,36 @@ extern "C" int32_t launch_matmul_add_bias_residual_fwd(const void* x, const void
         EpiBiasResidual<__half>::Params ep{static_cast<const __half*>(bias), static_cast<const __half*>(residual),
                                            static_cast<__half*>(y), m, n, vec_ok};
         return run_fused<__half, EpiBiasResidual<__half>>(x, weight, m, k, n, ep, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+// y = x @ weight^T + bias (+ residual when not NULL), bit for bit what launch_matmul_add_bias_fwd
+// (launch_matmul_add_bias_residual_fwd) stores, plus the per-(row, 256-column tile) statistics of the
+// stored values the next op needs: row_sumsq / row_amax are [cck_gemm_stat_tiles(n), m] float32,
+// either may be NULL.
+extern "C" int64_t cck_gemm_stat_tiles(int64_t n) { return n <= 0 ? 0 : (n + cck::tc::kBN - 1) / cck::tc::kBN; }
+
+extern "C" int32_t launch_matmul_add_bias_stats_fwd(const void* x, const void* weight, const void* bias,
+                                                    const void* residual, void* y, float* row_sumsq, float* row_amax,
+                                                    int64_t m, int64_t k, int64_t n, int32_t dtype, void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (m <= 0 || k <= 0 || n <= 0) return cudaSuccess;
+    if (!tc_shape_ok(x, weight, m, k, n)) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int vec_ok = (n % 8 == 0 && aligned16(y) && (residual == nullptr || aligned16(residual))) ? 1 : 0;
+    if (dtype == kBF16) {
+        using T = __nv_bfloat16;
+        EpiBiasResidualStats<T>::Params ep{static_cast<const T*>(bias), static_cast<const T*>(residual),
+                                           static_cast<T*>(y), row_sumsq, row_amax, m, n, vec_ok};
+        return run_fused<T, EpiBiasResidualStats<T>>(x, weight, m, k, n, ep, s);
+    }
+    if (dtype == kF16) {
+        using T = __half;
+        EpiBiasResidualStats<T>::Params ep{static_cast<const T*>(bias), static_cast<const T*>(residual),
+                                           static_cast<T*>(y), row_sumsq, row_amax, m, n, vec_ok};
+        return run_fused<T, EpiBiasResidualStats<T>>(x, weight, m, k, n, ep, s);
     }
     return cudaErrorInvalidValue;
 }

@@ -591,7 +591,6 @@ void matmul_add_bias_fp8_fwd(const at::Tensor& a, const at::Tensor& a_scale, con
                     std::to_string(n) + "]");
     if (has_bias && (bias->dim() != 1 || bias->size(0) != n))
         value_error("shape mismatch: bias shape " + shape_str(*bias) + " must be [" + std::to_string(n) + "]");
-    if (k % 16 != 0) value_error("shape mismatch: the FP8 GEMM needs K to be a multiple of 16, got " + std::to_string(k));
     at::Tensor none;
     Launch l(a, {&a_scale, &w, &w_scale, &y, has_bias ? &*bias : &none});
     check_launch("launch_matmul_add_bias_fp8_fwd",
@@ -862,6 +861,100 @@ uint32_t take_device_status(const at::Tensor& like) {
     return v;
 }
 
+// GEMM (+ bias, + residual) that also leaves per-(row, 256-column tile) statistics of its output
+void matmul_add_bias_stats_fwd(const at::Tensor& x, const at::Tensor& weight, const c10::optional<at::Tensor>& bias,
+                               const c10::optional<at::Tensor>& residual, const at::Tensor& y,
+                               const c10::optional<at::Tensor>& row_sumsq, const c10::optional<at::Tensor>& row_amax) {
+    const int32_t dt = tag_of("x", x);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "' for the fused path; expected float16 or bfloat16");
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_same_dtype("y", tag_of("y", y), dt);
+    const bool has_bias = bias.has_value() && bias->defined();
+    const bool has_res = residual.has_value() && residual->defined();
+    if (has_bias) expect_same_dtype("bias", tag_of("bias", *bias), dt);
+    if (has_res) expect_same_dtype("residual", tag_of("residual", *residual), dt);
+    if (x.dim() != 2 || weight.dim() != 2)
+        value_error("shape mismatch: x and weight must be 2-D; got x=" + shape_str(x) + ", weight=" + shape_str(weight));
+    const int64_t m = x.size(0), k = x.size(1), n = weight.size(0);
+    if (weight.size(1) != k)
+        value_error("shape mismatch: weight's in_features (" + std::to_string(weight.size(1)) +
+                    ") must match x's last dim (" + std::to_string(k) + ")");
+    if (k % 8 != 0) value_error("shape mismatch: the fused path needs K to be a multiple of 8");
+    if (y.dim() != 2 || y.size(0) != m || y.size(1) != n)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " + std::to_string(n) + "]");
+    if (has_bias && (bias->dim() != 1 || bias->size(0) != n))
+        value_error("shape mismatch: bias shape " + shape_str(*bias) + " must be [" + std::to_string(n) + "]");
+    if (has_res && residual->sizes() != y.sizes())
+        value_error("shape mismatch: residual shape " + shape_str(*residual) + " must match y's " + shape_str(y));
+    const int64_t tiles = cck_gemm_stat_tiles(n);
+    at::Tensor none;
+    const at::Tensor* stats[2] = {row_sumsq.has_value() && row_sumsq->defined() ? &*row_sumsq : nullptr,
+                                  row_amax.has_value() && row_amax->defined() ? &*row_amax : nullptr};
+    const char* stat_names[2] = {"row_sumsq", "row_amax"};
+    for (int i = 0; i < 2; ++i) {
+        if (!stats[i]) continue;
+        expect_f32(stat_names[i], tag_of(stat_names[i], *stats[i]));
+        if (stats[i]->dim() != 2 || stats[i]->size(0) != tiles || stats[i]->size(1) != m)
+            value_error(std::string("shape mismatch: ") + stat_names[i] + " shape " + shape_str(*stats[i]) + " must be [" +
+                        std::to_string(tiles) + ", " + std::to_string(m) + "]");
+    }
+    Launch l(x, {&weight, &y, has_bias ? &*bias : &none, has_res ? &*residual : &none, stats[0] ? stats[0] : &none,
+                 stats[1] ? stats[1] : &none});
+    check_launch("launch_matmul_add_bias_stats_fwd",
+                 launch_matmul_add_bias_stats_fwd(x.data_ptr(), weight.data_ptr(), has_bias ? bias->data_ptr() : nullptr,
+                                                  has_res ? residual->data_ptr() : nullptr, y.data_ptr(),
+                                                  stats[0] ? static_cast<float*>(stats[0]->data_ptr()) : nullptr,
+                                                  stats[1] ? static_cast<float*>(stats[1]->data_ptr()) : nullptr, m, k, n, dt,
+                                                  l.stream));
+}
+
+void rmsnorm_from_stats_fwd(const at::Tensor& x, const at::Tensor& row_sumsq, const at::Tensor& weight,
+                            const at::Tensor& y, double eps) {
+    const int32_t dt = tag_of("x", x);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_same_dtype("y", tag_of("y", y), dt);
+    expect_f32("row_sumsq", tag_of("row_sumsq", row_sumsq));
+    if (x.dim() != 2 || y.sizes() != x.sizes())
+        value_error("shape mismatch: x and y must be 2-D of the same shape; got x=" + shape_str(x) + ", y=" + shape_str(y));
+    const int64_t rows = x.size(0), cols = x.size(1);
+    if (weight.dim() != 1 || weight.size(0) != cols)
+        value_error("shape mismatch: weight shape " + shape_str(weight) + " must be [" + std::to_string(cols) + "]");
+    if (row_sumsq.dim() != 2 || row_sumsq.size(1) != rows || row_sumsq.size(0) < 1)
+        value_error("shape mismatch: row_sumsq shape " + shape_str(row_sumsq) + " must be [n_tiles, " + std::to_string(rows) + "]");
+    if (cols % 8 != 0) value_error("shape mismatch: cols must be a multiple of 8");
+    Launch l(x, {&row_sumsq, &weight, &y});
+    check_launch("launch_rmsnorm_from_stats_fwd",
+                 launch_rmsnorm_from_stats_fwd(x.data_ptr(), static_cast<const float*>(row_sumsq.data_ptr()),
+                                               row_sumsq.size(0), weight.data_ptr(), y.data_ptr(), rows, cols,
+                                               static_cast<float>(eps), dt, l.stream));
+}
+
+void fp8_quant_token_from_amax_fwd(const at::Tensor& x, const at::Tensor& row_amax, const at::Tensor& x_fp8,
+                                   const at::Tensor& scale, const std::string& fp8_format) {
+    const int32_t dt = tag_of("x", x);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
+    const int32_t fmt = parse_fp8_format(fp8_format);
+    if (tag_of("x_fp8", x_fp8) != fmt) value_error("dtype mismatch: x_fp8 must be the torch float8 type of fp8_format");
+    expect_f32("scale", tag_of("scale", scale));
+    expect_f32("row_amax", tag_of("row_amax", row_amax));
+    if (x.dim() != 2 || x_fp8.sizes() != x.sizes())
+        value_error("shape mismatch: x and x_fp8 must be 2-D of the same shape; got x=" + shape_str(x) + ", x_fp8=" + shape_str(x_fp8));
+    const int64_t m = x.size(0), n = x.size(1);
+    if (scale.numel() != m) value_error("shape mismatch: scale must have " + std::to_string(m) + " elements");
+    if (row_amax.dim() != 2 || row_amax.size(1) != m || row_amax.size(0) < 1)
+        value_error("shape mismatch: row_amax shape " + shape_str(row_amax) + " must be [n_tiles, " + std::to_string(m) + "]");
+    if (n % 8 != 0) value_error("shape mismatch: n must be a multiple of 8");
+    Launch l(x, {&row_amax, &x_fp8, &scale});
+    check_launch("launch_fp8_quant_token_from_amax_fwd",
+                 launch_fp8_quant_token_from_amax_fwd(x.data_ptr(), static_cast<const float*>(row_amax.data_ptr()),
+                                                      row_amax.size(0), static_cast<uint8_t*>(x_fp8.data_ptr()),
+                                                      static_cast<float*>(scale.data_ptr()), m, n, dt, fmt, l.stream));
+}
+
 uint64_t set_wait_limit_ns(const at::Tensor& like, uint64_t limit_ns) {
     c10::cuda::CUDAGuard guard(like.device());
     uint64_t previous = 0;
@@ -937,6 +1030,14 @@ PYBIND11_MODULE(_native, m) {
     m.def("lce_workspace_bytes", &lce_workspace_bytes, py::arg("like"), py::arg("n"), py::arg("v_count"));
     m.def("lce_finalize", &lce_finalize, py::arg("stats"), py::arg("targets"), py::arg("ignore_index"),
           py::arg("loss_rows").none(true), py::arg("reduce_out"));
+    m.def("matmul_add_bias_stats_fwd", &matmul_add_bias_stats_fwd, py::arg("x"), py::arg("weight"),
+          py::arg("bias").none(true), py::arg("residual").none(true), py::arg("y"), py::arg("row_sumsq").none(true),
+          py::arg("row_amax").none(true));
+    m.def("rmsnorm_from_stats_fwd", &rmsnorm_from_stats_fwd, py::arg("x"), py::arg("row_sumsq"), py::arg("weight"),
+          py::arg("y"), py::arg("eps"));
+    m.def("fp8_quant_token_from_amax_fwd", &fp8_quant_token_from_amax_fwd, py::arg("x"), py::arg("row_amax"),
+          py::arg("x_fp8"), py::arg("scale"), py::arg("fp8_format"));
+    m.def("gemm_stat_tiles", [](int64_t n) { return cck_gemm_stat_tiles(n); }, py::arg("n"));
     m.def("take_device_status", &take_device_status, py::arg("like"));
     m.def("set_wait_limit_ns", &set_wait_limit_ns, py::arg("like"), py::arg("limit_ns"));
     m.def("wait_limit_selftest", &wait_limit_selftest, py::arg("a"), py::arg("b"), py::arg("y"), py::arg("variant"));

@@ -97,6 +97,66 @@ rmsnorm_rowreg_kernel(const T* __restrict__ x, const T* __restrict__ res, const 
     }
 }
 
+// The norm of a row whose sum of squares already exists as `n_tiles` partial sums (written by the
+// producing GEMM's epilogue, [n_tiles][rows]): no reduction, no barrier.  Each thread issues its
+// VPT 16-byte loads of the row up front, adds the partials in tile order while they fly (the same
+// fp32 additions in every thread, so all threads hold the same factor) and scales its vectors.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024)
+rmsnorm_from_stats_kernel(const T* __restrict__ x, const float* __restrict__ sumsq, int n_tiles, int64_t rows,
+                          const T* __restrict__ w, T* __restrict__ y, int cols, int n_vec, float eps) {
+    constexpr int kPer = Store<T>::kPerVec;
+    const int64_t row = blockIdx.x;
+    const Vec16* x16 = reinterpret_cast<const Vec16*>(x) + row * n_vec;
+    const Vec16* w16 = reinterpret_cast<const Vec16*>(w);
+    Vec16* y16 = reinterpret_cast<Vec16*>(y) + row * n_vec;
+    Vec16 xv[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) xv[j] = ld_stream(x16 + i);
+    }
+    float total = 0.0f;
+    for (int t = 0; t < n_tiles; ++t) total += sumsq[static_cast<int64_t>(t) * rows + row];
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(cols) + eps);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) {
+            float a[kPer], g[kPer];
+            unpack<T>(xv[j], a);
+            unpack<T>(ld_cached(w16 + i), g);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) a[e] = Store<T>::round(a[e] * inv) * g[e];
+            st_stream(y16 + i, pack<T>(a));
+        }
+    }
+}
+
+template <typename T>
+cudaError_t run_from_stats(const void* x, const float* sumsq, int64_t n_tiles, const void* w, void* y, int64_t rows,
+                           int64_t cols, float eps, cudaStream_t stream) {
+    constexpr int kPer = Store<T>::kPerVec;
+    if (rows > 0x7fffffffLL || n_tiles <= 0 || n_tiles > 4096 || sumsq == nullptr) return cudaErrorInvalidValue;
+    const int64_t n_vec = cols / kPer;
+    if (cols % kPer != 0 || n_vec > 8 * 1024 || !aligned16(x) || !aligned16(w) || !aligned16(y))
+        return cudaErrorInvalidValue;
+    const int vpt = n_vec <= 4 * 1024 ? 4 : 8;
+    int threads = static_cast<int>(ceil_div64(ceil_div64(n_vec, vpt), 32) * 32);
+    if (threads < 32) threads = 32;
+    const unsigned grid = static_cast<unsigned>(rows);
+    const T* xp = static_cast<const T*>(x);
+    const T* wp = static_cast<const T*>(w);
+    T* yp = static_cast<T*>(y);
+    if (vpt == 4)
+        rmsnorm_from_stats_kernel<T, 4><<<grid, threads, 0, stream>>>(xp, sumsq, static_cast<int>(n_tiles), rows, wp, yp,
+                                                                      static_cast<int>(cols), static_cast<int>(n_vec), eps);
+    else
+        rmsnorm_from_stats_kernel<T, 8><<<grid, threads, 0, stream>>>(xp, sumsq, static_cast<int>(n_tiles), rows, wp, yp,
+                                                                      static_cast<int>(cols), static_cast<int>(n_vec), eps);
+    return cudaGetLastError();
+}
+
 // Any column count / alignment: scalar accesses, the row sum is written to
 // residual_out in pass one and read back (by the thread that wrote it) in pass two.
 template <typename T, bool kResidual>
@@ -183,3 +243,22 @@ extern "C" int32_t launch_rmsnorm_fwd(const void* x, const void* weight, void* y
         default:         return cudaErrorInvalidValue;
     }
 }
+
+// y = x * rsqrt(sum_t row_sumsq[t][row] / cols + eps) * weight: the norm of rows whose sums of squares
+// the producing GEMM left as n_tiles partials per row (launch_matmul_add_bias_stats_fwd).  Same
+// rounding chain as launch_rmsnorm_fwd; the statistics differ from that kernel's only in the order
+// of the fp32 additions.  cols must be a multiple of the 16-byte vector width and at most 65536
+// (16-bit types), pointers 16-byte aligned; otherwise cudaErrorInvalidValue.  No counterpart in the reference.
+extern "C" int32_t launch_rmsnorm_from_stats_fwd(const void* x, const float* row_sumsq, int64_t n_tiles,
+                                                 const void* weight, void* y, int64_t rows, int64_t cols, float eps,
+                                                 int32_t dtype, void* stream) {
+    if (rows <= 0 || cols <= 0) return cudaSuccess;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case cck::kF16:  return cck::run_from_stats<__half>(x, row_sumsq, n_tiles, weight, y, rows, cols, eps, s);
+        case cck::kBF16: return cck::run_from_stats<__nv_bfloat16>(x, row_sumsq, n_tiles, weight, y, rows, cols, eps, s);
+        default:         return cudaErrorInvalidValue;
+    }
+}
+
+CCK_DEBUG_BOUNDS_EXPORT(rmsnorm)

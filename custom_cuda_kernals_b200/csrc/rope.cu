@@ -106,8 +106,8 @@ rope_scalar_kernel(const T* __restrict__ q, const T* __restrict__ k, const float
         const int rem = static_cast<int>(idx - tok * per_token);
         const int h = rem / half, i = rem - h * half;
         const int s_idx = static_cast<int>(tok % seq_len);
-        const float c = cos_t[static_cast<int64_t>(s_idx) * half + i];
-        const float sn = sin_t[static_cast<int64_t>(s_idx) * half + i];
+        const float c = Store<float>::load1(cos_t + static_cast<int64_t>(s_idx) * half + i);
+        const float sn = Store<float>::load1(sin_t + static_cast<int64_t>(s_idx) * half + i);
         const bool is_q = h < hq;
         const T* src = is_q ? q : k;
         T* dst = is_q ? q_out : k_out;
@@ -199,3 +199,5 @@ extern "C" int32_t launch_rope_strided_fwd(const void* q, const void* k, const v
     return rope_dispatch(q, k, cos_table, sin_table, q_out, k_out, batch, seq_len, n_q_heads, n_kv_heads, head_dim,
                          q_token_stride, k_token_stride, dtype, stream);
 }
+
+CCK_DEBUG_BOUNDS_EXPORT(rope)

@@ -96,3 +96,5 @@ extern "C" int32_t launch_swiglu_fwd(const void* gate, const void* up, void* y, 
         default:         return cudaErrorInvalidValue;
     }
 }
+
+CCK_DEBUG_BOUNDS_EXPORT(swiglu)

@@ -8,7 +8,8 @@ import torch
 
 from .. import _native
 
-__all__ = ["interleave_gate_up", "matmul_swiglu", "matmul_add_bias_residual", "GATE_UP_BLOCK"]
+__all__ = ["interleave_gate_up", "matmul_swiglu", "matmul_add_bias_residual", "matmul_add_bias_stats",
+           "rmsnorm_from_stats", "fp8_quant_token_from_amax", "GATE_UP_BLOCK"]
 
 GATE_UP_BLOCK = 128
 
@@ -40,3 +41,48 @@ def matmul_add_bias_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.
     y = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
     _native.matmul_add_bias_residual_fwd(x, weight, bias, residual, y)
     return y
+
+
+def matmul_add_bias_stats(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                          residual: torch.Tensor | None = None, sumsq: bool = True, amax: bool = False
+                          ) -> tuple[torch.Tensor, torch.Tensor | None, torch.Tensor | None]:
+    """``y = x @ weight.T + bias (+ residual)`` - bit for bit what ``matmul_add_bias`` (or
+    ``matmul_add_bias_residual``) returns - together with what the op after it needs, computed in
+    the same epilogue from the stored values: ``row_sumsq`` and / or ``row_amax``, each
+    ``[ceil(N / 256), M]`` float32 (one value per row and 256-column output tile; the tiles of a row
+    are computed by different CTAs).  Feed them to ``rmsnorm_from_stats`` /
+    ``fp8_quant_token_from_amax``, which then skip their own row reduction.  These are the steps
+    either side of o_proj and down_proj in the reference's block (examples/llama_block.py:163-172).
+    Returns ``(y, row_sumsq or None, row_amax or None)``."""
+    m, n = x.shape[0], weight.shape[0]
+    tiles = _native.gemm_stat_tiles(n)
+    y = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    stats = torch.empty((int(sumsq) + int(amax), tiles, m), dtype=torch.float32, device=x.device)
+    ss = stats[0] if sumsq else None
+    am = stats[int(sumsq)] if amax else None
+    _native.matmul_add_bias_stats_fwd(x, weight, bias, residual, y, ss, am)
+    return y, ss, am
+
+
+def rmsnorm_from_stats(x: torch.Tensor, row_sumsq: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """``rmsnorm(x, weight, eps)`` for an ``x`` that came out of ``matmul_add_bias_stats``: the
+    sum of squares of every row is the sum of its ``row_sumsq`` partials (added in tile order),
+    so this pass only scales.  Same rounding chain as ``rmsnorm``; the two can differ where the
+    order of the fp32 additions moves the statistic by an ulp."""
+    y = torch.empty_like(x)
+    _native.rmsnorm_from_stats_fwd(x, row_sumsq, weight, y, eps)
+    return y
+
+
+def fp8_quant_token_from_amax(x: torch.Tensor, row_amax: torch.Tensor, fp8_format: str = "e4m3"
+                              ) -> tuple[torch.Tensor, torch.Tensor]:
+    """``fp8_quant(x, fp8_format, "token")`` for an ``x`` that came out of
+    ``matmul_add_bias_stats(..., amax=True)``: bit-identical codes and ``[M, 1]`` scales, without
+    the row-wide maximum (it is the maximum of the row's ``row_amax`` partials)."""
+    if fp8_format not in ("e4m3", "e5m2"):
+        raise ValueError(f"fp8_format must be 'e4m3' or 'e5m2', got {fp8_format!r}")
+    fp8_dtype = torch.float8_e4m3fn if fp8_format == "e4m3" else torch.float8_e5m2
+    codes = torch.empty(x.shape, dtype=fp8_dtype, device=x.device)
+    scale = torch.empty((x.shape[0], 1), dtype=torch.float32, device=x.device)
+    _native.fp8_quant_token_from_amax_fwd(x, row_amax, codes, scale, fp8_format)
+    return codes, scale

@@ -78,10 +78,12 @@ int32_t launch_linear_ce_chunk_update(const void* logits_chunk, const int64_t* t
 int32_t launch_fp8_quant_token_fwd(const void* x, uint8_t* x_fp8, float* scale, int64_t m, int64_t n,
                                    int32_t dtype, int32_t fp8_format, void* stream);
 
-/* y = (a_codes * a_scale[row]) @ (w_codes * w_scale[col])^T + bias with e4m3 operands on the
- * tensor cores.  a_codes [m, k], w_codes [n, k] e4m3 bytes; a_scale [m], w_scale [n] float32;
- * bias [n] in out_dtype or NULL; y [m, n] in out_dtype (CCK_BF16 or CCK_F16).
- * Requires k % 16 == 0 and 16-byte aligned operands; otherwise cudaErrorInvalidValue. */
+/* y = (a_codes * a_scale[row]) @ (w_codes * w_scale[col])^T + bias with e4m3 operands.
+ * a_codes [m, k], w_codes [n, k] e4m3 bytes; a_scale [m], w_scale [n] float32; bias [n] in
+ * out_dtype or NULL; y [m, n] in out_dtype (CCK_BF16 or CCK_F16, else cudaErrorInvalidValue).
+ * Every shape runs, like launch_matmul_add_bias_fwd (the reference's launcher falls back for
+ * every shape, csrc/kernels/matmul_add_bias.cu:170-180): k % 16 == 0 with 16-byte aligned
+ * operands goes to the tensor cores (tcgen05 kind::f8f6f4), anything else to a CUDA-core kernel. */
 int32_t launch_matmul_add_bias_fp8_fwd(const uint8_t* a_codes, const float* a_scale, const uint8_t* w_codes,
                                        const float* w_scale, const void* bias, void* y, int64_t m, int64_t k,
                                        int64_t n, int32_t out_dtype, void* stream);
@@ -253,6 +255,37 @@ int32_t launch_transpose_2byte(const void* in, int64_t rows, int64_t cols, void*
  * 16-byte aligned x, weight and y; otherwise cudaErrorInvalidValue. */
 int32_t launch_matmul_accumulate_f32_fwd(const void* x, const void* weight, float* y, int64_t m, int64_t k,
                                          int64_t n, int32_t dtype, void* stream);
+
+/* y = x @ weight^T + bias (+ residual when not NULL): bit for bit what launch_matmul_add_bias_fwd
+ * (or launch_matmul_add_bias_residual_fwd) stores, and in the same epilogue the statistics the op
+ * AFTER the GEMM needs, per row and per 256-column output tile, taken from the stored (rounded)
+ * values: row_sumsq[t][row] = sum of squares, row_amax[t][row] = largest magnitude, each
+ * [cck_gemm_stat_tiles(n), m] float32, either may be NULL.  A row's tiles are computed by
+ * different CTAs, so the row-wide reduction is the consumer's (n_tiles values per row):
+ * launch_rmsnorm_from_stats_fwd and launch_fp8_quant_token_from_amax_fwd.  float16/bfloat16,
+ * k % 8 == 0, 16-byte aligned x and weight; otherwise cudaErrorInvalidValue.  These are the steps
+ * either side of the projections in the reference's decoder block (examples/llama_block.py:163-172:
+ * o_proj -> norm, down_proj -> next norm); the reference has no fused form of them. */
+int64_t cck_gemm_stat_tiles(int64_t n);
+int32_t launch_matmul_add_bias_stats_fwd(const void* x, const void* weight, const void* bias, const void* residual,
+                                         void* y, float* row_sumsq, float* row_amax, int64_t m, int64_t k,
+                                         int64_t n, int32_t dtype, void* stream);
+
+/* y = x * rsqrt(sum_t row_sumsq[t][row] / cols + eps) * weight: launch_rmsnorm_fwd for rows whose sums
+ * of squares the producing GEMM left as n_tiles partials per row.  Same rounding chain; the
+ * statistic differs from launch_rmsnorm_fwd's only in the order of its fp32 additions.
+ * float16/bfloat16, cols a multiple of 8 and at most 65536, 16-byte aligned pointers; otherwise
+ * cudaErrorInvalidValue.  No reference counterpart. */
+int32_t launch_rmsnorm_from_stats_fwd(const void* x, const float* row_sumsq, int64_t n_tiles, const void* weight,
+                                      void* y, int64_t rows, int64_t cols, float eps, int32_t dtype, void* stream);
+
+/* launch_fp8_quant_token_fwd for rows whose largest magnitudes the producing GEMM left as n_tiles
+ * partial maxima per row (row_amax [n_tiles, m]); codes and scales are bit for bit the same.
+ * float16/bfloat16, n a multiple of 8 and at most 65536, x 16-byte and x_fp8 8-byte aligned;
+ * otherwise cudaErrorInvalidValue.  No reference counterpart. */
+int32_t launch_fp8_quant_token_from_amax_fwd(const void* x, const float* row_amax, int64_t n_tiles, uint8_t* x_fp8,
+                                             float* scale, int64_t m, int64_t n, int32_t dtype, int32_t fp8_format,
+                                             void* stream);
 
 /* Number of two-CTA pairs the tensor-core GEMM keeps resident on the current device; 0 means
  * the pair kernel is unavailable (or disabled with CCK_GEMM_SINGLE_CTA=1) and the single-CTA
