@@ -222,6 +222,83 @@ fp8_token_from_amax_kernel(const T* __restrict__ x, const float* __restrict__ am
     }
 }
 
+// RMSNorm and per-token quantisation in one pass: codes, scale = fp8_quant(rmsnorm(x, w), "token"),
+// bit for bit, without the normalised row ever going to HBM (it is read 2 bytes per element and
+// written 1; the two-kernel chain moves 2 + 2 + 2 + 1).  The row lives in registers from the load to
+// the store; the sum of squares is reduced exactly as rmsnorm_rowreg_kernel reduces it (same
+// thread-to-vector map, same fp32 additions), or - when the producing GEMM left partial sums of
+// squares ([n_tiles][rows]) - taken from those in tile order, as launch_rmsnorm_from_stats_fwd does.
+// `y`, when not null, also receives the normalised row in the storage type.
+template <typename T, bool E5M2, int VPT>
+__global__ void __launch_bounds__(1024)
+rmsnorm_fp8_token_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ sumsq, int n_tiles,
+                         int64_t rows, T* __restrict__ y, uint8_t* __restrict__ codes, float* __restrict__ scale,
+                         int cols, int n_vec, float eps) {
+    constexpr int kPer = Store<T>::kPerVec;
+    __shared__ float slots[32];
+    const int64_t row = blockIdx.x;
+    const Vec16* x16 = reinterpret_cast<const Vec16*>(x) + row * n_vec;
+    const Vec16* w16 = reinterpret_cast<const Vec16*>(w);
+    Vec16 v[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) v[j] = ld_stream(x16 + i);
+    }
+    float total;
+    if (sumsq != nullptr) {
+        total = 0.0f;
+        for (int t = 0; t < n_tiles; ++t) total += sumsq[static_cast<int64_t>(t) * rows + row];
+    } else {
+        float sq = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            if (static_cast<int>(threadIdx.x + j * blockDim.x) < n_vec) {
+                float a[kPer];
+                unpack<T>(v[j], a);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) sq = fmaf(a[e], a[e], sq);
+            }
+        }
+        sq = warp_sum(sq);                              // the reduction of rmsnorm_rowreg_kernel
+        const int warps = blockDim.x >> 5;
+        if (warps == 1) {
+            total = sq;
+        } else {
+            if ((threadIdx.x & 31) == 0) slots[threadIdx.x >> 5] = sq;
+            __syncthreads();
+            total = 0.0f;
+            for (int i = 0; i < warps; ++i) total += slots[i];
+            __syncthreads();                            // slots are reused by the maximum below
+        }
+    }
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(cols) + eps);
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) {
+            float a[kPer], g[kPer];
+            unpack<T>(v[j], a);
+            unpack<T>(ld_cached(w16 + i), g);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) a[e] = Store<T>::round(a[e] * inv) * g[e];
+            v[j] = pack<T>(a);                          // the normalised row, rounded to the storage type
+            if (y != nullptr) st_stream(reinterpret_cast<Vec16*>(y) + row * n_vec + i, v[j]);
+            m = fmaxf(m, Chunk<T>::amax(v[j]));
+        }
+    }
+    const float sc = scale_of<E5M2>(cta_max_dyn(m, slots));
+    if (threadIdx.x == 0) scale[row] = sc;
+    const ExactDiv div = ExactDiv::make(sc);
+    uint8_t* cr = codes + row * cols;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n_vec) Chunk<T>::template quantise_store<E5M2>(v[j], div, cr + static_cast<int64_t>(i) * kPer);
+    }
+}
+
 // any n / alignment: scalar, the row is read twice (second time from L1/L2)
 template <typename T, bool E5M2>
 __global__ void __launch_bounds__(256)
@@ -427,6 +504,29 @@ cudaError_t run_token(const void* x, uint8_t* codes, float* scale, int64_t m, in
 }
 
 template <typename T, bool E5M2>
+cudaError_t run_rmsnorm_fp8(const void* x, const void* w, const float* sumsq, int64_t n_tiles, void* y, uint8_t* codes,
+                            float* scale, int64_t rows, int64_t cols, float eps, cudaStream_t s) {
+    constexpr int kPer = Store<T>::kPerVec;
+    const int64_t n_vec = cols / kPer;
+    if (rows > 0x7fffffffLL || cols % kPer != 0 || n_vec > 8 * 1024 || !aligned16(x) || !aligned16(w) ||
+        (y != nullptr && !aligned16(y)) || (reinterpret_cast<uintptr_t>(codes) % kPer) != 0 ||
+        (sumsq != nullptr && (n_tiles <= 0 || n_tiles > 4096)))
+        return cudaErrorInvalidValue;
+    const int vpt = n_vec <= 4 * 1024 ? 4 : 8;         // the CTA shape of rmsnorm_rowreg_kernel
+    int threads = static_cast<int>(ceil_div64(ceil_div64(n_vec, vpt), 32) * 32);
+    if (threads < 32) threads = 32;
+    const unsigned grid = static_cast<unsigned>(rows);
+    const int nt = static_cast<int>(n_tiles), nc = static_cast<int>(cols), nv = static_cast<int>(n_vec);
+    if (vpt == 4)
+        rmsnorm_fp8_token_kernel<T, E5M2, 4><<<grid, threads, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(w), sumsq,
+                                                                      nt, rows, static_cast<T*>(y), codes, scale, nc, nv, eps);
+    else
+        rmsnorm_fp8_token_kernel<T, E5M2, 8><<<grid, threads, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(w), sumsq,
+                                                                      nt, rows, static_cast<T*>(y), codes, scale, nc, nv, eps);
+    return cudaGetLastError();
+}
+
+template <typename T, bool E5M2>
 cudaError_t run_token_from_amax(const void* x, const float* amax, int64_t n_tiles, uint8_t* codes, float* scale,
                                 int64_t m, int64_t n, cudaStream_t s) {
     constexpr int kPer = Store<T>::kPerVec;
@@ -576,6 +676,34 @@ extern "C" int32_t launch_fp8_quant_token_from_amax_fwd(const void* x, const flo
         case kBF16:
             return e5 ? run_token_from_amax<__nv_bfloat16, true>(x, row_amax, n_tiles, x_fp8, scale, m, n, s)
                       : run_token_from_amax<__nv_bfloat16, false>(x, row_amax, n_tiles, x_fp8, scale, m, n, s);
+        default:
+            return cudaErrorInvalidValue;
+    }
+}
+
+// x_fp8, scale = fp8_quant(rmsnorm(x, weight, eps), "token"), bit for bit, in one pass over x: the
+// normalised row stays in registers between the norm and the quantiser (3 bytes of HBM traffic per
+// element instead of 7).  row_sumsq, when not NULL, holds n_tiles partial sums of squares per row
+// ([n_tiles, rows], from launch_matmul_add_bias_stats_fwd) and replaces the row reduction (the result
+// then equals fp8_quant(rmsnorm_from_stats(...))).  y, when not NULL, also receives the normalised
+// rows.  float16/bfloat16, cols a multiple of 8 and at most 65536, 16-byte aligned x, weight and y,
+// 8-byte aligned x_fp8; otherwise cudaErrorInvalidValue.  No counterpart in the reference.
+extern "C" int32_t launch_rmsnorm_fp8_quant_token_fwd(const void* x, const void* weight, const float* row_sumsq,
+                                                      int64_t n_tiles, void* y, uint8_t* x_fp8, float* scale,
+                                                      int64_t rows, int64_t cols, float eps, int32_t dtype,
+                                                      int32_t fp8_format, void* stream) {
+    using namespace cck;
+    if (rows <= 0 || cols <= 0) return cudaSuccess;
+    if (fp8_format != kF8E4M3 && fp8_format != kF8E5M2) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool e5 = fp8_format == kF8E5M2;
+    switch (dtype) {
+        case kF16:
+            return e5 ? run_rmsnorm_fp8<__half, true>(x, weight, row_sumsq, n_tiles, y, x_fp8, scale, rows, cols, eps, s)
+                      : run_rmsnorm_fp8<__half, false>(x, weight, row_sumsq, n_tiles, y, x_fp8, scale, rows, cols, eps, s);
+        case kBF16:
+            return e5 ? run_rmsnorm_fp8<__nv_bfloat16, true>(x, weight, row_sumsq, n_tiles, y, x_fp8, scale, rows, cols, eps, s)
+                      : run_rmsnorm_fp8<__nv_bfloat16, false>(x, weight, row_sumsq, n_tiles, y, x_fp8, scale, rows, cols, eps, s);
         default:
             return cudaErrorInvalidValue;
     }

@@ -18,6 +18,13 @@
 // roles on a pair of CTAs that share a 256 x 256 tile (cta_group::2) and is the
 // default.  Every CTA fetches its own operand tiles; no load is shared across CTAs.
 // All waits are bounded; a time-out sets bit 0 of *status and the CTA leaves.
+//
+// Operand layouts (kMajors): by default A [M,K] and B [N,K] are both K-major (rows contiguous
+// along K: activations [tokens, features], nn.Linear weights [out, in]).  Bit 0 (kAMn) / bit 1
+// (kBMn) of kMajors switch an operand to MN-major: it is stored as [K, M] (or [K, N]) row-major
+// - the transpose of the above - and is fed to the tensor cores as stored, through 64 x 64
+// TMA boxes and MN-major shared-memory descriptors, so gradient GEMMs (dX = dY W, dW = dY^T X)
+// need no transposed copies of their operands.  16-bit types only.
 #pragma once
 
 #include <cstdlib>
@@ -43,6 +50,8 @@ constexpr int kTmemCols = 512;                 // two 256-column fp32 accumulato
 constexpr int kScratchFloatsPerWarp = 2 * kBN; // per-epilogue-warp staging (bias / scales)
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
                            kEpiWarps * kScratchFloatsPerWarp * 4;
+constexpr int kAMn = 1, kBMn = 2;              // kMajors bits: operand stored [K, M] / [K, N]
+constexpr int kMnBoxBytes = 64 * kRowBytes;    // one 64 (MN) x 64 (K) box of an MN-major operand: 8 KiB
 
 struct TileWork {
     int m_tile, n_tile;
@@ -133,7 +142,30 @@ template <int BN> struct TileShape {
     static constexpr int kSmemBytesN = kStagesN * kStageBytesN + 1024 + 256 + kEpiWarps * kScratchFloatsPerWarp * 4;
 };
 
-template <bool kFp8, class Sched, class Epi, int BN = kBN>
+// One K slab of one operand into shared memory at `dst`: a single box for a K-major operand,
+// `mn_extent / 64` boxes of 64 x 64 for an MN-major one (x = M / N coordinate, y = K coordinate).
+template <bool kMn, bool kPairLoad>
+__device__ __forceinline__ void load_slab(uint32_t dst, const CUtensorMap* map, uint32_t bar, int kb, int elems_per_slab,
+                                          int mn0, int mn_extent) {
+    if constexpr (!kMn) {
+        if constexpr (kPairLoad) ptx::tma_load_2d_pair(dst, map, bar, kb * elems_per_slab, mn0);
+        else                     ptx::tma_load_2d(dst, map, bar, kb * elems_per_slab, mn0);
+    } else {
+        for (int j = 0; j < mn_extent / 64; ++j) {
+            if constexpr (kPairLoad) ptx::tma_load_2d_pair(dst + j * kMnBoxBytes, map, bar, mn0 + 64 * j, kb * 64);
+            else                     ptx::tma_load_2d(dst + j * kMnBoxBytes, map, bar, mn0 + 64 * j, kb * 64);
+        }
+    }
+}
+template <bool kMn>
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+    if constexpr (kMn) return ptx::smem_desc_mn_sw128(saddr, kMnBoxBytes);
+    else               return ptx::smem_desc_k_sw128(saddr);
+}
+// what one 16-element K step adds to the descriptor's start-address field
+template <bool kMn> __host__ __device__ constexpr uint64_t k_step() { return kMn ? (2048 >> 4) : (32 >> 4); }
+
+template <bool kFp8, class Sched, class Epi, int BN = kBN, int kMajors = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const typename Sched::Params sp, const typename Epi::Params ep, int k_blocks, uint32_t idesc,
@@ -157,6 +189,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int kElemsPerSlab = kFp8 ? 128 : 64;
+    constexpr bool kAIsMn = (kMajors & kAMn) != 0, kBIsMn = (kMajors & kBMn) != 0;
+    static_assert(!kFp8 || kMajors == 0, "MN-major operands are for 16-bit types");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -195,8 +229,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
                     const uint32_t a_dst = base + stage * kStageBytes;
-                    ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kElemsPerSlab, m0);
-                    ptx::tma_load_2d(a_dst + kABytes, &tmap_b, full_bar(stage), kb * kElemsPerSlab, n0);
+                    load_slab<kAIsMn, false>(a_dst, &tmap_a, full_bar(stage), kb, kElemsPerSlab, m0, kBM);
+                    load_slab<kBIsMn, false>(a_dst + kABytes, &tmap_b, full_bar(stage), kb, kElemsPerSlab, n0, BN);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -220,13 +254,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, status)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
                     const uint32_t a_src = base + stage * kStageBytes;
-                    const uint64_t da = ptx::smem_desc_k_sw128(a_src);
-                    const uint64_t db = ptx::smem_desc_k_sw128(a_src + kABytes);
+                    const uint64_t da = operand_desc<kAIsMn>(a_src);
+                    const uint64_t db = operand_desc<kBIsMn>(a_src + kABytes);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {        // 4 x 32 bytes of K per slab
                         const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
-                        if (kFp8) ptx::mma_f8(d, da + 2 * k, db + 2 * k, idesc, acc);
-                        else      ptx::mma_f16(d, da + 2 * k, db + 2 * k, idesc, acc);
+                        if (kFp8) ptx::mma_f8(d, da + k_step<kAIsMn>() * k, db + k_step<kBIsMn>() * k, idesc, acc);
+                        else      ptx::mma_f16(d, da + k_step<kAIsMn>() * k, db + k_step<kBIsMn>() * k, idesc, acc);
                     }
                     ptx::mma_commit(empty_bar(stage));   // stage reusable once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -298,7 +332,7 @@ constexpr int kPairBBytes = 128 * kRowBytes;                    // this CTA's ha
 constexpr int kPairStageBytes = kABytes + kPairBBytes;          // 32 KiB
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256 + kEpiWarps * kScratchFloatsPerWarp * 4;
 
-template <bool kFp8, class Sched, class Epi>
+template <bool kFp8, class Sched, class Epi, int kMajors = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const typename Sched::Params sp, const typename Epi::Params ep, int k_blocks, uint32_t idesc,
@@ -322,6 +356,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const bool leader = rank == 0;
     const int pair_id = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     constexpr int kElemsPerSlab = kFp8 ? 128 : 64;
+    constexpr bool kAIsMn = (kMajors & kAMn) != 0, kBIsMn = (kMajors & kBMn) != 0;
+    static_assert(!kFp8 || kMajors == 0, "MN-major operands are for 16-bit types");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPairStages; ++s) {
@@ -364,8 +400,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
                     if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * kPairStageBytes);
                     const uint32_t a_dst = base + stage * kPairStageBytes;
-                    ptx::tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * kElemsPerSlab, m0);
-                    ptx::tma_load_2d_pair(a_dst + kABytes, &tmap_b, leader_full, kb * kElemsPerSlab, n0);
+                    load_slab<kAIsMn, true>(a_dst, &tmap_a, leader_full, kb, kElemsPerSlab, m0, kBM);
+                    load_slab<kBIsMn, true>(a_dst + kABytes, &tmap_b, leader_full, kb, kElemsPerSlab, n0, 128);
                     if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -389,13 +425,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, status)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
                     const uint32_t a_src = base + stage * kPairStageBytes;
-                    const uint64_t da = ptx::smem_desc_k_sw128(a_src);
-                    const uint64_t db = ptx::smem_desc_k_sw128(a_src + kABytes);
+                    const uint64_t da = operand_desc<kAIsMn>(a_src);
+                    const uint64_t db = operand_desc<kBIsMn>(a_src + kABytes);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
-                        if (kFp8) ptx::mma_f8_pair(d, da + 2 * k, db + 2 * k, idesc, acc);
-                        else      ptx::mma_f16_pair(d, da + 2 * k, db + 2 * k, idesc, acc);
+                        if (kFp8) ptx::mma_f8_pair(d, da + k_step<kAIsMn>() * k, db + k_step<kBIsMn>() * k, idesc, acc);
+                        else      ptx::mma_f16_pair(d, da + k_step<kAIsMn>() * k, db + k_step<kBIsMn>() * k, idesc, acc);
                     }
                     ptx::mma_commit_pair(ptx::map_to_cta(empty_bar(stage), 0));   // stage free in both CTAs
                     ptx::mma_commit_pair(ptx::map_to_cta(empty_bar(stage), 1));
@@ -472,6 +508,21 @@ inline cudaError_t make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int elem_
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// MN-major operand: the matrix is stored [k_rows, mn_cols] row-major; box = 64 (MN, 128 bytes) x 64 (K).
+inline cudaError_t make_tmap_mn(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr, int64_t k_rows,
+                                int64_t mn_cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn_cols), static_cast<cuuint64_t>(k_rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(mn_cols) * 2};
+    const cuuint32_t box[2] = {64, 64};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 // CCK_GEMM_SINGLE_CTA=1 in the environment keeps every GEMM on the single-CTA kernel.
 inline bool pair_kernels_enabled() {
     static const bool on = [] {
@@ -514,10 +565,10 @@ inline int sm_count() {
     return n;
 }
 
-template <bool kFp8, class Sched, class Epi, int BN = kBN>
+template <bool kFp8, class Sched, class Epi, int BN = kBN, int kMajors = 0>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const typename Sched::Params& sp,
                    const typename Epi::Params& ep, int64_t k_elems, uint32_t idesc, int ctas, cudaStream_t s) {
-    auto kern = gemm_kernel<kFp8, Sched, Epi, BN>;
+    auto kern = gemm_kernel<kFp8, Sched, Epi, BN, kMajors>;
     constexpr int kSmemBytes = TileShape<BN>::kSmemBytesN;
     static bool configured[kMaxDevices] = {};   // per instantiation and device
     const int slot = current_device_slot();
@@ -536,14 +587,14 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const typename 
 }
 
 // Number of CTA pairs that can be resident at once (at most one pair per TPC).
-template <bool kFp8, class Sched, class Epi>
+template <bool kFp8, class Sched, class Epi, int kMajors = 0>
 int max_pairs() {
     static int cached_per_device[kMaxDevices] = {};
     const int slot = current_device_slot();
     if (slot < 0) return 0;
     int& cached = cached_per_device[slot];
     if (cached > 0) return cached;
-    auto kern = gemm_pair_kernel<kFp8, Sched, Epi>;
+    auto kern = gemm_pair_kernel<kFp8, Sched, Epi, kMajors>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess) return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * sm_count());
@@ -570,18 +621,18 @@ int max_pairs() {
 }
 
 // `pair_tiles` = number of 256-row x 256-column tiles (or units) to spread over the pairs.
-template <bool kFp8, class Sched, class Epi>
+template <bool kFp8, class Sched, class Epi, int kMajors = 0>
 cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const typename Sched::Params& sp,
                         const typename Epi::Params& ep, int64_t k_elems, uint32_t idesc, int64_t pair_tiles,
                         cudaStream_t s) {
-    const int cap = max_pairs<kFp8, Sched, Epi>();
+    const int cap = max_pairs<kFp8, Sched, Epi, kMajors>();
     if (cap <= 0) return cudaErrorLaunchOutOfResources;
     unsigned int* st = status_word();
     if (!st) return cudaErrorMemoryAllocation;
     const int pairs = static_cast<int>(pair_tiles < cap ? pair_tiles : cap);
     const int slab = kFp8 ? 128 : 64;
     const int k_blocks = static_cast<int>((k_elems + slab - 1) / slab);
-    gemm_pair_kernel<kFp8, Sched, Epi><<<2 * pairs, kThreads, kPairSmemBytes, s>>>(ta, tb, sp, ep, k_blocks, idesc, st);
+    gemm_pair_kernel<kFp8, Sched, Epi, kMajors><<<2 * pairs, kThreads, kPairSmemBytes, s>>>(ta, tb, sp, ep, k_blocks, idesc, st);
     return cudaGetLastError();
 }
 

@@ -424,8 +424,10 @@ lce_dlogits_from_logits_kernel(const float* __restrict__ logits, const int64_t* 
         const float d = ex2_approx(fmaf(lg[i].w, kLog2e, par.x)) * par.y;
         const uint32_t p0 = Store<T>::pack2(a, b), p1 = Store<T>::pack2(c, d);
         if (row0 + r < n && col_ok) st_stream8(dl + (row0 + r) * v + col, p0, p1);
-        const int slot = (r >> 2) + 16 * (r & 3);
-        *reinterpret_cast<uint2*>(&tile[slot * kDlPitchW + 2 * lane]) = make_uint2(p0, p1);
+        if (dl_t != nullptr) {
+            const int slot = (r >> 2) + 16 * (r & 3);
+            *reinterpret_cast<uint2*>(&tile[slot * kDlPitchW + 2 * lane]) = make_uint2(p0, p1);
+        }
     }
     __syncthreads();
     if (my_target >= 0) {                             // the target column's element: (p - 1) * scale
@@ -436,8 +438,9 @@ lce_dlogits_from_logits_kernel(const float* __restrict__ logits, const int64_t* 
         Store<T>::store1(&val, (ex2_approx(fmaf(l, kLog2e, par.x)) - 1.0f) * par.y);
         dl[(row0 + r) * v + my_target] = val;
         const int c = static_cast<int>(my_target - col0);
-        reinterpret_cast<T*>(&tile[((r >> 2) + 16 * (r & 3)) * kDlPitchW])[c] = val;
+        if (dl_t != nullptr) reinterpret_cast<T*>(&tile[((r >> 2) + 16 * (r & 3)) * kDlPitchW])[c] = val;
     }
+    if (dl_t == nullptr) return;                      // row-major output only (the GEMMs that follow read it as stored)
     __syncthreads();
     const int quad = lane & 15, half = lane >> 4;
     const int64_t rq = row0 + 4 * quad;               // first row of this lane's quad
@@ -533,9 +536,9 @@ extern "C" int32_t launch_linear_cross_entropy_fwd_store(const void* hidden, con
                                       workspace_bytes, logits, dtype, static_cast<cudaStream_t>(stream));
 }
 
-// d(loss)/d(logits) from stored logits: dlogits [n, v] and its transpose dlogits_t [v, ld_t]
-// (ld_t >= n, a multiple of 4; columns n..ld_t of dlogits_t are not written), both in the
-// storage type.  `targets` index the columns of `logits` (a value outside [0, v) selects none);
+// d(loss)/d(logits) from stored logits: dlogits [n, v] and, unless dlogits_t is NULL, its
+// transpose dlogits_t [v, ld_t] (ld_t >= n, a multiple of 4; columns n..ld_t of dlogits_t are
+// not written), both in the storage type.  `targets` index the columns of `logits` (a value outside [0, v) selects none);
 // v % 4 == 0.
 extern "C" int32_t launch_lce_dlogits_from_logits(const float* logits, const int64_t* targets, const float* lse,
                                                   int64_t n, int64_t v, int64_t ignore_index, float grad_scale,
@@ -545,8 +548,8 @@ extern "C" int32_t launch_lce_dlogits_from_logits(const float* logits, const int
     using namespace cck::tc;
     if (n <= 0 || v <= 0) return cudaSuccess;
     if (dtype != kBF16 && dtype != kF16) return cudaErrorInvalidValue;
-    if (v % 4 != 0 || ld_t < n || ld_t % 4 != 0 || !aligned16(logits) || (reinterpret_cast<uintptr_t>(dlogits) & 7u) ||
-        (reinterpret_cast<uintptr_t>(dlogits_t) & 7u))
+    if (v % 4 != 0 || !aligned16(logits) || (reinterpret_cast<uintptr_t>(dlogits) & 7u)) return cudaErrorInvalidValue;
+    if (dlogits_t != nullptr && (ld_t < n || ld_t % 4 != 0 || (reinterpret_cast<uintptr_t>(dlogits_t) & 7u)))
         return cudaErrorInvalidValue;
     const int64_t gx = ceil_div64(v, kDlCols), gy = ceil_div64(n, kDlRows);
     if (gy > 65535) return cudaErrorInvalidValue;

@@ -762,7 +762,9 @@ void lce_dlogits_fwd(const at::Tensor& hidden, const at::Tensor& weight, const a
 
 void lce_dlogits_from_logits(const at::Tensor& logits, const at::Tensor& targets, const at::Tensor& lse,
                              int64_t ignore_index, double grad_scale, const at::Tensor& dlogits,
-                             const at::Tensor& dlogits_t) {
+                             const c10::optional<at::Tensor>& dlogits_t_opt) {
+    const bool want_t = dlogits_t_opt.has_value() && dlogits_t_opt->defined();
+    const at::Tensor dlogits_t = want_t ? *dlogits_t_opt : at::Tensor();
     expect_f32("logits", tag_of("logits", logits));
     expect_f32("lse", tag_of("lse", lse));
     expect_int("targets", targets, at::kLong, "int64");
@@ -771,8 +773,8 @@ void lce_dlogits_from_logits(const at::Tensor& logits, const at::Tensor& targets
         value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
     // dlogits_t may be a column range of a wider row-major matrix (the transposes of several row
     // chunks side by side): rows are stride(0) apart, elements within a row adjacent
-    if (!dlogits_t.is_cuda()) value_error("argument 'dlogits_t' must be a CUDA tensor");
-    if (dlogits_t.scalar_type() != dlogits.scalar_type())
+    if (want_t && !dlogits_t.is_cuda()) value_error("argument 'dlogits_t' must be a CUDA tensor");
+    if (want_t && dlogits_t.scalar_type() != dlogits.scalar_type())
         value_error("dtype mismatch: 'dlogits_t' must have dlogits' dtype");
     if (logits.dim() != 2) value_error("shape mismatch: logits must be 2-D; got " + shape_str(logits));
     const int64_t n = logits.size(0), v = logits.size(1);
@@ -780,8 +782,8 @@ void lce_dlogits_from_logits(const at::Tensor& logits, const at::Tensor& targets
         value_error("shape mismatch: targets and lse must have " + std::to_string(n) + " elements");
     if (dlogits.dim() != 2 || dlogits.size(0) != n || dlogits.size(1) != v)
         value_error("shape mismatch: dlogits shape " + shape_str(dlogits) + " must be " + shape_str(logits));
-    if (dlogits_t.dim() != 2 || dlogits_t.size(0) != v || dlogits_t.size(1) < n || dlogits_t.stride(1) != 1 ||
-        dlogits_t.stride(0) < dlogits_t.size(1) || dlogits_t.stride(0) % 4 != 0 || dlogits_t.storage_offset() % 4 != 0)
+    if (want_t && (dlogits_t.dim() != 2 || dlogits_t.size(0) != v || dlogits_t.size(1) < n || dlogits_t.stride(1) != 1 ||
+        dlogits_t.stride(0) < dlogits_t.size(1) || dlogits_t.stride(0) % 4 != 0 || dlogits_t.storage_offset() % 4 != 0))
         value_error("shape mismatch: dlogits_t shape " + shape_str(dlogits_t) + " must be [" + std::to_string(v) +
                     ", >= " + std::to_string(n) + "] with unit inner stride, and a row pitch and offset that are multiples of 4");
     if (v % 4 != 0) value_error("shape mismatch: the vocabulary size must be a multiple of 4");
@@ -791,7 +793,8 @@ void lce_dlogits_from_logits(const at::Tensor& logits, const at::Tensor& targets
                                                 static_cast<const int64_t*>(targets.data_ptr()),
                                                 static_cast<const float*>(lse.data_ptr()), n, v, ignore_index,
                                                 static_cast<float>(grad_scale), dlogits.data_ptr(),
-                                                dlogits_t.data_ptr(), dlogits_t.stride(0), dt, l.stream));
+                                                want_t ? dlogits_t.data_ptr() : nullptr, want_t ? dlogits_t.stride(0) : 0,
+                                                dt, l.stream));
 }
 
 void transpose_2byte(const at::Tensor& in, const at::Tensor& out) {
@@ -955,6 +958,31 @@ void fp8_quant_token_from_amax_fwd(const at::Tensor& x, const at::Tensor& row_am
                                                       static_cast<float*>(scale.data_ptr()), m, n, dt, fmt, l.stream));
 }
 
+// y = op(a) op(b)^T with operands read as stored (transposed or not); see launch_matmul_general_fwd
+void matmul_general_fwd(const at::Tensor& a, const at::Tensor& b, const at::Tensor& y, bool a_is_km, bool b_is_kn,
+                        bool accumulate) {
+    const int32_t dt = tag_of("a", a);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
+    expect_same_dtype("b", tag_of("b", b), dt);
+    const int32_t ydt = tag_of("y", y);
+    if (accumulate) expect_f32("y", ydt, " when accumulating");
+    else expect_same_dtype("y", ydt, dt);
+    if (a.dim() != 2 || b.dim() != 2 || y.dim() != 2) value_error("shape mismatch: a, b and y must be 2-D");
+    const int64_t m = a_is_km ? a.size(1) : a.size(0), k = a_is_km ? a.size(0) : a.size(1);
+    const int64_t n = b_is_kn ? b.size(1) : b.size(0), kb = b_is_kn ? b.size(0) : b.size(1);
+    if (kb != k)
+        value_error("shape mismatch: contraction lengths differ: a gives " + std::to_string(k) + ", b gives " + std::to_string(kb));
+    if (y.size(0) != m || y.size(1) != n)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " + std::to_string(n) + "]");
+    if (a.size(1) % 8 != 0 || b.size(1) % 8 != 0)
+        value_error("shape mismatch: the contiguous dimension of a and of b must be a multiple of 8");
+    Launch l(a, {&b, &y});
+    check_launch("launch_matmul_general_fwd",
+                 launch_matmul_general_fwd(a.data_ptr(), b.data_ptr(), y.data_ptr(), m, k, n, a_is_km ? 1 : 0,
+                                           b_is_kn ? 1 : 0, accumulate ? 1 : 0, dt, l.stream));
+}
+
 uint64_t set_wait_limit_ns(const at::Tensor& like, uint64_t limit_ns) {
     c10::cuda::CUDAGuard guard(like.device());
     uint64_t previous = 0;
@@ -1006,7 +1034,7 @@ PYBIND11_MODULE(_native, m) {
           py::arg("targets"), py::arg("v_start"), py::arg("row_stats"), py::arg("workspace"),
           py::arg("logits") = py::none());
     m.def("lce_dlogits_from_logits", &lce_dlogits_from_logits, py::arg("logits"), py::arg("targets"), py::arg("lse"),
-          py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"), py::arg("dlogits_t"));
+          py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"), py::arg("dlogits_t").none(true));
     m.def("lce_dlogits_fwd", &lce_dlogits_fwd, py::arg("hidden"), py::arg("weight"), py::arg("targets"), py::arg("lse"),
           py::arg("ignore_index"), py::arg("grad_scale"), py::arg("dlogits"));
     m.def("moe_router_fwd", &moe_router_fwd, py::arg("logits"), py::arg("topk_weights"), py::arg("topk_indices"),
@@ -1037,6 +1065,8 @@ PYBIND11_MODULE(_native, m) {
           py::arg("y"), py::arg("eps"));
     m.def("fp8_quant_token_from_amax_fwd", &fp8_quant_token_from_amax_fwd, py::arg("x"), py::arg("row_amax"),
           py::arg("x_fp8"), py::arg("scale"), py::arg("fp8_format"));
+    m.def("matmul_general_fwd", &matmul_general_fwd, py::arg("a"), py::arg("b"), py::arg("y"), py::arg("a_is_km"),
+          py::arg("b_is_kn"), py::arg("accumulate"));
     m.def("gemm_stat_tiles", [](int64_t n) { return cck_gemm_stat_tiles(n); }, py::arg("n"));
     m.def("take_device_status", &take_device_status, py::arg("like"));
     m.def("set_wait_limit_ns", &set_wait_limit_ns, py::arg("like"), py::arg("limit_ns"));

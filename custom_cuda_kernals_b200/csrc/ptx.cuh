@@ -217,10 +217,28 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t saddr) {
     d |= static_cast<uint64_t>(2) << 61;           // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: fp32 accumulate, both operands K-major, dense.
+// The same for an MN-major operand tile: the matrix is stored with the M (or N) index contiguous,
+// i.e. as [K, MN] row-major in global memory, and a TMA load with a 64-element (128-byte) inner
+// box and the 128-byte swizzle writes, per box, K rows of 128 bytes.  Eight consecutive K rows
+// form one 1024-byte swizzle atom; atoms follow each other along K every 1024 bytes (stride
+// byte offset) and the next 64 MN elements start `lbo_bytes` further on (leading byte offset =
+// the size of one box, K rows x 128 bytes).  Stepping 16 elements along K skips two atoms:
+// add 2048 bytes (>>4) to the start-address field.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>(lbo_bytes >> 4) << 16;   // between 64-element groups along M / N
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;        // between 8-row groups along K
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;                // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: fp32 accumulate, dense; a_mn / b_mn = 1 for an MN-major ("transposed")
+// operand (16-bit kinds only), 0 for K-major.
 //   fmt: kind::f16 -> 0 = f16, 1 = bf16;  kind::f8f6f4 -> 0 = e4m3, 1 = e5m2
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt_a, uint32_t fmt_b, uint32_t m, uint32_t n) {
-    return (1u << 4) | (fmt_a << 7) | (fmt_b << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt_a, uint32_t fmt_b, uint32_t m, uint32_t n,
+                                                  uint32_t a_mn = 0, uint32_t b_mn = 0) {
+    return (1u << 4) | (fmt_a << 7) | (fmt_b << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 }  // namespace ptx

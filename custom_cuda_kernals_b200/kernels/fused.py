@@ -9,7 +9,7 @@ import torch
 from .. import _native
 
 __all__ = ["interleave_gate_up", "matmul_swiglu", "matmul_add_bias_residual", "matmul_add_bias_stats",
-           "rmsnorm_from_stats", "fp8_quant_token_from_amax", "GATE_UP_BLOCK"]
+           "rmsnorm_from_stats", "fp8_quant_token_from_amax", "matmul_general", "GATE_UP_BLOCK"]
 
 GATE_UP_BLOCK = 128
 
@@ -86,3 +86,25 @@ def fp8_quant_token_from_amax(x: torch.Tensor, row_amax: torch.Tensor, fp8_forma
     scale = torch.empty((x.shape[0], 1), dtype=torch.float32, device=x.device)
     _native.fp8_quant_token_from_amax_fwd(x, row_amax, codes, scale, fp8_format)
     return codes, scale
+
+
+def matmul_general(a: torch.Tensor, b: torch.Tensor, a_transposed: bool = False, b_transposed: bool = False,
+                   out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``A @ B.T`` on the tensor cores with either operand read as stored.
+
+    ``a`` holds ``A [M, K]``, or with ``a_transposed`` its transpose ``[K, M]``; ``b`` holds
+    ``B [N, K]`` (the ``nn.Linear`` weight layout), or with ``b_transposed`` ``[K, N]``.  The
+    gradients of ``y = x @ W.T`` are the transposed forms - ``dx = matmul_general(dy, W,
+    b_transposed=True)``, ``dW = matmul_general(dy, x, a_transposed=True, b_transposed=True)`` - and
+    no transposed copy of ``dy``, ``W`` or ``x`` is made.  With ``accumulate`` the product is added
+    to the float32 tensor ``out`` (a gradient summed over row chunks); otherwise the result is in
+    the operands' dtype (written to ``out`` if given).  float16 / bfloat16; the contiguous
+    dimension of each operand must be a multiple of 8."""
+    m = a.shape[1] if a_transposed else a.shape[0]
+    n = b.shape[1] if b_transposed else b.shape[0]
+    if accumulate and out is None:
+        raise ValueError("accumulate=True needs the float32 tensor to accumulate into (out=...)")
+    if out is None:
+        out = torch.empty((m, n), dtype=a.dtype, device=a.device)
+    _native.matmul_general_fwd(a, b, out, a_transposed, b_transposed, accumulate)
+    return out

@@ -128,23 +128,6 @@ def lce_grad_scale(targets: torch.Tensor, ignore_index: int, reduction: str) -> 
     return 1.0 / valid if valid else float("nan")
 
 
-_DLT_BYTES_MAX = 16 << 30
-
-
-def _padded_transpose(x: torch.Tensor, width: int | None = None) -> torch.Tensor:
-    """``x.T`` as a contiguous ``[cols, width]`` tensor (``width >= rows``, a multiple of 4),
-    zero-filled beyond ``x``'s rows."""
-    rows, cols = x.shape
-    width = rows if width is None else width
-    out = torch.empty(cols, width, dtype=x.dtype, device=x.device)
-    if cols % 4 == 0 and width % 4 == 0 and x.is_contiguous():
-        _native.transpose_2byte(x, out)
-    else:
-        out[:, :rows] = x.t()
-        out[:, rows:] = 0
-    return out
-
-
 def lce_stats_and_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, grad_scale: float,
                             v_start: int = 0, ignore_index: int = IGNORE_INDEX, rows_per_chunk: int = 8192,
                             weight_t: torch.Tensor | None = None, gather=None, recompute: bool = False
@@ -156,32 +139,28 @@ def lce_stats_and_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets:
        buffer ``[rows, V]`` (with ``recompute`` it does not, and step 2 runs the contraction a
        second time instead - no fp32 buffer, one more GEMM);
     2. ``gather`` (the statistics all-gather of a vocabulary-sharded run) and the row-wise
-       log-sum-exp; ``dlogits = (exp(logit - lse) - onehot) * grad_scale`` written in the storage
-       type, row-major and transposed, by one bandwidth-bound pass over the logits;
-    3. ``d_hidden[chunk] = dlogits @ W`` and ``d_weight += dlogits^T @ hidden[chunk]`` on the
-       tcgen05 GEMM (fp32 accumulation across chunks; written directly when one chunk covers
-       all rows).
+       log-sum-exp; ``dlogits = (exp(logit - lse) - onehot) * grad_scale`` written once, row-major,
+       in the storage type, by one bandwidth-bound pass over the logits (6 bytes per logit);
+    3. ``d_hidden[chunk] = dlogits @ W`` and ``d_weight (+)= dlogits^T @ hidden[chunk]`` on the
+       tcgen05 GEMM, which reads ``dlogits``, ``W`` and ``hidden`` as they are stored (MN-major
+       operand descriptors): no transposed copy of any of them exists.  ``d_weight`` is written
+       directly when one chunk covers all rows, else accumulated in fp32 across the chunks.
+
+    Scratch memory: ``rows_per_chunk * V * 6`` bytes (fp32 logits + dlogits of one chunk; ``* 2``
+    with ``recompute``), plus a ``V * H`` fp32 accumulator when there are several chunks.
+    ``weight_t`` is accepted for compatibility and ignored (no transposed weight is needed).
 
     Returns ``(stats [shards, 3, N], d_hidden - this shard's contribution, d_weight)``."""
+    from .fused import matmul_general
     n, h = hidden.shape
     v = weight.shape[0]
     if not (_fused_ok(hidden, weight) and hidden.is_cuda) or v % 8 != 0:
         raise ValueError("the gradient path needs float16/bfloat16 CUDA inputs with H and V multiples of 8")
     dev, dt = hidden.device, hidden.dtype
     local, local_ignore = _local_targets(targets, v_start, v, ignore_index)
-    w_t = weight_t if weight_t is not None else _padded_transpose(weight)             # [H, V]
     d_hidden = torch.empty_like(hidden)
     one_chunk = n <= rows_per_chunk
-    n_pad = (n + 7) // 8 * 8
-    # Weight gradient: with the transposed dlogits of every chunk side by side ([V, N], 2*V*N
-    # bytes) it is ONE contraction over all N rows, written directly in the storage type; beyond
-    # _DLT_BYTES_MAX the chunks are contracted one at a time into an fp32 accumulator instead.
-    side_by_side = not recompute and rows_per_chunk % 8 == 0 and v * n_pad * hidden.element_size() <= _DLT_BYTES_MAX
-    if side_by_side:
-        dl_t_all = (torch.empty if n_pad == n else torch.zeros)(v, n_pad, dtype=dt, device=dev)
-        d_weight = torch.empty(v, h, dtype=dt, device=dev)
-    else:
-        d_weight = torch.empty(v, h, dtype=dt, device=dev) if one_chunk else torch.zeros(v, h, dtype=torch.float32, device=dev)
+    d_weight = torch.empty(v, h, dtype=dt, device=dev) if one_chunk else torch.zeros(v, h, dtype=torch.float32, device=dev)
     rows_max = min(n, rows_per_chunk)
     logits = None if recompute else torch.empty(rows_max, v, dtype=torch.float32, device=dev)
     dl_buf = torch.empty(rows_max, v, dtype=dt, device=dev)
@@ -189,7 +168,6 @@ def lce_stats_and_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets:
     for r0 in range(0, n, rows_per_chunk):
         r1 = min(n, r0 + rows_per_chunk)
         rows = r1 - r0
-        width = (rows + 7) // 8 * 8             # K of the weight-gradient GEMM, a multiple of 8
         hc, tc = hidden[r0:r1], targets[r0:r1]
         dl = dl_buf[:rows]
         stats = torch.empty(3, rows, dtype=torch.float32, device=dev)
@@ -200,23 +178,11 @@ def lce_stats_and_gradients(hidden: torch.Tensor, weight: torch.Tensor, targets:
         lse = lce_lse_from_stats(stats)
         if recompute:
             _native.lce_dlogits_fwd(hc, weight, local[r0:r1], lse, local_ignore, grad_scale, dl)
-            dl_t = _padded_transpose(dl, width)
         else:
-            if side_by_side:
-                dl_t = dl_t_all[:, r0:r0 + width]
-            else:
-                dl_t = (torch.empty if width == rows else torch.zeros)(v, width, dtype=dt, device=dev)
-            _native.lce_dlogits_from_logits(logits[:rows], local[r0:r1], lse, local_ignore, grad_scale, dl, dl_t)
-        _native.matmul_add_bias_fwd(dl, w_t, None, d_hidden[r0:r1])                # [r, V] x [H, V]^T
-        if side_by_side:
-            continue
-        hc_t = _padded_transpose(hc, width)
-        if one_chunk:
-            _native.matmul_add_bias_fwd(dl_t, hc_t, None, d_weight)                # [V, r] x [H, r]^T
-        else:
-            _native.matmul_accumulate_f32_fwd(dl_t, hc_t, d_weight)
-    if side_by_side:
-        _native.matmul_add_bias_fwd(dl_t_all, _padded_transpose(hidden, n_pad), None, d_weight)   # [V, N] x [H, N]^T
+            _native.lce_dlogits_from_logits(logits[:rows], local[r0:r1], lse, local_ignore, grad_scale, dl, None)
+        matmul_general(dl, weight, b_transposed=True, out=d_hidden[r0:r1])                     # [r, V] x [V, H]
+        matmul_general(dl, hc, a_transposed=True, b_transposed=True, out=d_weight,            # [r, V]^T x [r, H]
+                       accumulate=not one_chunk)
     stats_all = stats_parts[0] if one_chunk else torch.cat(stats_parts, dim=2)
     return stats_all, d_hidden, d_weight if d_weight.dtype == dt else d_weight.to(dt)
 
@@ -230,10 +196,9 @@ def linear_cross_entropy_fwd_bwd(hidden: torch.Tensor, weight: torch.Tensor, tar
     linear_cross_entropy.py:11-18).  float16/bfloat16, ``H`` and ``V`` multiples of 8.
 
     See ``lce_stats_and_gradients``; scratch memory is ``rows_per_chunk * V * 6`` bytes (fp32
-    logits and dlogits of a chunk) plus ``2 * N * V`` for the transposed dlogits of all rows
-    (capped at 16 GiB, beyond which it is per chunk again); ``rows_per_chunk * V * 4`` with
-    ``recompute``.  ``weight_t`` may pass a
-    cached ``weight.T.contiguous()``.  Returns ``(loss, d_hidden, d_weight)``."""
+    logits and dlogits of a chunk; ``* 2`` bytes with ``recompute``) plus a ``V * H`` fp32
+    accumulator when ``N > rows_per_chunk``.  ``weight_t`` is ignored (kept for compatibility: no
+    transposed weight is needed).  Returns ``(loss, d_hidden, d_weight)``."""
     scale = lce_grad_scale(targets, ignore_index, reduction)
     stats, d_hidden, d_weight = lce_stats_and_gradients(hidden, weight, targets, scale, 0, ignore_index,
                                                         rows_per_chunk, weight_t, None, recompute)

@@ -287,6 +287,18 @@ int32_t launch_fp8_quant_token_from_amax_fwd(const void* x, const float* row_ama
                                              float* scale, int64_t m, int64_t n, int32_t dtype, int32_t fp8_format,
                                              void* stream);
 
+/* y[m, n] = A B^T on the tensor cores with either operand read as stored: A [m, k] (a_is_km = 0) or
+ * its transpose [k, m] (a_is_km = 1); B [n, k] (b_is_kn = 0, the reference's weight layout,
+ * custom_cuda/kernels/matmul_add_bias.py:16-26) or its transpose [k, n] (b_is_kn = 1).  The
+ * gradient GEMMs of a linear layer, dX = dY W and dW = dY^T X, are the transposed forms; no
+ * transposed copy of an operand is made (MN-major tcgen05 descriptors).  accumulate_f32 = 0: y in
+ * `dtype`, overwritten; 1: y float32, the product is added to it.  float16 / bfloat16; the
+ * contiguous dimension of each operand a multiple of 8, pointers 16-byte aligned; otherwise
+ * cudaErrorInvalidValue.  No reference counterpart (the reference is forward-only). */
+int32_t launch_matmul_general_fwd(const void* a, const void* b, void* y, int64_t m, int64_t k, int64_t n,
+                                  int32_t a_is_km, int32_t b_is_kn, int32_t accumulate_f32, int32_t dtype,
+                                  void* stream);
+
 /* Number of two-CTA pairs the tensor-core GEMM keeps resident on the current device; 0 means
  * the pair kernel is unavailable (or disabled with CCK_GEMM_SINGLE_CTA=1) and the single-CTA
  * kernel is used. */

@@ -8,7 +8,8 @@ fp32 FMA chain per row and 256-column tile, columns ascending; a maximum has no 
   * ``rmsnorm_from_stats(y, row_sumsq, w)`` == the norm's rounding chain evaluated with the
     canonical statistic, bit for bit; against ``rmsnorm(y, w)`` (same chain, its own summation
     order) it may differ only where the statistic moved by an ulp: at most 1e-3 of the elements,
-    each by one unit in the last place of the storage type.
+    each by at most two units in the last place of the storage type (one from the rounding of the
+    normalised value, which the multiplication by the weight and the second rounding can double).
 
 These are the steps either side of o_proj and down_proj in the reference's decoder block
 (examples/llama_block.py:163-172); the reference has no fused form, so the unfused chain of this
@@ -21,7 +22,7 @@ from tests.gpu_util import DEV, device_status_clean
 
 pytestmark = pytest.mark.gpu
 
-SHAPES = [(300, 512, 1024), (1000, 1024, 4096), (130, 64, 264), (77, 128, 256), (4096, 4096, 4096), (256, 256, 8)]
+SHAPES = [(300, 512, 1024), (1000, 1024, 4096), (130, 64, 264), (77, 128, 256), (4096, 4096, 4096), (1024, 256, 8)]
 
 
 def _inputs(m, k, n, dtype, seed):
@@ -88,16 +89,19 @@ def test_stats_epilogue_and_its_consumers(shape, dtype, with_residual):
         total = torch.zeros(m, device=DEV)
         for t in range(ss.shape[0]):
             total = total + ss[t]
-        inv = 1.0 / torch.sqrt(total / n + eps)
+        # tensor / tensor is an IEEE division on the GPU; tensor / python-scalar is a multiplication by
+        # the rounded reciprocal, which differs when n is not a power of two
+        cols = torch.tensor(float(n), device=DEV)
+        inv = torch.ones((), device=DEV) / torch.sqrt(total / cols + eps)
         chain = (y.float() * inv[:, None]).to(dtype) * gw                    # round, multiply in the storage type
         assert torch.equal(h, chain)
         unfused = rmsnorm(y, gw, eps)
         differ = (h != unfused)
         assert differ.float().mean().item() <= 1e-3
-        if differ.any():                                                     # one unit in the last place at most
+        if differ.any():                                                     # two units in the last place at most
             a, c = h[differ].float(), unfused[differ].float()
             ulp = torch.maximum(a.abs(), c.abs()) * (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10)
-            assert torch.all((a - c).abs() <= ulp)
+            assert torch.all((a - c).abs() <= 2.01 * ulp)
     assert device_status_clean(y)
 
 

@@ -277,3 +277,53 @@ def test_fused_ops_reject_what_they_cannot_run():
     with pytest.raises(ValueError):
         matmul_add_bias_residual(xb, torch.randn(32, 64, device=DEV).to(torch.bfloat16), None,
                                  torch.randn(16, 31, device=DEV).to(torch.bfloat16))
+
+
+GENERAL_SHAPES = [(256, 512, 512), (1000, 1024, 1408), (130, 72, 384), (64, 200, 264), (4096, 1000, 1024),
+                  (8, 8, 8), (300, 77, 136), (2048, 8192, 512)]
+
+
+@pytest.mark.parametrize("shape", GENERAL_SHAPES)
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_matmul_general_reads_transposed_operands_as_stored(shape, a_t, b_t, dtype):
+    """``A @ B.T`` with A stored [M,K] or [K,M] and B stored [N,K] or [K,N] (MN-major tensor-core
+    descriptors, no transposed copies): equal bit for bit to this library's GEMM on explicitly
+    transposed copies (same products, same accumulation order), and within the GEMM tolerance of an
+    fp64 product.  Ragged M, N and K (K = 77, 200, 1000: partial last slab, zero-filled by TMA)."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    from custom_cuda_kernals_b200.kernels.fused import matmul_general
+    m, k, n = shape
+    if (a_t and m % 8) or (not a_t and k % 8) or (b_t and n % 8) or (not b_t and k % 8):
+        pytest.skip("the contiguous dimension of an operand must be a multiple of 8")
+    g = torch.Generator(device=DEV).manual_seed(m + k + n)
+    a = torch.randn(m, k, device=DEV, generator=g).to(dtype)
+    b = (k ** -0.5 * torch.randn(n, k, device=DEV, generator=g)).to(dtype)
+    a_st = a.t().contiguous() if a_t else a
+    b_st = b.t().contiguous() if b_t else b
+    y = matmul_general(a_st, b_st, a_t, b_t)
+    want = matmul_add_bias(a, b)
+    if 2 * m * n * k >= 1 << 22 and k % 8 == 0:      # both on the tensor cores: identical arithmetic
+        assert torch.equal(y, want)
+    check(y.double().cpu(), a.double().cpu() @ b.double().cpu().T, dtype, ops.TOLERANCE_GEMM)
+    # accumulating form: out (fp32) += product, twice
+    acc = torch.full((m, n), 0.5, device=DEV)
+    matmul_general(a_st, b_st, a_t, b_t, out=acc, accumulate=True)
+    matmul_general(a_st, b_st, a_t, b_t, out=acc, accumulate=True)
+    torch.testing.assert_close(acc.double().cpu(), 0.5 + 2 * (a.double().cpu() @ b.double().cpu().T), rtol=1e-3, atol=1e-3)
+    assert device_status_clean(y)
+
+
+def test_matmul_general_rejects_bad_arguments():
+    from custom_cuda_kernals_b200.kernels.fused import matmul_general
+    a = torch.zeros(64, 32, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="contraction lengths differ"):
+        matmul_general(a, torch.zeros(16, 48, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="multiple of 8"):
+        matmul_general(torch.zeros(64, 36, device=DEV, dtype=torch.bfloat16), torch.zeros(16, 36, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="float16 or bfloat16"):
+        matmul_general(a.float(), a.float())
+    with pytest.raises(ValueError, match="accumulate=True needs"):
+        matmul_general(a, a, accumulate=True)
+    with pytest.raises(ValueError, match="must be float32"):
+        matmul_general(a, a, out=torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16), accumulate=True)
