@@ -675,6 +675,41 @@ def run_ours(args, rank, world, local):
                 torch.distributed.barrier()
             e2e_secs = dist.max_over_ranks(ev0.elapsed_time(ev1) * 1e-3, dev)
 
+    # The same block with FP8 projections (an extra row, not the headline: the metric is quoted in
+    # bfloat16): device-timed like `value`, with its distance from the bf16 block's output.
+    fp8_row = None
+    if not args.skip_ops:
+        from custom_cuda_kernals_b200.llama_block import LlamaBlockFP8
+        with torch.no_grad():
+            block8 = LlamaBlockFP8(weights, CFG["n_heads"], CFG["n_kv_heads"], CFG["eps"], CFG["theta"], SEQ)
+            y16, y8 = block(x_dev[:1]).float(), block8(x_dev[:1]).float()
+            rel = float((y8 - y16).norm() / y16.norm())
+            for _ in range(3):
+                block8(x_dev)
+            torch.cuda.synchronize()
+            if world > 1:
+                torch.distributed.barrier()
+            ev0.record()
+            for _ in range(args.steps):
+                block8(x_dev)
+            ev1.record()
+            torch.cuda.synchronize()
+            secs8 = dist.max_over_ranks(ev0.elapsed_time(ev1) * 1e-3, dev)
+            t8 = OpTimer()
+            for _ in range(args.steps):
+                block8(x_dev, timer=t8)
+            torch.cuda.synchronize()
+        tot8 = t8.totals()
+        gemm8_ms = dist.max_over_ranks(sum(v["ms"] for k, v in tot8.items() if k.startswith("gemm")), dev)
+        fp8_row = {"value": BATCH * SEQ * args.steps / secs8, "unit": UNIT, "ms_per_step": secs8 / args.steps * 1e3,
+                   "dtype": "e4m3 projections (per-token activation scales, per-channel weight scales), bf16 elsewhere",
+                   "gemm_tflops": round(block8.gemm_flops(nb * SEQ) * args.steps / (gemm8_ms * 1e-3) / 1e12, 1),
+                   "rel_rms_diff_vs_bf16_block": rel,
+                   "step_breakdown_ms": {k: round(v["ms"] / args.steps, 4) for k, v in sorted(tot8.items())},
+                   "kernels_per_step": block8.launches_per_forward,
+                   "note": "extra row: reduced precision, not comparable with `value`"}
+        del block8
+
     tokens = BATCH * SEQ
     totals = timer.totals()
     gemm_kinds = [k for k in totals if k.startswith("gemm")]          # plain, + swiglu, + residual epilogues
@@ -707,6 +742,8 @@ def run_ours(args, rank, world, local):
     line["gpu_launches"] = block.launches_per_forward * args.steps * world
     line["clocks"] = clocks.summary()
     line["parity"] = parity
+    if fp8_row is not None:
+        line["fp8_block"] = fp8_row
     if not args.skip_ops:
         line["ops"] = bench_ops(dev, rank, world, peaks, src, args.with_reference_kernels)
     if rank == 0 and world == 1:

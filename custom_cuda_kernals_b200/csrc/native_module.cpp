@@ -15,6 +15,7 @@
 #include <torch/extension.h>
 
 #include <sstream>
+#include <tuple>
 #include <string>
 #include <vector>
 
@@ -958,6 +959,116 @@ void fp8_quant_token_from_amax_fwd(const at::Tensor& x, const at::Tensor& row_am
                                                       static_cast<float*>(scale.data_ptr()), m, n, dt, fmt, l.stream));
 }
 
+// rmsnorm -> per-token FP8 quantisation in one pass
+void rmsnorm_fp8_quant_token_fwd(const at::Tensor& x, const at::Tensor& weight, const c10::optional<at::Tensor>& row_sumsq,
+                                 const c10::optional<at::Tensor>& y, const at::Tensor& x_fp8, const at::Tensor& scale,
+                                 double eps, const std::string& fp8_format) {
+    const int32_t dt = tag_of("x", x);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "'; expected float16 or bfloat16");
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    const int32_t fmt = parse_fp8_format(fp8_format);
+    if (tag_of("x_fp8", x_fp8) != fmt) value_error("dtype mismatch: x_fp8 must be the torch float8 type of fp8_format");
+    expect_f32("scale", tag_of("scale", scale));
+    if (x.dim() != 2 || x_fp8.sizes() != x.sizes())
+        value_error("shape mismatch: x and x_fp8 must be 2-D of the same shape; got x=" + shape_str(x) + ", x_fp8=" + shape_str(x_fp8));
+    const int64_t rows = x.size(0), cols = x.size(1);
+    if (weight.dim() != 1 || weight.size(0) != cols)
+        value_error("shape mismatch: weight shape " + shape_str(weight) + " must be [" + std::to_string(cols) + "]");
+    if (scale.numel() != rows) value_error("shape mismatch: scale must have " + std::to_string(rows) + " elements");
+    if (cols % 8 != 0) value_error("shape mismatch: cols must be a multiple of 8");
+    const bool has_ss = row_sumsq.has_value() && row_sumsq->defined();
+    const bool has_y = y.has_value() && y->defined();
+    if (has_ss) {
+        expect_f32("row_sumsq", tag_of("row_sumsq", *row_sumsq));
+        if (row_sumsq->dim() != 2 || row_sumsq->size(1) != rows || row_sumsq->size(0) < 1)
+            value_error("shape mismatch: row_sumsq shape " + shape_str(*row_sumsq) + " must be [n_tiles, " + std::to_string(rows) + "]");
+    }
+    if (has_y) {
+        expect_same_dtype("y", tag_of("y", *y), dt);
+        if (y->sizes() != x.sizes()) value_error("shape mismatch: y shape " + shape_str(*y) + " must match x's " + shape_str(x));
+    }
+    at::Tensor none;
+    Launch l(x, {&weight, &x_fp8, &scale, has_ss ? &*row_sumsq : &none, has_y ? &*y : &none});
+    check_launch("launch_rmsnorm_fp8_quant_token_fwd",
+                 launch_rmsnorm_fp8_quant_token_fwd(x.data_ptr(), weight.data_ptr(),
+                                                    has_ss ? static_cast<const float*>(row_sumsq->data_ptr()) : nullptr,
+                                                    has_ss ? row_sumsq->size(0) : 0, has_y ? y->data_ptr() : nullptr,
+                                                    static_cast<uint8_t*>(x_fp8.data_ptr()), static_cast<float*>(scale.data_ptr()),
+                                                    rows, cols, static_cast<float>(eps), dt, fmt, l.stream));
+}
+
+// shared checks of the FP8 GEMM entry points; returns (m, k, n)
+std::tuple<int64_t, int64_t, int64_t> check_fp8_operands(const at::Tensor& a, const at::Tensor& a_scale, const at::Tensor& w,
+                                                         const at::Tensor& w_scale) {
+    if (tag_of("a_fp8", a) != CCK_F8E4M3 || tag_of("w_fp8", w) != CCK_F8E4M3)
+        value_error("unsupported dtype 'a_fp8 and w_fp8 must be float8_e4m3fn'");
+    expect_f32("a_scale", tag_of("a_scale", a_scale));
+    expect_f32("w_scale", tag_of("w_scale", w_scale));
+    if (a.dim() != 2 || w.dim() != 2)
+        value_error("shape mismatch: a_fp8 and w_fp8 must be 2-D; got a_fp8=" + shape_str(a) + ", w_fp8=" + shape_str(w));
+    const int64_t m = a.size(0), k = a.size(1), n = w.size(0);
+    if (w.size(1) != k)
+        value_error("shape mismatch: w_fp8's in_features (" + std::to_string(w.size(1)) + ") must match a_fp8's last dim (" +
+                    std::to_string(k) + ")");
+    if (a_scale.numel() != m) value_error("shape mismatch: a_scale must have " + std::to_string(m) + " elements");
+    if (w_scale.numel() != n) value_error("shape mismatch: w_scale must have " + std::to_string(n) + " elements");
+    if (k % 16 != 0) value_error("shape mismatch: the fused FP8 GEMMs need K to be a multiple of 16, got " + std::to_string(k));
+    return {m, k, n};
+}
+
+void matmul_swiglu_fp8_fwd(const at::Tensor& a, const at::Tensor& a_scale, const at::Tensor& w_gate_up,
+                           const at::Tensor& w_scale, const at::Tensor& y, const c10::optional<at::Tensor>& row_amax) {
+    auto [m, k, f2] = check_fp8_operands(a, a_scale, w_gate_up, w_scale);
+    const int32_t odt = tag_of("y", y);
+    if (odt != CCK_BF16 && odt != CCK_F16) value_error("unsupported dtype 'y must be bfloat16 or float16'");
+    if (f2 % 256 != 0) value_error("shape mismatch: w_gate_up must have a multiple of 256 rows (128-feature gate/up blocks)");
+    const int64_t f = f2 / 2;
+    if (y.dim() != 2 || y.size(0) != m || y.size(1) != f)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " + std::to_string(f) + "]");
+    const bool has_amax = row_amax.has_value() && row_amax->defined();
+    if (has_amax) {
+        expect_f32("row_amax", tag_of("row_amax", *row_amax));
+        if (row_amax->dim() != 2 || row_amax->size(0) != f / 128 || row_amax->size(1) != m)
+            value_error("shape mismatch: row_amax shape " + shape_str(*row_amax) + " must be [" + std::to_string(f / 128) + ", " +
+                        std::to_string(m) + "]");
+    }
+    at::Tensor none;
+    Launch l(a, {&a_scale, &w_gate_up, &w_scale, &y, has_amax ? &*row_amax : &none});
+    check_launch("launch_matmul_swiglu_fp8_fwd",
+                 launch_matmul_swiglu_fp8_fwd(static_cast<const uint8_t*>(a.data_ptr()), static_cast<const float*>(a_scale.data_ptr()),
+                                              static_cast<const uint8_t*>(w_gate_up.data_ptr()),
+                                              static_cast<const float*>(w_scale.data_ptr()), y.data_ptr(),
+                                              has_amax ? static_cast<float*>(row_amax->data_ptr()) : nullptr, m, k, f, odt,
+                                              l.stream));
+}
+
+void matmul_add_bias_residual_fp8_fwd(const at::Tensor& a, const at::Tensor& a_scale, const at::Tensor& w,
+                                      const at::Tensor& w_scale, const c10::optional<at::Tensor>& bias,
+                                      const at::Tensor& residual, const at::Tensor& y) {
+    auto [m, k, n] = check_fp8_operands(a, a_scale, w, w_scale);
+    const int32_t odt = tag_of("y", y);
+    if (odt != CCK_BF16 && odt != CCK_F16) value_error("unsupported dtype 'y must be bfloat16 or float16'");
+    expect_same_dtype("residual", tag_of("residual", residual), odt);
+    const bool has_bias = bias.has_value() && bias->defined();
+    if (has_bias) expect_same_dtype("bias", tag_of("bias", *bias), odt);
+    if (y.dim() != 2 || y.size(0) != m || y.size(1) != n)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " + std::to_string(n) + "]");
+    if (residual.sizes() != y.sizes())
+        value_error("shape mismatch: residual shape " + shape_str(residual) + " must match y's " + shape_str(y));
+    if (has_bias && (bias->dim() != 1 || bias->size(0) != n))
+        value_error("shape mismatch: bias shape " + shape_str(*bias) + " must be [" + std::to_string(n) + "]");
+    at::Tensor none;
+    Launch l(a, {&a_scale, &w, &w_scale, &residual, &y, has_bias ? &*bias : &none});
+    check_launch("launch_matmul_add_bias_residual_fp8_fwd",
+                 launch_matmul_add_bias_residual_fp8_fwd(static_cast<const uint8_t*>(a.data_ptr()),
+                                                         static_cast<const float*>(a_scale.data_ptr()),
+                                                         static_cast<const uint8_t*>(w.data_ptr()),
+                                                         static_cast<const float*>(w_scale.data_ptr()),
+                                                         has_bias ? bias->data_ptr() : nullptr, residual.data_ptr(), y.data_ptr(),
+                                                         m, k, n, odt, l.stream));
+}
+
 // y = op(a) op(b)^T with operands read as stored (transposed or not); see launch_matmul_general_fwd
 void matmul_general_fwd(const at::Tensor& a, const at::Tensor& b, const at::Tensor& y, bool a_is_km, bool b_is_kn,
                         bool accumulate) {
@@ -1065,6 +1176,13 @@ PYBIND11_MODULE(_native, m) {
           py::arg("y"), py::arg("eps"));
     m.def("fp8_quant_token_from_amax_fwd", &fp8_quant_token_from_amax_fwd, py::arg("x"), py::arg("row_amax"),
           py::arg("x_fp8"), py::arg("scale"), py::arg("fp8_format"));
+    m.def("rmsnorm_fp8_quant_token_fwd", &rmsnorm_fp8_quant_token_fwd, py::arg("x"), py::arg("weight"),
+          py::arg("row_sumsq").none(true), py::arg("y").none(true), py::arg("x_fp8"), py::arg("scale"), py::arg("eps"),
+          py::arg("fp8_format"));
+    m.def("matmul_swiglu_fp8_fwd", &matmul_swiglu_fp8_fwd, py::arg("a_fp8"), py::arg("a_scale"), py::arg("w_gate_up"),
+          py::arg("w_scale"), py::arg("y"), py::arg("row_amax").none(true));
+    m.def("matmul_add_bias_residual_fp8_fwd", &matmul_add_bias_residual_fp8_fwd, py::arg("a_fp8"), py::arg("a_scale"),
+          py::arg("w_fp8"), py::arg("w_scale"), py::arg("bias").none(true), py::arg("residual"), py::arg("y"));
     m.def("matmul_general_fwd", &matmul_general_fwd, py::arg("a"), py::arg("b"), py::arg("y"), py::arg("a_is_km"),
           py::arg("b_is_kn"), py::arg("accumulate"));
     m.def("gemm_stat_tiles", [](int64_t n) { return cck_gemm_stat_tiles(n); }, py::arg("n"));

@@ -9,7 +9,8 @@ import torch
 from .. import _native
 
 __all__ = ["interleave_gate_up", "matmul_swiglu", "matmul_add_bias_residual", "matmul_add_bias_stats",
-           "rmsnorm_from_stats", "fp8_quant_token_from_amax", "matmul_general", "GATE_UP_BLOCK"]
+           "rmsnorm_from_stats", "fp8_quant_token_from_amax", "matmul_general", "rmsnorm_fp8_quant",
+           "matmul_swiglu_fp8", "matmul_add_bias_residual_fp8", "GATE_UP_BLOCK"]
 
 GATE_UP_BLOCK = 128
 
@@ -108,3 +109,45 @@ def matmul_general(a: torch.Tensor, b: torch.Tensor, a_transposed: bool = False,
         out = torch.empty((m, n), dtype=a.dtype, device=a.device)
     _native.matmul_general_fwd(a, b, out, a_transposed, b_transposed, accumulate)
     return out
+
+
+def _fp8_dtype(fp8_format: str) -> torch.dtype:
+    if fp8_format not in ("e4m3", "e5m2"):
+        raise ValueError(f"fp8_format must be 'e4m3' or 'e5m2', got {fp8_format!r}")
+    return torch.float8_e4m3fn if fp8_format == "e4m3" else torch.float8_e5m2
+
+
+def rmsnorm_fp8_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, fp8_format: str = "e4m3",
+                      row_sumsq: torch.Tensor | None = None, want_normed: bool = False):
+    """``fp8_quant(rmsnorm(x, weight, eps), fp8_format, "token")`` in one pass over ``x``: the
+    normalised row never goes to memory (unless ``want_normed`` asks for it too), so the norm that
+    feeds an FP8 projection costs 3 bytes of HBM traffic per element instead of 7.  Codes and
+    ``[M, 1]`` scales are bit-identical to the two-kernel chain.  ``row_sumsq`` (from
+    ``matmul_add_bias_stats``) replaces the row reduction, as in ``rmsnorm_from_stats``.
+    Returns ``(codes, scale)`` or ``(codes, scale, normed)``."""
+    codes = torch.empty(x.shape, dtype=_fp8_dtype(fp8_format), device=x.device)
+    scale = torch.empty((x.shape[0], 1), dtype=torch.float32, device=x.device)
+    y = torch.empty_like(x) if want_normed else None
+    _native.rmsnorm_fp8_quant_token_fwd(x, weight, row_sumsq, y, codes, scale, eps, fp8_format)
+    return (codes, scale, y) if want_normed else (codes, scale)
+
+
+def matmul_swiglu_fp8(a_fp8: torch.Tensor, a_scale: torch.Tensor, w_gate_up_fp8: torch.Tensor, w_scale: torch.Tensor,
+                      out_dtype: torch.dtype = torch.bfloat16, amax: bool = False):
+    """``matmul_swiglu`` with e4m3 operands: ``a_fp8 [M, K]`` with per-token scales, ``w_gate_up_fp8
+    [2F, K]`` = the per-row quantisation of ``interleave_gate_up(Wg, Wu)`` with its ``[2F]`` scales.
+    Equals ``swiglu(matmul_add_bias_fp8(a, Wg), matmul_add_bias_fp8(a, Wu))`` bit for bit.  With
+    ``amax`` also returns ``row_amax [F / 128, M]`` for ``fp8_quant_token_from_amax``."""
+    m, f = a_fp8.shape[0], w_gate_up_fp8.shape[0] // 2
+    y = torch.empty((m, f), dtype=out_dtype, device=a_fp8.device)
+    am = torch.empty((f // GATE_UP_BLOCK, m), dtype=torch.float32, device=a_fp8.device) if amax else None
+    _native.matmul_swiglu_fp8_fwd(a_fp8, a_scale, w_gate_up_fp8, w_scale, y, am)
+    return (y, am) if amax else y
+
+
+def matmul_add_bias_residual_fp8(a_fp8: torch.Tensor, a_scale: torch.Tensor, w_fp8: torch.Tensor, w_scale: torch.Tensor,
+                                 bias: torch.Tensor | None, residual: torch.Tensor) -> torch.Tensor:
+    """``matmul_add_bias_fp8(a, w, bias) + residual`` in one kernel (same roundings)."""
+    y = torch.empty((a_fp8.shape[0], w_fp8.shape[0]), dtype=residual.dtype, device=a_fp8.device)
+    _native.matmul_add_bias_residual_fp8_fwd(a_fp8, a_scale, w_fp8, w_scale, bias, residual, y)
+    return y

@@ -26,13 +26,15 @@ from typing import Callable
 import torch
 import torch.nn.functional as F
 
-from .kernels.fused import GATE_UP_BLOCK, interleave_gate_up, matmul_add_bias_residual, matmul_swiglu
-from .kernels.matmul_add_bias import matmul_add_bias
+from .kernels.fp8_quant import fp8_quant
+from .kernels.fused import (GATE_UP_BLOCK, fp8_quant_token_from_amax, interleave_gate_up, matmul_add_bias_residual,
+                            matmul_add_bias_residual_fp8, matmul_swiglu, matmul_swiglu_fp8, rmsnorm_fp8_quant)
+from .kernels.matmul_add_bias import matmul_add_bias, matmul_add_bias_fp8
 from .kernels.rmsnorm_residual import rmsnorm, rmsnorm_residual
 from .kernels.rope import rope, rope_strided
 from .kernels.swiglu import swiglu
 
-__all__ = ["LlamaBlock", "rope_tables", "OpTimer", "PARAM_NAMES"]
+__all__ = ["LlamaBlock", "LlamaBlockFP8", "rope_tables", "OpTimer", "PARAM_NAMES"]
 
 PARAM_NAMES = ("input_layernorm_weight", "post_attention_layernorm_weight", "q_proj", "k_proj", "v_proj",
                "o_proj", "gate_proj", "up_proj", "down_proj")
@@ -223,4 +225,90 @@ class LlamaBlock:
         shapes = [self.w[n].shape for n in ("o_proj", "down_proj")]
         shapes += ([self.w_gate_up.shape, self.w_qkv.shape] if self.fused else
                    [self.w[n].shape for n in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj")])
+        return sum(2 * tokens * o * i for o, i in shapes)
+
+
+class LlamaBlockFP8:
+    """The same decoder block with every projection on the FP8 tensor-core path (e4m3 operands,
+    fp32 accumulation): weights quantised once per output channel, activations per token on the
+    fly.  An addition - the reference's block and this library's ``LlamaBlock`` compute in
+    bfloat16 - for serving stacks that accept FP8 projections; the residual stream, RoPE, the
+    attention core and both norms' arithmetic stay in bfloat16 / fp32.  The quantisers are folded
+    into their neighbours so no activation makes an extra trip through HBM:
+
+        x --[rmsnorm + quant, one pass]--> qkv GEMM (fp8) --> rope, SDPA (bf16)
+          --[per-token quant]--> o_proj GEMM (fp8) + residual epilogue
+          --[rmsnorm + quant, one pass]--> gate-up GEMM (fp8) + SwiGLU epilogue, which also leaves
+            each row's maxima per 128 columns --[quant from those maxima]--> down GEMM (fp8) +
+            residual epilogue
+
+    ``fused=False`` runs the same arithmetic as separate kernels (norm, quantise, GEMM, swiglu,
+    add); the two give identical results."""
+
+    def __init__(self, weights: dict[str, torch.Tensor], n_heads: int = 32, n_kv_heads: int = 8, eps: float = 1e-5,
+                 theta: float = 500000.0, max_seq_len: int = 2048, fused: bool = True):
+        missing = [n for n in PARAM_NAMES if n not in weights]
+        if missing:
+            raise ValueError(f"missing block parameters: {missing}")
+        for name in PARAM_NAMES:
+            if not weights[name].is_cuda or not weights[name].is_contiguous():
+                raise ValueError(f"parameter '{name}' must be a contiguous CUDA tensor")
+        self.hidden = weights["q_proj"].shape[1]
+        self.n_heads, self.n_kv_heads = n_heads, n_kv_heads
+        self.head_dim = weights["q_proj"].shape[0] // n_heads
+        self.eps, self.fused = eps, fused
+        self.device = weights["q_proj"].device
+        self.ffn = weights["gate_proj"].shape[0]
+        if self.ffn % GATE_UP_BLOCK or self.hidden % 16 or self.ffn % 16:
+            raise ValueError("the FP8 block needs hidden and FFN sizes that are multiples of 16 (FFN of 128)")
+        self.cos, self.sin = rope_tables(max_seq_len, self.head_dim, theta, self.device)
+        self.w_in, self.w_post = weights["input_layernorm_weight"], weights["post_attention_layernorm_weight"]
+        self.q_cols, self.kv_cols = weights["q_proj"].shape[0], weights["k_proj"].shape[0]
+        quant = lambda w: fp8_quant(w.contiguous(), "e4m3", "token")            # one scale per output channel
+        self.qkv = quant(torch.cat([weights["q_proj"], weights["k_proj"], weights["v_proj"]], dim=0))
+        self.o = quant(weights["o_proj"])
+        self.gate_up = quant(interleave_gate_up(weights["gate_proj"], weights["up_proj"]))
+        self.gate, self.up = quant(weights["gate_proj"]), quant(weights["up_proj"])
+        self.down = quant(weights["down_proj"])
+        if fused:
+            del self.gate, self.up
+        #: this library's kernels per forward: 2 norm+quant, 2 quantisers, rope, 4 GEMMs
+        self.launches_per_forward = 9 if fused else 15
+
+    def forward(self, x: torch.Tensor, timer: OpTimer | None = None) -> torch.Tensor:
+        t = timer if timer is not None else _NoTimer
+        b, s, hid = x.shape
+        x2 = x.view(b * s, hid)
+        if self.fused:
+            h8, hs = t.run("rmsnorm_quant", rmsnorm_fp8_quant, x2, self.w_in, self.eps)
+        else:
+            h8, hs = fp8_quant(rmsnorm(x2, self.w_in, self.eps), "e4m3", "token")
+        qkv = t.run("gemm_fp8", matmul_add_bias_fp8, h8, hs, *self.qkv).view(b, s, -1)
+        qc, kc = self.q_cols, self.kv_cols
+        q = qkv[..., :qc].unflatten(-1, (self.n_heads, self.head_dim))
+        k = qkv[..., qc:qc + kc].unflatten(-1, (self.n_kv_heads, self.head_dim))
+        v = qkv[..., qc + kc:].unflatten(-1, (self.n_kv_heads, self.head_dim))
+        q, k = t.run("rope", rope_strided, q, k, self.cos[:s], self.sin[:s])
+        att = t.run("sdpa", F.scaled_dot_product_attention, q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                    is_causal=True, enable_gqa=self.n_heads != self.n_kv_heads)
+        att = att.transpose(1, 2).contiguous().view(b * s, hid)
+        a8, a_s = t.run("quant", fp8_quant, att, "e4m3", "token")
+        if self.fused:
+            res2 = t.run("gemm_fp8_residual", matmul_add_bias_residual_fp8, a8, a_s, *self.o, None, x2)
+            h28, h2s = t.run("rmsnorm_quant", rmsnorm_fp8_quant, res2, self.w_post, self.eps)
+            act, amax = t.run("gemm_fp8_swiglu", matmul_swiglu_fp8, h28, h2s, *self.gate_up, amax=True)
+            act8, act_s = t.run("quant", fp8_quant_token_from_amax, act, amax)
+            out = t.run("gemm_fp8_residual", matmul_add_bias_residual_fp8, act8, act_s, *self.down, None, res2)
+        else:
+            res2 = matmul_add_bias_fp8(a8, a_s, *self.o) + x2
+            h28, h2s = fp8_quant(rmsnorm(res2, self.w_post, self.eps), "e4m3", "token")
+            act = swiglu(matmul_add_bias_fp8(h28, h2s, *self.gate), matmul_add_bias_fp8(h28, h2s, *self.up))
+            act8, act_s = fp8_quant(act, "e4m3", "token")
+            out = matmul_add_bias_fp8(act8, act_s, *self.down) + res2
+        return out.view(b, s, hid)
+
+    __call__ = forward
+
+    def gemm_flops(self, tokens: int) -> int:
+        shapes = [self.qkv[0].shape, self.o[0].shape, self.gate_up[0].shape, self.down[0].shape]
         return sum(2 * tokens * o * i for o, i in shapes)

@@ -287,6 +287,33 @@ int32_t launch_fp8_quant_token_from_amax_fwd(const void* x, const float* row_ama
                                              float* scale, int64_t m, int64_t n, int32_t dtype, int32_t fp8_format,
                                              void* stream);
 
+/* x_fp8, scale = launch_fp8_quant_token_fwd(launch_rmsnorm_fwd(x, weight, eps)), bit for bit, in ONE
+ * pass over x: the normalised row stays in registers between the norm and the quantiser (3 bytes of
+ * HBM traffic per element instead of 7).  row_sumsq, when not NULL, holds n_tiles partial sums of
+ * squares per row ([n_tiles, rows], from launch_matmul_add_bias_stats_fwd) and replaces the row
+ * reduction.  y, when not NULL, also receives the normalised rows.  float16/bfloat16, cols a multiple
+ * of 8 and at most 65536, 16-byte aligned x, weight, y, 8-byte aligned x_fp8; otherwise
+ * cudaErrorInvalidValue.  The norm -> projection step of the reference's block
+ * (examples/llama_block.py:161-163,168-170) for FP8 projections; no reference counterpart. */
+int32_t launch_rmsnorm_fp8_quant_token_fwd(const void* x, const void* weight, const float* row_sumsq, int64_t n_tiles,
+                                           void* y, uint8_t* x_fp8, float* scale, int64_t rows, int64_t cols,
+                                           float eps, int32_t dtype, int32_t fp8_format, void* stream);
+
+/* FP8 forms of launch_matmul_swiglu_fwd and launch_matmul_add_bias_residual_fwd: e4m3 codes with one
+ * float32 scale per row of each operand (as launch_fp8_quant_token_fwd produces; the weight's scales
+ * are per output channel).  Results equal, bit for bit, launch_matmul_add_bias_fp8_fwd followed by
+ * launch_swiglu_fwd / the residual add.  w_gate_up [2 f, k] and w_scale [2 f] are in the interleaved
+ * row order of launch_matmul_swiglu_fwd; row_amax [f / 128, m] (or NULL) receives each row's largest
+ * stored magnitude per 128 output columns, for launch_fp8_quant_token_from_amax_fwd.  k % 16 == 0,
+ * f % 128 == 0, 16-byte aligned codes; out_dtype CCK_BF16 or CCK_F16; otherwise
+ * cudaErrorInvalidValue.  No reference counterpart. */
+int32_t launch_matmul_swiglu_fp8_fwd(const uint8_t* a_codes, const float* a_scale, const uint8_t* w_gate_up,
+                                     const float* w_scale, void* y, float* row_amax, int64_t m, int64_t k, int64_t f,
+                                     int32_t out_dtype, void* stream);
+int32_t launch_matmul_add_bias_residual_fp8_fwd(const uint8_t* a_codes, const float* a_scale, const uint8_t* w_codes,
+                                                const float* w_scale, const void* bias, const void* residual, void* y,
+                                                int64_t m, int64_t k, int64_t n, int32_t out_dtype, void* stream);
+
 /* y[m, n] = A B^T on the tensor cores with either operand read as stored: A [m, k] (a_is_km = 0) or
  * its transpose [k, m] (a_is_km = 1); B [n, k] (b_is_kn = 0, the reference's weight layout,
  * custom_cuda/kernels/matmul_add_bias.py:16-26) or its transpose [k, n] (b_is_kn = 1).  The

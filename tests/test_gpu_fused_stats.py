@@ -123,3 +123,66 @@ def test_stats_entry_points_reject_bad_arguments():
     bad = torch.empty(2, 64, device=DEV)
     with pytest.raises(ValueError, match="row_sumsq shape"):
         _native.matmul_add_bias_stats_fwd(x, w, None, None, torch.empty_like(y), bad, None)
+
+
+@pytest.mark.parametrize("rows,cols", [(300, 1024), (64, 4096), (7, 8), (100, 264), (16, 8192), (3, 32768 + 8)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+def test_rmsnorm_fp8_quant_equals_the_two_kernel_chain(rows, cols, dtype, fmt):
+    """norm + per-token quantiser in one pass == fp8_quant(rmsnorm(x)) bit for bit (codes, scales and
+    the optional normalised output), also when the sums of squares come from a GEMM epilogue."""
+    from custom_cuda.kernels.fp8_quant import fp8_quant
+    from custom_cuda_kernals_b200.kernels.fused import matmul_add_bias_stats, rmsnorm_fp8_quant, rmsnorm_from_stats
+    from custom_cuda_kernals_b200.kernels.rmsnorm_residual import rmsnorm
+    g = torch.Generator(device=DEV).manual_seed(rows + cols)
+    x = torch.randn(rows, cols, device=DEV, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(cols, device=DEV, generator=g)).to(dtype)
+    normed = rmsnorm(x, w, 1e-5)
+    want_codes, want_scale = fp8_quant(normed, fmt, "token")
+    codes, scale, y = rmsnorm_fp8_quant(x, w, 1e-5, fmt, want_normed=True)
+    assert torch.equal(y, normed)
+    assert torch.equal(codes.view(torch.uint8), want_codes.view(torch.uint8)) and torch.equal(scale, want_scale)
+    c2, s2 = rmsnorm_fp8_quant(x, w, 1e-5, fmt)
+    assert torch.equal(c2.view(torch.uint8), codes.view(torch.uint8)) and torch.equal(s2, scale)
+    if cols <= 4096:      # sums of squares from the producing GEMM's epilogue
+        a = torch.randn(rows, 64, device=DEV, generator=g).to(dtype)
+        wt = (0.125 * torch.randn(cols, 64, device=DEV, generator=g)).to(dtype)
+        out, ss, _ = matmul_add_bias_stats(a, wt)
+        c3, s3 = rmsnorm_fp8_quant(out, w, 1e-5, fmt, row_sumsq=ss)
+        w3, ws3 = fp8_quant(rmsnorm_from_stats(out, ss, w, 1e-5), fmt, "token")
+        assert torch.equal(c3.view(torch.uint8), w3.view(torch.uint8)) and torch.equal(s3, ws3)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 1024, 1408), (130, 64, 384), (4096, 4096, 2048)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fp8_fused_epilogues_equal_the_unfused_chains(shape, dtype):
+    """FP8 gate-up GEMM + SwiGLU (+ row maxima) and FP8 GEMM + residual against
+    matmul_add_bias_fp8 -> swiglu / add, bit for bit; the maxima reproduce fp8_quant(act)."""
+    from custom_cuda.kernels.fp8_quant import fp8_quant
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias_fp8
+    from custom_cuda.kernels.swiglu import swiglu
+    from custom_cuda_kernals_b200.kernels.fused import (fp8_quant_token_from_amax, interleave_gate_up,
+                                                        matmul_add_bias_residual_fp8, matmul_swiglu_fp8)
+    m, k, f = shape
+    g = torch.Generator(device=DEV).manual_seed(m + f)
+    x = torch.randn(m, k, device=DEV, generator=g).to(dtype)
+    wg = (k ** -0.5 * torch.randn(f, k, device=DEV, generator=g)).to(dtype)
+    wu = (k ** -0.5 * torch.randn(f, k, device=DEV, generator=g)).to(dtype)
+    x8, xs = fp8_quant(x, "e4m3", "token")
+    wg8, wgs = fp8_quant(wg, "e4m3", "token")
+    wu8, wus = fp8_quant(wu, "e4m3", "token")
+    wgu8, wgus = fp8_quant(interleave_gate_up(wg, wu), "e4m3", "token")
+    want = swiglu(matmul_add_bias_fp8(x8, xs, wg8, wgs, None, dtype), matmul_add_bias_fp8(x8, xs, wu8, wus, None, dtype))
+    act, amax = matmul_swiglu_fp8(x8, xs, wgu8, wgus, dtype, amax=True)
+    assert torch.equal(act, want)
+    assert torch.equal(matmul_swiglu_fp8(x8, xs, wgu8, wgus, dtype), want)
+    c, s = fp8_quant_token_from_amax(act, amax)
+    cw, sw = fp8_quant(act, "e4m3", "token")
+    assert torch.equal(c.view(torch.uint8), cw.view(torch.uint8)) and torch.equal(s, sw)
+    # GEMM + bias + residual
+    b = (0.1 * torch.randn(f, device=DEV, generator=g)).to(dtype)
+    r = torch.randn(m, f, device=DEV, generator=g).to(dtype)
+    for bias in (b, None):
+        got = matmul_add_bias_residual_fp8(x8, xs, wg8, wgs, bias, r)
+        assert torch.equal(got, matmul_add_bias_fp8(x8, xs, wg8, wgs, bias, dtype) + r)
+    assert device_status_clean(act)
