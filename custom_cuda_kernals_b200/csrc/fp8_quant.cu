@@ -33,6 +33,7 @@ namespace cck {
 namespace {
 
 constexpr float kScaleFloor = 1e-12f;
+constexpr int kMaxStatTiles = 1024;   // partial statistics per row a consumer kernel accepts
 constexpr int kTile = 128;
 
 template <bool E5M2> struct Fmt;
@@ -193,14 +194,16 @@ fp8_token_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes, float* __
 }
 
 // The same quantiser for rows whose largest magnitude already exists as `n_tiles` partial maxima
-// per row ([n_tiles][rows], written by the producing GEMM's epilogue): no reduction, no barrier.
-// A maximum does not depend on the order it is taken in, so codes and scales are bit for bit
-// those of fp8_token_kernel.
+// per row ([n_tiles][rows], written by the producing GEMM's epilogue): the row itself is not
+// scanned, the threads share the loads of the partials and one CTA-wide maximum finishes.  A
+// maximum does not depend on the order it is taken in, so codes and scales are bit for bit those
+// of fp8_token_kernel.
 template <typename T, bool E5M2, int VPT>
 __global__ void __launch_bounds__(1024)
 fp8_token_from_amax_kernel(const T* __restrict__ x, const float* __restrict__ amax, int n_tiles, int64_t rows,
                            uint8_t* __restrict__ codes, float* __restrict__ scale, int64_t n, int n_vec) {
     constexpr int kPer = Store<T>::kPerVec;
+    __shared__ float slots[32];
     const int64_t row = blockIdx.x;
     const T* xr = x + row * n;
     uint8_t* cr = codes + row * n;
@@ -210,15 +213,28 @@ fp8_token_from_amax_kernel(const T* __restrict__ x, const float* __restrict__ am
         const int i = threadIdx.x + j * blockDim.x;
         if (i < n_vec) v[j] = ld_stream(xr + static_cast<int64_t>(i) * kPer);
     }
+    // the row's partial maxima, spread over the threads (one load each where n_tiles <= CTA width)
     float m = 0.0f;
-    for (int t = 0; t < n_tiles; ++t) m = fmaxf(m, amax[static_cast<int64_t>(t) * rows + row]);
-    const float sc = scale_of<E5M2>(m);
+    for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) m = fmaxf(m, amax[static_cast<int64_t>(t) * rows + row]);
+    const float sc = scale_of<E5M2>(cta_max_dyn(m, slots));
     if (threadIdx.x == 0) scale[row] = sc;
     const ExactDiv div = ExactDiv::make(sc);
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < n_vec) Chunk<T>::template quantise_store<E5M2>(v[j], div, cr + static_cast<int64_t>(i) * kPer);
+    }
+}
+
+// packed product of two pairs of 16-bit values, each rounded once to the storage type
+template <typename T>
+__device__ __forceinline__ uint32_t mul2_16(uint32_t a, uint32_t b) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    } else {
+        const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
     }
 }
 
@@ -247,8 +263,12 @@ rmsnorm_fp8_token_kernel(const T* __restrict__ x, const T* __restrict__ w, const
     }
     float total;
     if (sumsq != nullptr) {
+        // partials fetched once per CTA into shared memory, then added in tile order by every thread
+        __shared__ float part[kMaxStatTiles];
+        for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) part[t] = sumsq[static_cast<int64_t>(t) * rows + row];
+        __syncthreads();
         total = 0.0f;
-        for (int t = 0; t < n_tiles; ++t) total += sumsq[static_cast<int64_t>(t) * rows + row];
+        for (int t = 0; t < n_tiles; ++t) total += part[t];
     } else {
         float sq = 0.0f;
 #pragma unroll
@@ -278,12 +298,15 @@ rmsnorm_fp8_token_kernel(const T* __restrict__ x, const T* __restrict__ w, const
     for (int j = 0; j < VPT; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < n_vec) {
-            float a[kPer], g[kPer];
-            unpack<T>(v[j], a);
-            unpack<T>(ld_cached(w16 + i), g);
+            // round(x * inv) to the storage type, times weight in the storage type: two elements per
+            // instruction - one packed conversion, one packed multiply (the product of two 16-bit
+            // values is exact in fp32, so a packed multiply rounds exactly as multiply-then-convert)
+            const Vec16 g = ld_cached(w16 + i);
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) a[e] = Store<T>::round(a[e] * inv) * g[e];
-            v[j] = pack<T>(a);                          // the normalised row, rounded to the storage type
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t n2 = Store<T>::pack2(Store<T>::get(v[j], 2 * q) * inv, Store<T>::get(v[j], 2 * q + 1) * inv);
+                v[j].w[q] = mul2_16<T>(n2, g.w[q]);
+            }
             if (y != nullptr) st_stream(reinterpret_cast<Vec16*>(y) + row * n_vec + i, v[j]);
             m = fmaxf(m, Chunk<T>::amax(v[j]));
         }
@@ -510,7 +533,7 @@ cudaError_t run_rmsnorm_fp8(const void* x, const void* w, const float* sumsq, in
     const int64_t n_vec = cols / kPer;
     if (rows > 0x7fffffffLL || cols % kPer != 0 || n_vec > 8 * 1024 || !aligned16(x) || !aligned16(w) ||
         (y != nullptr && !aligned16(y)) || (reinterpret_cast<uintptr_t>(codes) % kPer) != 0 ||
-        (sumsq != nullptr && (n_tiles <= 0 || n_tiles > 4096)))
+        (sumsq != nullptr && (n_tiles <= 0 || n_tiles > kMaxStatTiles)))
         return cudaErrorInvalidValue;
     const int vpt = n_vec <= 4 * 1024 ? 4 : 8;         // the CTA shape of rmsnorm_rowreg_kernel
     int threads = static_cast<int>(ceil_div64(ceil_div64(n_vec, vpt), 32) * 32);

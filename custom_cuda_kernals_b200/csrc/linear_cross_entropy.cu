@@ -102,11 +102,16 @@ struct EpiLceT {
             const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
             if (row < p.n_rows) {
                 float* out = p.logits + row * p.v_count + col0;
-                if (valid == 32) {
+                if (valid == 32) {       // written once, read once by the gradient pass: keep it out of the way in L2
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        *reinterpret_cast<float4*>(out + 4 * q) =
-                            make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+                    for (int q = 0; q < 8; ++q) {
+                        Vec16 o;
+                        o.w[0] = __float_as_uint(acc[4 * q]);
+                        o.w[1] = __float_as_uint(acc[4 * q + 1]);
+                        o.w[2] = __float_as_uint(acc[4 * q + 2]);
+                        o.w[3] = __float_as_uint(acc[4 * q + 3]);
+                        st_stream(out + 4 * q, o);
+                    }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)

@@ -155,7 +155,7 @@ cudaError_t gemm_tc(const void* x, const void* w, const void* bias, void* y, int
     const int64_t wide_tiles = static_cast<int64_t>(m_tiles) * n_tiles;
     if (wide_tiles <= sm_count() / 2 && narrow_tiles_enabled()) {
         const int n_narrow = static_cast<int>(ceil_div64(n, kNarrow));
-        const int splits = splitk_enabled() ? splitk_factor(static_cast<int64_t>(m_tiles) * n_narrow,
+        const int splits = splitk_enabled(m) ? splitk_factor(static_cast<int64_t>(m_tiles) * n_narrow,
                                                             static_cast<int>(ceil_div64(k, 64))) : 1;
         if (splits > 1 || wide_tiles <= sm_count() / 4) {
             e = make_tmap(&tb, dt, 2, w, n, k, kNarrow);

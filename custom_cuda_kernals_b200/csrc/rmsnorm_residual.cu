@@ -98,9 +98,11 @@ rmsnorm_rowreg_kernel(const T* __restrict__ x, const T* __restrict__ res, const 
 }
 
 // The norm of a row whose sum of squares already exists as `n_tiles` partial sums (written by the
-// producing GEMM's epilogue, [n_tiles][rows]): no reduction, no barrier.  Each thread issues its
-// VPT 16-byte loads of the row up front, adds the partials in tile order while they fly (the same
-// fp32 additions in every thread, so all threads hold the same factor) and scales its vectors.
+// producing GEMM's epilogue, [n_tiles][rows]): the row is not reduced.  Each thread issues its VPT
+// 16-byte loads of the row up front; meanwhile the CTA fetches the partials once into shared
+// memory and every thread adds them in tile order (the same fp32 additions in every thread, so
+// all hold the same factor), then scales its vectors.
+constexpr int kMaxStatTiles = 1024;
 template <typename T, int VPT>
 __global__ void __launch_bounds__(1024)
 rmsnorm_from_stats_kernel(const T* __restrict__ x, const float* __restrict__ sumsq, int n_tiles, int64_t rows,
@@ -116,8 +118,12 @@ rmsnorm_from_stats_kernel(const T* __restrict__ x, const float* __restrict__ sum
         const int i = threadIdx.x + j * blockDim.x;
         if (i < n_vec) xv[j] = ld_stream(x16 + i);
     }
+    // partials fetched once per CTA into shared memory, then added in tile order by every thread
+    __shared__ float part[kMaxStatTiles];
+    for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) part[t] = sumsq[static_cast<int64_t>(t) * rows + row];
+    __syncthreads();
     float total = 0.0f;
-    for (int t = 0; t < n_tiles; ++t) total += sumsq[static_cast<int64_t>(t) * rows + row];
+    for (int t = 0; t < n_tiles; ++t) total += part[t];
     const float inv = 1.0f / sqrtf(total / static_cast<float>(cols) + eps);
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
@@ -137,7 +143,7 @@ template <typename T>
 cudaError_t run_from_stats(const void* x, const float* sumsq, int64_t n_tiles, const void* w, void* y, int64_t rows,
                            int64_t cols, float eps, cudaStream_t stream) {
     constexpr int kPer = Store<T>::kPerVec;
-    if (rows > 0x7fffffffLL || n_tiles <= 0 || n_tiles > 4096 || sumsq == nullptr) return cudaErrorInvalidValue;
+    if (rows > 0x7fffffffLL || n_tiles <= 0 || n_tiles > kMaxStatTiles || sumsq == nullptr) return cudaErrorInvalidValue;
     const int64_t n_vec = cols / kPer;
     if (cols % kPer != 0 || n_vec > 8 * 1024 || !aligned16(x) || !aligned16(w) || !aligned16(y))
         return cudaErrorInvalidValue;

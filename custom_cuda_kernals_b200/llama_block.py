@@ -34,7 +34,8 @@ from .kernels.rmsnorm_residual import rmsnorm, rmsnorm_residual
 from .kernels.rope import rope, rope_strided
 from .kernels.swiglu import swiglu
 
-__all__ = ["LlamaBlock", "LlamaBlockFP8", "rope_tables", "OpTimer", "PARAM_NAMES"]
+__all__ = ["LlamaBlock", "LlamaBlockFP8", "rope_tables", "OpTimer", "PARAM_NAMES", "host_pipeline_groups",
+           "host_pipeline_items"]
 
 PARAM_NAMES = ("input_layernorm_weight", "post_attention_layernorm_weight", "q_proj", "k_proj", "v_proj",
                "o_proj", "gate_proj", "up_proj", "down_proj")
@@ -101,6 +102,56 @@ def host_pipeline_groups(batch: int, chunks: int | None = None) -> list[tuple[in
     return [g for g in groups if g[1] > g[0]]
 
 
+_LOWER_RIGHT_OK = True
+
+
+def _continuation_attention(q, k, v, gqa: bool):
+    """Attention of ``L`` new queries over ``S >= L`` keys whose last ``L`` are the queries' own
+    positions: causal mask aligned bottom-right.  Uses torch's fused kernels through
+    ``causal_lower_right``; where this torch build has no fused kernel for that mask on the
+    device, an explicit boolean mask gives the same result (slower)."""
+    global _LOWER_RIGHT_OK
+    seq_q, seq_k = q.shape[-2], k.shape[-2]
+    if _LOWER_RIGHT_OK:
+        try:
+            from torch.nn.attention.bias import causal_lower_right
+            return F.scaled_dot_product_attention(q, k, v, attn_mask=causal_lower_right(seq_q, seq_k), enable_gqa=gqa)
+        except (RuntimeError, TypeError, ValueError):
+            _LOWER_RIGHT_OK = False
+    mask = torch.ones(seq_q, seq_k, dtype=torch.bool, device=q.device).tril(diagonal=seq_k - seq_q)
+    return F.scaled_dot_product_attention(q, k, v, attn_mask=mask, enable_gqa=gqa)
+
+
+def host_pipeline_items(batch: int, seq: int, chunks: int | None = None, seq_pieces: int | None = None,
+                        min_piece: int = 512) -> list[tuple[int, int, int, int]]:
+    """Work items ``(b0, b1, s0, s1)`` of the host pipeline: sequences ``[b0, b1)``, positions
+    ``[s0, s1)``, in execution order.  The groups of ``host_pipeline_groups``; the first and the
+    last group, when they are one sequence, are cut into ``seq_pieces`` equal runs of positions, so
+    that only the first piece's copy-in and the last piece's copy-out stay exposed.  With at most
+    three sequences every group is a single sequence and every one is cut.
+
+    Default: two pieces when the call holds ONE sequence (one sequence per rank, where nothing
+    else can overlap the copies), none otherwise.  Measured on one B200 (PCIe uncontended), 2048
+    tokens: 1 sequence 1.39 ms whole, 1.35 ms in 2 pieces, 1.71 ms in 4; 2 sequences 2.19 / 2.41 /
+    3.29 ms; 8 sequences 6.73 / 6.91 / 8.00 ms - a piece of 512 tokens runs ten launches whose
+    host-side cost (~0.3 ms) exceeds their device time, so finer cuts turn the pipeline
+    launch-bound.  Eight ranks sharing the host's PCIe root stretch the copies, which favours the
+    cut at one sequence per rank."""
+    groups = host_pipeline_groups(batch, chunks)
+    if seq_pieces is None:
+        seq_pieces = 2 if (batch == 1 and seq >= 2 * min_piece) else 1
+    seq_pieces = max(1, min(seq_pieces, seq))
+    items = []
+    for i, (b0, b1) in enumerate(groups):
+        ends = i == 0 or i == len(groups) - 1 or batch <= 3
+        if seq_pieces > 1 and b1 - b0 == 1 and ends and chunks is None:
+            cuts = [seq * j // seq_pieces for j in range(seq_pieces + 1)]
+            items += [(b0, b1, lo, hi) for lo, hi in zip(cuts[:-1], cuts[1:]) if hi > lo]
+        else:
+            items.append((b0, b1, 0, seq))
+    return items
+
+
 class LlamaBlock:
     """One decoder block; ``weights`` maps PARAM_NAMES to CUDA tensors
     (projections as ``[out_features, in_features]``, the nn.Linear layout)."""
@@ -136,10 +187,18 @@ class LlamaBlock:
         #: qkv + o + gate-up-swiglu + down-residual (fused: 7 in all)
         self.launches_per_forward = 7 if self.fused else 11
 
-    def forward(self, x: torch.Tensor, timer: OpTimer | None = None, pos_offset: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, timer: OpTimer | None = None, pos_offset: int = 0,
+                kv_cache: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
         """x ``[B, S, hidden]`` -> ``[B, S, hidden]``.  ``pos_offset`` shifts the RoPE positions:
         ``x[:, i]`` is rotated as position ``pos_offset + i`` (attention stays causal within
-        the ``S`` tokens given)."""
+        the ``S`` tokens given).
+
+        With ``kv_cache = (k, v)``, two ``[B, max_len, n_kv_heads, head_dim]`` buffers that hold the
+        rotated keys and the values of positions ``0 .. pos_offset - 1`` of the same sequences, the
+        ``S`` tokens are a continuation: their keys / values are appended to the cache and they
+        attend causally to everything up to themselves.  Feeding a sequence piece by piece this
+        way computes the same function as one call on the whole sequence (every other op of the
+        block works on tokens independently)."""
         t = timer if timer is not None else _NoTimer
         w = self.w
         b, s, hid = x.shape
@@ -165,8 +224,23 @@ class LlamaBlock:
             k = t.run("gemm", matmul_add_bias, h, w["k_proj"]).view(b, s, self.n_kv_heads, self.head_dim)
             v = t.run("gemm", matmul_add_bias, h, w["v_proj"]).view(b, s, self.n_kv_heads, self.head_dim)
             q, k = t.run("rope", rope, q, k, cos, sin)
-        att = t.run("sdpa", F.scaled_dot_product_attention, q.transpose(1, 2), k.transpose(1, 2),
-                    v.transpose(1, 2), is_causal=True, enable_gqa=self.n_heads != self.n_kv_heads)
+        gqa = self.n_heads != self.n_kv_heads
+        if kv_cache is None:
+            att = t.run("sdpa", F.scaled_dot_product_attention, q.transpose(1, 2), k.transpose(1, 2),
+                        v.transpose(1, 2), is_causal=True, enable_gqa=gqa)
+        else:
+            k_all, v_all = kv_cache
+            end = pos_offset + s
+            if k_all.shape[0] != b or end > k_all.shape[1]:
+                raise ValueError(f"kv_cache of shape {tuple(k_all.shape)} cannot hold positions up to {end} of {b} sequences")
+            k_all[:, pos_offset:end].copy_(k)
+            v_all[:, pos_offset:end].copy_(v)
+            if pos_offset == 0:
+                att = t.run("sdpa", F.scaled_dot_product_attention, q.transpose(1, 2), k_all[:, :end].transpose(1, 2),
+                            v_all[:, :end].transpose(1, 2), is_causal=True, enable_gqa=gqa)
+            else:        # the new queries sit at the END of the key range: causal mask aligned bottom-right
+                att = t.run("sdpa", _continuation_attention, q.transpose(1, 2), k_all[:, :end].transpose(1, 2),
+                            v_all[:, :end].transpose(1, 2), gqa)
         att = t.run("copy", lambda a: a.transpose(1, 2).contiguous().view(b * s, hid), att)
         if self.fused:       # o_proj adds the residual in its epilogue; the norm reads that sum once
             res2 = t.run("gemm_residual", matmul_add_bias_residual, att, w["o_proj"], None, res)
@@ -187,36 +261,48 @@ class LlamaBlock:
 
     __call__ = forward
 
-    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunks: int | None = None) -> torch.Tensor:
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, chunks: int | None = None,
+                     seq_pieces: int | None = None) -> torch.Tensor:
         """Host-buffer entry point: ``x_host`` / ``out_host`` are pinned CPU tensors
-        ``[B, S, hidden]``.  The batch is cut into groups of whole sequences
-        (``host_pipeline_groups``) that flow through three streams - copy-in, compute (the
-        current stream) and copy-out - so the PCIe transfers of one group overlap the kernels
-        of another.  Returns ``out_host`` once every group has landed in it."""
+        ``[B, S, hidden]``.  The work is cut into items that flow through three streams - copy-in,
+        compute (the current stream) and copy-out - so the PCIe transfers of one item overlap the
+        kernels of another.  Items are groups of whole sequences (``host_pipeline_groups``); a
+        group that is a single sequence at either end of the schedule - the only places where a
+        copy cannot hide behind compute, and at one sequence per rank the whole job - is further
+        cut into ``seq_pieces`` runs of positions that are fed through ``forward(..., kv_cache=)``
+        one after the other (``host_pipeline_items``).  ``seq_pieces=1`` keeps sequences whole.
+        Returns ``out_host`` once every item has landed in it."""
         dev = self.device
-        b = x_host.shape[0]
+        b, seq = x_host.shape[0], x_host.shape[1]
         if not hasattr(self, "_copy_in"):
             self._copy_in, self._copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         compute = torch.cuda.current_stream(dev)
-        bounds = host_pipeline_groups(b, chunks)
+        items = host_pipeline_items(b, seq, chunks, seq_pieces if self.fused else 1)
         self._copy_in.wait_stream(compute)
         staged = []
         with torch.cuda.stream(self._copy_in):
-            for b0, b1 in bounds:
-                xd = x_host[b0:b1].to(dev, non_blocking=True)
+            for b0, b1, s0, s1 in items:
+                xd = x_host[b0:b1, s0:s1].to(dev, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self._copy_in)
                 staged.append((xd, ev))
-        for (b0, b1), (xd, ev) in zip(bounds, staged):
+        cache = None
+        for (b0, b1, s0, s1), (xd, ev) in zip(items, staged):
             compute.wait_event(ev)
             xd.record_stream(compute)
-            y = self.forward(xd)
+            if s0 == 0 and s1 == seq:
+                y = self.forward(xd)
+            else:
+                if s0 == 0:
+                    shape = (b1 - b0, seq, self.n_kv_heads, self.head_dim)
+                    cache = (torch.empty(shape, dtype=xd.dtype, device=dev), torch.empty(shape, dtype=xd.dtype, device=dev))
+                y = self.forward(xd, pos_offset=s0, kv_cache=cache)
             done = torch.cuda.Event()
             done.record(compute)
             self._copy_out.wait_event(done)
             y.record_stream(self._copy_out)
             with torch.cuda.stream(self._copy_out):
-                out_host[b0:b1].copy_(y, non_blocking=True)
+                out_host[b0:b1, s0:s1].copy_(y, non_blocking=True)
         self._copy_out.synchronize()
         return out_host
 

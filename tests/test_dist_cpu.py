@@ -228,3 +228,28 @@ def test_host_pipeline_groups_cover_the_batch_with_single_sequence_ends():
             assert groups[0] == (0, 1) and groups[-1] == (batch - 1, batch) and len(groups) <= 4
     assert host_pipeline_groups(8, 4) == [(0, 2), (2, 4), (4, 6), (6, 8)]
     assert host_pipeline_groups(3, 8) == [(0, 1), (1, 2), (2, 3)]
+
+
+def test_host_pipeline_items_cut_single_sequence_ends_into_position_pieces():
+    from custom_cuda_kernals_b200.llama_block import host_pipeline_items
+    for batch in range(0, 12):
+        for seq in (1, 300, 1024, 2048, 4096):
+            for pieces in (None, 1, 2, 4):
+                items = host_pipeline_items(batch, seq, seq_pieces=pieces)
+                covered = torch.zeros(batch, seq, dtype=torch.int32)
+                for b0, b1, s0, s1 in items:
+                    assert b1 > b0 and s1 > s0
+                    if (s0, s1) != (0, seq):
+                        assert b1 - b0 == 1                      # only single sequences are cut
+                    covered[b0:b1, s0:s1] += 1
+                assert torch.all(covered == 1)                   # every token exactly once
+                order = [(b0, s0) for b0, _, s0, _ in items]
+                assert order == sorted(order)                    # pieces of a sequence in position order
+    # default: one sequence per call is cut in two, everything else stays whole
+    assert host_pipeline_items(1, 2048) == [(0, 1, 0, 1024), (0, 1, 1024, 2048)]
+    assert host_pipeline_items(1, 512) == [(0, 1, 0, 512)]
+    assert host_pipeline_items(2, 2048) == [(0, 1, 0, 2048), (1, 2, 0, 2048)]
+    assert host_pipeline_items(8, 2048) == [(0, 1, 0, 2048), (1, 4, 0, 2048), (4, 7, 0, 2048), (7, 8, 0, 2048)]
+    assert host_pipeline_items(1, 2048, seq_pieces=4) == [(0, 1, 0, 512), (0, 1, 512, 1024), (0, 1, 1024, 1536), (0, 1, 1536, 2048)]
+    assert [i for i in host_pipeline_items(8, 2048, seq_pieces=4) if i[3] - i[2] == 2048] == [(1, 4, 0, 2048), (4, 7, 0, 2048)]
+    assert host_pipeline_items(8, 2048, chunks=4) == [(0, 2, 0, 2048), (2, 4, 0, 2048), (4, 6, 0, 2048), (6, 8, 0, 2048)]
