@@ -154,16 +154,20 @@ def timed_loop(fn, arg_sets, iters, warm=3, graph=False):
     current stream around `iters` back-to-back launches.  With graph=True the launches are
     captured into one CUDA graph and the replay is timed, which takes the Python and
     allocator overhead of each call (10-15 us, more than some of these kernels run) off the
-    device timeline."""
+    device timeline; inputs rotate through sets larger than the L2 and every launch writes
+    buffers of its own."""
     for i in range(warm):
         fn(*arg_sets[i % len(arg_sets)])
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if graph:
-        g = torch.cuda.CUDAGraph()
+        # every launch keeps its own output buffers for the life of the graph: were they freed at
+        # once, the capture's allocator would hand every launch the same address range and part of
+        # the write stream could stay in the 126 MB L2 instead of going to HBM
+        g, keep = torch.cuda.CUDAGraph(), []
         with torch.cuda.graph(g):
             for i in range(iters):
-                fn(*arg_sets[i % len(arg_sets)])
+                keep.append(fn(*arg_sets[i % len(arg_sets)]))
         g.replay()                      # one untimed replay
         torch.cuda.synchronize()
         a.record()
@@ -171,7 +175,7 @@ def timed_loop(fn, arg_sets, iters, warm=3, graph=False):
         b.record()
         torch.cuda.synchronize()
         secs = a.elapsed_time(b) * 1e-3 / iters
-        del g
+        del g, keep
         return secs
     a.record()
     for i in range(iters):
@@ -623,6 +627,7 @@ def run_ours(args, rank, world, local):
     # of the elements at 2048 tokens, so the budget is 7.5 %.
     parity = None
     if rank == 0:
+        torch.set_num_threads(os.cpu_count() or 1)     # torchrun pins OMP_NUM_THREADS=1; the other ranks wait for this
         w_cpu = {k: v.cpu() for k, v in weights.items()}
         xs = x_all[b0:b0 + 1]
         want = cpu_block_step(xs, w_cpu).float()
@@ -754,7 +759,8 @@ def run_ours(args, rank, world, local):
     line["e2e"] = {"value": tokens * args.steps / e2e_secs, "unit": UNIT,
                    "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": out_host.numel() * 2 * world,
                    "ms_per_step": e2e_secs / args.steps * 1e3,
-                   "api": "LlamaBlock.forward_host(pinned x, pinned out): H2D, 7 library kernels + SDPA per group of sequences, D2H; groups pipelined over 3 streams"}
+                   "api": "LlamaBlock.forward_host(pinned x, pinned out): H2D, 7 library kernels + SDPA per group of sequences, D2H; groups "
+                          "pipelined over 3 streams (a lone sequence per rank is cut into two runs of positions fed through a KV cache)"}
     line["gpu_launches"] = block.launches_per_forward * args.steps * world
     line["clocks"] = clocks.summary()
     line["parity"] = parity
