@@ -91,8 +91,8 @@ moe_router_kernel(const T* __restrict__ logits, float* __restrict__ topk_w, int6
     if constexpr (L == 32 && sizeof(T) == 2) {
         // 16-bit logits, whole warp per token: value and expert id fit one 32-bit key - the value's
         // bits made order-preserving in the high half, 255 - expert in the low byte, so that a
-        // plain unsigned max picks the largest logit and, among equals, the lowest expert.  A
-        // round is then 7 max ops, one redux.sync and 8 compare-and-clear ops; keys are unique.
+        // plain unsigned max picks the largest logit and, among equals, the lowest expert; keys
+        // are unique.
         uint32_t key[kRouterVals];
 #pragma unroll
         for (int i = 0; i < kRouterVals; ++i) {
@@ -101,13 +101,30 @@ moe_router_kernel(const T* __restrict__ logits, float* __restrict__ topk_w, int6
             const uint32_t ord = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
             key[i] = e < experts ? ((ord << 16) | static_cast<uint32_t>(255 - e)) : 0u;
         }
+        // Each lane first sorts its eight keys (19 compare-exchanges); a round is then ONE
+        // redux.sync over the lanes' current heads, and the lane that owned the winner moves its
+        // list up by one - 10 instructions a round where scanning the eight keys took 24.
+#define CCK_CE(a, b)                                         \
+    {                                                        \
+        const uint32_t hi = max(key[a], key[b]);             \
+        key[b] = min(key[a], key[b]);                        \
+        key[a] = hi;                                         \
+    }
+        CCK_CE(0, 1) CCK_CE(2, 3) CCK_CE(4, 5) CCK_CE(6, 7)
+        CCK_CE(0, 2) CCK_CE(1, 3) CCK_CE(4, 6) CCK_CE(5, 7)
+        CCK_CE(1, 2) CCK_CE(5, 6) CCK_CE(0, 4) CCK_CE(3, 7)
+        CCK_CE(1, 5) CCK_CE(2, 6)
+        CCK_CE(1, 4) CCK_CE(3, 6)
+        CCK_CE(2, 4) CCK_CE(3, 5)
+        CCK_CE(3, 4)
+#undef CCK_CE
         for (int j = 0; j < k; ++j) {
-            uint32_t local = key[0];
+            const uint32_t top = __reduce_max_sync(0xffffffffu, key[0]);
+            if (key[0] == top) {                 // keys are unique: exactly one lane
 #pragma unroll
-            for (int i = 1; i < kRouterVals; ++i) local = max(local, key[i]);
-            const uint32_t top = __reduce_max_sync(0xffffffffu, local);
-#pragma unroll
-            for (int i = 0; i < kRouterVals; ++i) key[i] = key[i] == top ? 0u : key[i];
+                for (int i = 0; i + 1 < kRouterVals; ++i) key[i] = key[i + 1];
+                key[kRouterVals - 1] = 0u;
+            }
             const uint32_t ord = top >> 16;
             const float best = Bits16<T>::to_float((ord & 0x8000u) ? (ord & 0x7fffu) : (~ord & 0xffffu));
             const float p = __expf(best - mx) * inv_sum;
@@ -328,6 +345,49 @@ token_combine_vec_kernel(const T* __restrict__ expert_out, const int64_t* __rest
     }
 }
 
+// Few choices per token (k <= 4, the usual top-2 / top-4): one CTA per token, a thread owns VPT
+// vectors of the row and issues the loads of all k expert rows for them up front (k * VPT 16-byte
+// loads in flight per thread, indices and weights read as broadcast loads), accumulates in index
+// order and stores - the shape of the other row kernels here, at a third of the registers of the
+// warp-per-token kernel above and therefore several times its resident warps.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024)
+token_combine_row_kernel(const T* __restrict__ expert_out, const int64_t* __restrict__ uidx,
+                         const float* __restrict__ weights, T* __restrict__ combined, int k, int n_vec) {
+    constexpr int kPer = Store<T>::kPerVec;
+    constexpr int kMaxK = 4;
+    const int64_t token = blockIdx.x;
+    const Vec16* base = reinterpret_cast<const Vec16*>(expert_out);
+    int64_t row[kMaxK];
+    float w[kMaxK];
+#pragma unroll
+    for (int j = 0; j < kMaxK; ++j) {
+        row[j] = j < k ? __ldg(uidx + token * k + j) : 0;
+        w[j] = j < k ? __ldg(weights + token * k + j) : 0.0f;
+    }
+    Vec16 x[kMaxK][VPT];
+#pragma unroll
+    for (int j = 0; j < kMaxK; ++j)
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+            const int i = threadIdx.x + u * blockDim.x;
+            if (j < k && i < n_vec) x[j][u] = ld_stream(base + row[j] * n_vec + i);
+        }
+    Vec16* out = reinterpret_cast<Vec16*>(combined) + token * n_vec;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int i = threadIdx.x + u * blockDim.x;
+        if (i >= n_vec) continue;
+        float acc[kPer];
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) acc[e] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j)
+            if (j < k) fma_vec<T>(acc, x[j][u], w[j]);
+        st_stream(out + i, pack<T>(acc));
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kCombineMaxThreads)
 token_combine_scalar_kernel(const T* __restrict__ expert_out, const int64_t* __restrict__ uidx,
@@ -350,6 +410,13 @@ cudaError_t run_combine(const void* expert_out, const int64_t* uidx, const float
     T* c = static_cast<T*>(combined);
     if (hidden % kPer == 0 && aligned16(expert_out) && aligned16(combined)) {
         const int64_t n_vec = hidden / kPer;
+        if (k <= 4 && n_vec <= 2048) {          // CTA per token, two vectors per thread
+            int threads = static_cast<int>(ceil_div64(ceil_div64(n_vec, 2), 32) * 32);
+            if (threads < 32) threads = 32;
+            token_combine_row_kernel<T, 2><<<static_cast<unsigned>(n_tokens), threads, 0, s>>>(
+                e, uidx, weights, c, static_cast<int>(k), static_cast<int>(n_vec));
+            return cudaGetLastError();
+        }
         token_combine_vec_kernel<T><<<warp_grid(n_tokens), kCombineMaxThreads, 0, s>>>(e, uidx, weights, c, n_tokens,
                                                                                      static_cast<int>(k), n_vec);
     } else {
