@@ -88,6 +88,12 @@ moe_router_kernel(const T* __restrict__ logits, float* __restrict__ topk_w, int6
     const float inv_sum = 1.0f / sum;
 
     float picked = 0.0f;                        // sum of the selected probabilities
+    // With k <= L, lane j of the group keeps the j-th result in registers: one coalesced store of
+    // weights and ids per token at the end, renormalised on the way, instead of two narrow stores
+    // per round and a global read-modify-write pass for the renormalisation.
+    const bool in_regs = k <= L;
+    float my_p = 0.0f;
+    int my_e = 0;
     if constexpr (L == 32 && sizeof(T) == 2) {
         // 16-bit logits, whole warp per token: value and expert id fit one 32-bit key - the value's
         // bits made order-preserving in the high half, 255 - expert in the low byte, so that a
@@ -129,9 +135,15 @@ moe_router_kernel(const T* __restrict__ logits, float* __restrict__ topk_w, int6
             const float best = Bits16<T>::to_float((ord & 0x8000u) ? (ord & 0x7fffu) : (~ord & 0xffffu));
             const float p = __expf(best - mx) * inv_sum;
             picked += p;
-            if (live && sub == j % L) {
+            const int e = 255 - static_cast<int>(top & 0xffu);
+            if (in_regs) {
+                if (sub == j) {
+                    my_p = p;
+                    my_e = e;
+                }
+            } else if (live && sub == j % L) {
                 topk_w[token * k + j] = p;
-                topk_i[token * k + j] = 255 - static_cast<int>(top & 0xffu);
+                topk_i[token * k + j] = e;
             }
         }
     } else {
@@ -177,13 +189,23 @@ moe_router_kernel(const T* __restrict__ logits, float* __restrict__ topk_w, int6
             }
             const float p = __expf(best - mx) * inv_sum;
             picked += p;
-            if (live && sub == j % L) {
+            if (in_regs) {
+                if (sub == j) {
+                    my_p = p;
+                    my_e = best_e;
+                }
+            } else if (live && sub == j % L) {
                 topk_w[token * k + j] = p;
                 topk_i[token * k + j] = best_e;
             }
         }
     }
-    if (renormalize && live) {
+    if (in_regs) {
+        if (live && sub < k) {
+            topk_w[token * k + sub] = renormalize ? my_p * (1.0f / picked) : my_p;
+            topk_i[token * k + sub] = my_e;
+        }
+    } else if (renormalize && live) {
         const float inv = 1.0f / picked;
         for (int j = sub; j < k; j += L) topk_w[token * k + j] *= inv;      // each lane rescales what it wrote
     }
