@@ -403,6 +403,22 @@ def bench_ops(dev, rank, world, peaks, src, with_reference_kernels=False):
         ca, cwt, cb = a[:1024].cpu(), w.cpu(), bias.cpu()
         cpu("matmul_add_bias_bf16", 2 * 1024 * 4096 * (n1 - n0), lambda: O.matmul_add_bias(ca, cwt, cb),
             "1024 of 8192 rows")
+    if world == 1:
+        # decode-sized batches (not a BASELINE configuration; the serving-side shape of the same op):
+        # 16 and 64 tokens against a 4096 x 4096 weight, six weights in rotation (201 MB > L2) so
+        # that W streams from HBM, cuBLAS (F.linear) beside it.  HBM-bound: W read once.
+        wd = [rn(4096, 4096, scale=0.02) for _ in range(6)]
+        bd = rn(4096, scale=0.02)
+        for m_dec in (16, 64):
+            xd = rn(m_dec, 4096)
+            name = f"matmul_add_bias_bf16_decode_m{m_dec}"
+            work = 4096 * 4096 * 2 + m_dec * 4096 * 2 * 2
+            record(name, "hbm", work, timed_loop(matmul_add_bias, [(xd, wt, bd) for wt in wd], 60, graph=True),
+                   f"{m_dec} x 4096 x 4096, weights rotate through 201 MB")
+            secs = timed_loop(torch.nn.functional.linear, [(xd, wt, bd) for wt in wd], 60, graph=True)
+            out[name]["library_gemm"] = {"us_per_launch": round(secs * 1e6, 2), "achieved": round(work / secs / 1e9, 1),
+                                         "unit": "GB/s", "what": "torch.nn.functional.linear (cuBLAS) on the same operands, same timing"}
+        del wd
     a8, a_s = fp8_quant(sets[0][0], "e4m3", "token") if rows == 8192 else fp8_quant(a, "e4m3", "token")
     w8, w_s = fp8_quant(w, "e4m3", "token")
     record("matmul_add_bias_fp8", "tensor", 2 * 8192 * 4096 * (n1 - n0),
@@ -560,7 +576,7 @@ def multi_gpu_parity(dev, rank, world):
     against the single-GPU result computed on this rank - the vocabulary-sharded loss (one
     all-gather), this rank's column shard of matmul_add_bias, and the vocabulary-parallel
     gradients (all-reduced d_hidden, own d_weight rows).  Every rank takes part in the collectives;
-    the verdict is the AND over ranks."""
+    the outcome is the AND over ranks."""
     from custom_cuda_kernals_b200 import dist
     from custom_cuda_kernals_b200.kernels.linear_cross_entropy import linear_cross_entropy, linear_cross_entropy_fwd_bwd
     from custom_cuda_kernals_b200.kernels.matmul_add_bias import matmul_add_bias

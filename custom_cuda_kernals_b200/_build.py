@@ -35,7 +35,7 @@ DEBUG_SOURCES = ["swiglu.cu", "rmsnorm_residual.cu", "rope.cu"]
 
 CU_SOURCES = ["swiglu.cu", "rmsnorm_residual.cu", "rope.cu", "fp8_quant.cu", "linear_ce_chunk_update.cu",
               "matmul_add_bias.cu", "matmul_fused.cu", "linear_cross_entropy.cu", "backward_elementwise.cu", "moe.cu"]
-HEADERS = ["common.cuh", "ptx.cuh", "gemm_simt.cuh", "gemm_tcgen05.cuh", "gemm_splitk.cuh"]
+HEADERS = ["common.cuh", "ptx.cuh", "gemm_simt.cuh", "gemm_tcgen05.cuh", "gemm_splitk.cuh", "gemm_decode.cuh"]
 
 # No --use_fast_math anywhere: fp8_quant.cu relies on IEEE division.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -13,6 +13,7 @@
 #include <type_traits>
 
 #include "gemm_simt.cuh"
+#include "gemm_decode.cuh"
 #include "gemm_splitk.cuh"
 
 namespace cck {
@@ -144,6 +145,10 @@ cudaError_t gemm_tc(const void* x, const void* w, const void* bias, void* y, int
     typename EpiBias<T>::Params ep{static_cast<const T*>(bias), static_cast<T*>(y), m, n,
                                    (n % 8 == 0 && aligned16(y)) ? 1 : 0};
     const uint32_t fmt = is_bf16 ? 1u : 0u;
+    // Decode-sized batches: the weight rows take the M side of the instruction, the tokens the N
+    // side, K split over a cluster (gemm_decode.cuh).
+    if (m <= 64 && splitk_enabled(m))
+        return launch_decode<T>(x, w, static_cast<const T*>(bias), static_cast<T*>(y), m, k, n, dt, fmt, s);
     CUtensorMap ta, tb;
     cudaError_t e = make_tmap(&ta, dt, 2, x, m, k, kBM);
     if (e != cudaSuccess) return e;

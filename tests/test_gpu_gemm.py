@@ -351,3 +351,27 @@ def test_decode_sized_batches_split_k_by_default(m):
     whole = matmul_add_bias(ad, wd, bd)[:m]
     check(y, whole, torch.bfloat16, ops.TOLERANCE_GEMM)        # same values up to summation order
     assert device_status_clean(y)
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (7, 1032, 520), (16, 72, 136), (17, 4096, 1000), (32, 2048, 6144),
+                                   (33, 512, 264), (48, 11008, 4096), (64, 4096, 14336), (3, 8192, 72), (64, 64, 4096)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_decode_kernel_ragged_shapes(shape, dtype):
+    """Batches of at most 64 tokens: the weight rows sit on the M side of the tensor-core instruction,
+    the tokens on the N side (16 / 32 / 64), K split over a cluster.  Ragged token counts, feature
+    counts that are not multiples of 128 or 8, K that ends inside a 64-element slab, with and
+    without bias; against the fp64 oracle at the GEMM tolerance, and identical run to run."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    m, k, n = shape
+    g = torch.Generator().manual_seed(m * 31 + n)
+    x = (torch.randn(m, k, generator=g) * 0.5).to(dtype)
+    w = (torch.randn(n, k, generator=g) * k ** -0.5).to(dtype)
+    b = torch.randn(n, generator=g).to(dtype)
+    xd, wd, bd = to_dev(x, w, b)
+    y = matmul_add_bias(xd, wd, bd)
+    assert y.shape == (m, n) and y.dtype == dtype
+    check(y.double(), ops.matmul_add_bias_fp64(x, w, b), dtype, ops.TOLERANCE_GEMM)
+    assert torch.equal(y, matmul_add_bias(xd, wd, bd))
+    y0 = matmul_add_bias(xd, wd, None)
+    check(y0.double(), ops.matmul_add_bias_fp64(x, w, None), dtype, ops.TOLERANCE_GEMM)
+    assert device_status_clean(y)
