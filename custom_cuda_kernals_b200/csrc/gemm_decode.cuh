@@ -1,14 +1,14 @@
-// Decode-sized GEMM: y[M,N] = x[M,K] @ W[N,K]^T + bias for a handful of tokens (M <= 64).
+// Decode-sized GEMM: y[M,N] = x[M,K] @ W[N,K]^T + bias for a handful of tokens (M <= 128).
 //
 // With so few rows the job is to stream the weight matrix once, at the HBM rate, through as
 // many SMs as possible - the arithmetic is negligible.  The roles of the operands are therefore
 // swapped with respect to gemm_tcgen05.cuh: the WEIGHT rows are the M side of the tensor-core
 // instruction (a CTA owns 128 consecutive output features and streams their 128 x K slab of W in
-// 16 KB stages), the tokens are the N side (tcgen05.mma with N = 16, 32 or 64; the x slab of a
-// stage is 2-8 KB and stays in L2), and the accumulator is y^T: TMEM lane = output feature,
-// column = token.  Eight stages of W are in flight per CTA, one CTA per SM.  When N / 128 tiles
+// 16 KB stages), the tokens are the N side (tcgen05.mma with N = 16, 32, 64 or 128; the x slab of a
+// stage is 2-16 KB and stays in L2), and the accumulator is y^T: TMEM lane = output feature,
+// column = token.  Eight stages of W are in flight per CTA (six with 128 tokens), one CTA per SM.  When N / 128 tiles
 // do not fill the machine, a thread-block cluster of 2-8 CTAs shares a tile and splits K; the
-// partial accumulators (128 x BT fp32, at most 32 KB) meet in the leader's registers through
+// partial accumulators (128 x BT fp32, at most 64 KB) meet in the leader's registers through
 // distributed shared memory, in rank order - no workspace, no atomics, deterministic, re-entrant
 // across streams.  The epilogue adds the bias and stores the transpose: for one token, the 32
 // lanes of a warp hold 32 consecutive output features, i.e. 64 contiguous bytes of y.
@@ -24,14 +24,15 @@
 namespace cck {
 namespace tc {
 
-constexpr int kDecStages = 8;
-constexpr int kDecTmemCols = 64;
+constexpr int kDecMaxTokens = 128;
 
 template <int BT> struct DecShape {
-    static_assert(BT == 16 || BT == 32 || BT == 64, "token tile of 16, 32 or 64");
-    static constexpr int kXBytes = BT * kRowBytes;                 // 2, 4 or 8 KiB
+    static_assert(BT == 16 || BT == 32 || BT == 64 || BT == 128, "token tile of 16, 32, 64 or 128");
+    static constexpr int kStages = BT <= 64 ? 8 : 6;
+    static constexpr int kTmemCols = BT <= 64 ? 64 : 128;
+    static constexpr int kXBytes = BT * kRowBytes;                 // 2, 4, 8 or 16 KiB
     static constexpr int kStageBytes = kABytes + kXBytes;          // W slab + x slab
-    static constexpr int kSmemBytes = kDecStages * kStageBytes + 1024 + 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
 
 template <typename T, int BT>
@@ -40,6 +41,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                    const T* __restrict__ bias, T* __restrict__ y, int64_t m, int64_t n, int k_blocks, uint32_t idesc,
                    unsigned int* status) {
     constexpr int kStageBytes = DecShape<BT>::kStageBytes;
+    constexpr int kDecStages = DecShape<BT>::kStages;
+    constexpr int kDecTmemCols = DecShape<BT>::kTmemCols;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_addr(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -78,7 +81,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    constexpr int kChunks = BT <= 32 ? 1 : 2;                       // 32-column TMEM reads per row
+    constexpr int kChunks = BT <= 32 ? 1 : BT / 32;                 // 32-column TMEM reads per row
     float acc[kChunks][32];                                         // this thread's output feature, all tokens
     bool have_acc = false;
     if (warp == 0) {
@@ -230,11 +233,11 @@ cudaError_t launch_decode_bt(const CUtensorMap& tw, const CUtensorMap& tx, const
     return cudaLaunchKernelEx(&cfg, kern, tw, tx, bias, y, m, n, k_blocks, idesc, st);
 }
 
-// x [m <= 64, k], W [n, k], 16-bit; k % 8 == 0 and 16-byte aligned operands (the caller checked).
+// x [m <= 128, k], W [n, k], 16-bit; k % 8 == 0 and 16-byte aligned operands (the caller checked).
 template <typename T>
 cudaError_t launch_decode(const void* x, const void* w, const T* bias, T* y, int64_t m, int64_t k, int64_t n,
                           CUtensorMapDataType dt, uint32_t fmt, cudaStream_t s) {
-    const int bt = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    const int bt = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
     CUtensorMap tw, tx;
     cudaError_t e = make_tmap(&tw, dt, 2, w, n, k, kBM);
     if (e != cudaSuccess) return e;
@@ -243,7 +246,8 @@ cudaError_t launch_decode(const void* x, const void* w, const T* bias, T* y, int
     switch (bt) {
         case 16: return launch_decode_bt<T, 16>(tw, tx, bias, y, m, n, k, fmt, s);
         case 32: return launch_decode_bt<T, 32>(tw, tx, bias, y, m, n, k, fmt, s);
-        default: return launch_decode_bt<T, 64>(tw, tx, bias, y, m, n, k, fmt, s);
+        case 64: return launch_decode_bt<T, 64>(tw, tx, bias, y, m, n, k, fmt, s);
+        default: return launch_decode_bt<T, 128>(tw, tx, bias, y, m, n, k, fmt, s);
     }
 }
 

@@ -542,12 +542,13 @@ inline bool narrow_tiles_enabled() {
 }
 
 // Split-K over a thread-block cluster for problems with too few output tiles to pull the weight
-// matrix at speed.  Default: on for decode-sized batches (M <= 64 rows: gemm_decode.cuh, weight
+// matrix at speed.  Default: on for decode-sized batches (M <= 128 rows: gemm_decode.cuh, weight
 // rows on the M side of the instruction), off above.  CCK_GEMM_SPLITK=1 extends it to every problem
-// that leaves SMs idle (gemm_splitk.cuh), CCK_GEMM_SPLITK=0 turns it off.  Why not everywhere: the other kernels add a row's products in one fixed order whatever M
-// and N are, so a row shard or a column shard of a problem gives bit for bit the rows / columns of
-// the whole; partial sums over K slices are added in another order, so where split-K runs that
-// invariance does not hold (results are still deterministic run to run).
+// that leaves SMs idle (gemm_splitk.cuh), CCK_GEMM_SPLITK=0 turns it off.  Why not everywhere: the
+// other kernels add a row's products in one fixed order whatever M and N are, so a row shard or a
+// column shard of a problem gives bit for bit the rows / columns of the whole; partial sums over K
+// slices are added in another order, so where split-K runs that invariance does not hold (results
+// are still deterministic run to run).
 inline int splitk_mode() {
     static const int mode = [] {
         const char* v = getenv("CCK_GEMM_SPLITK");
@@ -557,7 +558,7 @@ inline int splitk_mode() {
 }
 inline bool splitk_enabled(int64_t m_rows) {
     const int mode = splitk_mode();
-    return mode == 1 || (mode < 0 && m_rows <= 64);
+    return mode == 1 || (mode < 0 && m_rows <= 128);
 }
 
 inline int sm_count() {

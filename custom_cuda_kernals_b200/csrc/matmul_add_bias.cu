@@ -147,7 +147,7 @@ cudaError_t gemm_tc(const void* x, const void* w, const void* bias, void* y, int
     const uint32_t fmt = is_bf16 ? 1u : 0u;
     // Decode-sized batches: the weight rows take the M side of the instruction, the tokens the N
     // side, K split over a cluster (gemm_decode.cuh).
-    if (m <= 64 && splitk_enabled(m))
+    if (m <= kDecMaxTokens && splitk_enabled(m))
         return launch_decode<T>(x, w, static_cast<const T*>(bias), static_cast<T*>(y), m, k, n, dt, fmt, s);
     CUtensorMap ta, tb;
     cudaError_t e = make_tmap(&ta, dt, 2, x, m, k, kBM);

@@ -35,7 +35,7 @@ from .kernels.rope import rope, rope_strided
 from .kernels.swiglu import swiglu
 
 __all__ = ["LlamaBlock", "LlamaBlockFP8", "rope_tables", "OpTimer", "PARAM_NAMES", "host_pipeline_groups",
-           "host_pipeline_items"]
+           "host_pipeline_items", "HostStep"]
 
 PARAM_NAMES = ("input_layernorm_weight", "post_attention_layernorm_weight", "q_proj", "k_proj", "v_proj",
                "o_proj", "gate_proj", "up_proj", "down_proj")
@@ -161,6 +161,21 @@ def host_pipeline_items(batch: int, seq: int, chunks: int | None = None, seq_pie
     return items
 
 
+class HostStep:
+    """One step enqueued by ``LlamaBlock.forward_host_async``: ``input_consumed`` fires when the
+    step's input has been copied to the device, ``landed`` when its output is complete in
+    ``out_host``; ``wait()`` blocks the host on the latter and returns ``out_host``."""
+
+    __slots__ = ("out_host", "input_consumed", "landed")
+
+    def __init__(self, out_host: torch.Tensor, input_consumed: torch.cuda.Event, landed: torch.cuda.Event):
+        self.out_host, self.input_consumed, self.landed = out_host, input_consumed, landed
+
+    def wait(self) -> torch.Tensor:
+        self.landed.synchronize()
+        return self.out_host
+
+
 class LlamaBlock:
     """One decoder block; ``weights`` maps PARAM_NAMES to CUDA tensors
     (projections as ``[out_features, in_features]``, the nn.Linear layout)."""
@@ -281,13 +296,32 @@ class LlamaBlock:
         cut into ``seq_pieces`` runs of positions that are fed through ``forward(..., kv_cache=)``
         one after the other (``host_pipeline_items``).  ``seq_pieces=1`` keeps sequences whole.
         Returns ``out_host`` once every item has landed in it."""
+        self.forward_host_async(x_host, out_host, chunks, seq_pieces).wait()
+        return out_host
+
+    def forward_host_async(self, x_host: torch.Tensor, out_host: torch.Tensor, chunks: int | None = 1,
+                           seq_pieces: int | None = 1) -> "HostStep":
+        """``forward_host`` without the final wait: enqueues the copies and kernels of one step and
+        returns a ``HostStep`` at once.  ``step.wait()`` blocks the host until ``out_host`` is
+        complete; ``step.input_consumed`` is the event after which ``x_host`` may be overwritten.
+        Steps enqueued back to back overlap across the step boundary - the next step's copy-in runs
+        under this step's kernels, this step's copy-out under the next step's - which is what hides
+        the transfers when a step is a single sequence (one sequence per rank at 8 GPUs) and
+        nothing inside the step can.  Give every step in flight its own ``out_host``; two in
+        flight are enough to keep all three streams busy.  By default the step is one item
+        (``chunks=1``, ``seq_pieces=1``): with the neighbouring steps to overlap with, cutting it
+        up only shrinks the GEMMs and adds launches.  Measured on one B200, per step: one
+        2048-token sequence 0.78 ms whole and 1.01 ms in two runs of positions, against 0.72 ms of
+        kernels and 1.32 ms for the blocking call; eight sequences 6.1 ms as one item or two,
+        6.3-6.5 ms as four or as the blocking call's 1-2-2-2-1 plan, against 5.7 ms of kernels and
+        6.7 ms for the blocking call.  ``chunks=None`` / ``seq_pieces=None`` select the blocking
+        call's plan."""
         dev = self.device
         b, seq = x_host.shape[0], x_host.shape[1]
         if not hasattr(self, "_copy_in"):
             self._copy_in, self._copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         compute = torch.cuda.current_stream(dev)
         items = host_pipeline_items(b, seq, chunks, seq_pieces if self.fused else 1)
-        self._copy_in.wait_stream(compute)
         staged = []
         with torch.cuda.stream(self._copy_in):
             for b0, b1, s0, s1 in items:
@@ -295,6 +329,7 @@ class LlamaBlock:
                 ev = torch.cuda.Event()
                 ev.record(self._copy_in)
                 staged.append((xd, ev))
+        consumed = staged[-1][1]
         cache = None
         for (b0, b1, s0, s1), (xd, ev) in zip(items, staged):
             compute.wait_event(ev)
@@ -312,8 +347,9 @@ class LlamaBlock:
             y.record_stream(self._copy_out)
             with torch.cuda.stream(self._copy_out):
                 out_host[b0:b1, s0:s1].copy_(y, non_blocking=True)
-        self._copy_out.synchronize()
-        return out_host
+        landed = torch.cuda.Event()
+        landed.record(self._copy_out)
+        return HostStep(out_host, consumed, landed)
 
     def gemm_flops(self, tokens: int) -> int:
         """2*M*K*N summed over the seven projections for ``tokens`` rows."""

@@ -109,6 +109,15 @@ def test_block_is_deterministic_and_batch_independent():
             out_host.zero_()
             block.forward_host(x_host, out_host, chunks=chunks)
             assert torch.equal(out_host, full.cpu())
+        # several steps in flight (submit, then wait for the step before), different inputs, own outputs
+        inputs = [x_host, (x * 0.5).cpu().pin_memory(), x.flip(0).contiguous().cpu().pin_memory()]
+        wants = [full.cpu(), block(x * 0.5).cpu(), block(x.flip(0).contiguous()).cpu()]
+        outs = [torch.zeros_like(x_host).pin_memory() for _ in inputs]
+        steps = [block.forward_host_async(xi, oi) for xi, oi in zip(inputs, outs)]
+        assert steps[0].input_consumed is not steps[0].landed
+        for step, out, want in zip(steps, outs, wants):
+            assert step.wait() is out and torch.equal(out, want)
+        steps[-1].input_consumed.synchronize()
 
 
 def test_block_config4_full_size():

@@ -72,18 +72,18 @@ def test_small_m_narrow_tiles_match_oracle(shape):
 
 def test_row_and_column_shards_are_bitwise_slices_of_the_whole_at_small_sizes():
     """The default kernels (full-width and 128 x 64 tiles) add a row's products in one order
-    whatever the problem size: shards of more than 64 rows reproduce the whole exactly.  Batches of
-    at most 64 rows split K over a cluster by default (decode-sized problems), which adds in
+    whatever the problem size: shards of more than 128 rows reproduce the whole exactly.  Batches of
+    at most 128 rows split K over a cluster by default (decode-sized problems), which adds in
     another order: those agree to the GEMM tolerance, not bit for bit."""
     from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
     g = torch.Generator().manual_seed(8)
     x = torch.randn(768, 1024, generator=g).to(torch.bfloat16).to(DEV)
     w = (0.05 * torch.randn(1536, 1024, generator=g)).to(torch.bfloat16).to(DEV)
     whole = matmul_add_bias(x, w)
-    assert torch.equal(matmul_add_bias(x[:128].contiguous(), w), whole[:128])
-    assert torch.equal(matmul_add_bias(x[300:396].contiguous(), w), whole[300:396])
-    assert torch.equal(matmul_add_bias(x[670:749].contiguous(), w), whole[670:749])
-    for lo, hi in ((300, 316), (700, 749)):
+    assert torch.equal(matmul_add_bias(x[:256].contiguous(), w), whole[:256])
+    assert torch.equal(matmul_add_bias(x[300:429].contiguous(), w), whole[300:429])
+    assert torch.equal(matmul_add_bias(x[470:749].contiguous(), w), whole[470:749])
+    for lo, hi in ((300, 316), (700, 749), (0, 128), (300, 396)):
         check(matmul_add_bias(x[lo:hi].contiguous(), w), whole[lo:hi], torch.bfloat16, ops.TOLERANCE_GEMM)
     assert torch.equal(matmul_add_bias(x, w[512:1024].contiguous()), whole[:, 512:1024])
 
@@ -333,15 +333,15 @@ def test_matmul_general_rejects_bad_arguments():
         matmul_general(a, a, out=torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16), accumulate=True)
 
 
-@pytest.mark.parametrize("m", [1, 16, 64])
+@pytest.mark.parametrize("m", [1, 16, 64, 100, 128])
 def test_decode_sized_batches_split_k_by_default(m):
-    """M <= 64 rows: K is split over a thread-block cluster by default (the weight matrix then
+    """M <= 128 rows: K is split over a thread-block cluster by default (the weight matrix then
     streams through every SM).  Against the fp64 oracle at the GEMM tolerance, identical run to
     run, and - documented - not bit-identical to the rows of a larger batch, whose kernels add a
     row's products in one order."""
     from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
     g = torch.Generator().manual_seed(m)
-    a = torch.randn(128, 4096, generator=g).to(torch.bfloat16)
+    a = torch.randn(256, 4096, generator=g).to(torch.bfloat16)
     w = (0.02 * torch.randn(4096, 4096, generator=g)).to(torch.bfloat16)
     b = (0.02 * torch.randn(4096, generator=g)).to(torch.bfloat16)
     ad, wd, bd = to_dev(a, w, b)
@@ -354,11 +354,12 @@ def test_decode_sized_batches_split_k_by_default(m):
 
 
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (7, 1032, 520), (16, 72, 136), (17, 4096, 1000), (32, 2048, 6144),
-                                   (33, 512, 264), (48, 11008, 4096), (64, 4096, 14336), (3, 8192, 72), (64, 64, 4096)])
+                                   (33, 512, 264), (48, 11008, 4096), (64, 4096, 14336), (3, 8192, 72), (64, 64, 4096),
+                                   (65, 4096, 4096), (128, 4096, 4096), (100, 1032, 520), (128, 14336, 4096), (97, 72, 136)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_decode_kernel_ragged_shapes(shape, dtype):
-    """Batches of at most 64 tokens: the weight rows sit on the M side of the tensor-core instruction,
-    the tokens on the N side (16 / 32 / 64), K split over a cluster.  Ragged token counts, feature
+    """Batches of at most 128 tokens: the weight rows sit on the M side of the tensor-core instruction,
+    the tokens on the N side (16 / 32 / 64 / 128), K split over a cluster.  Ragged token counts, feature
     counts that are not multiples of 128 or 8, K that ends inside a 64-element slab, with and
     without bias; against the fp64 oracle at the GEMM tolerance, and identical run to run."""
     from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
