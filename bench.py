@@ -405,11 +405,11 @@ def bench_ops(dev, rank, world, peaks, src, with_reference_kernels=False):
             "1024 of 8192 rows")
     if world == 1:
         # decode-sized batches (not a BASELINE configuration; the serving-side shape of the same op):
-        # 16 and 64 tokens against a 4096 x 4096 weight, six weights in rotation (201 MB > L2) so
+        # 16, 64 and 128 tokens against a 4096 x 4096 weight, six weights in rotation (201 MB > L2) so
         # that W streams from HBM, cuBLAS (F.linear) beside it.  HBM-bound: W read once.
         wd = [rn(4096, 4096, scale=0.02) for _ in range(6)]
         bd = rn(4096, scale=0.02)
-        for m_dec in (16, 64):
+        for m_dec in (16, 64, 128):
             xd = rn(m_dec, 4096)
             name = f"matmul_add_bias_bf16_decode_m{m_dec}"
             work = 4096 * 4096 * 2 + m_dec * 4096 * 2 * 2

@@ -8,13 +8,14 @@
 // stage is 2-16 KB and stays in L2), and the accumulator is y^T: TMEM lane = output feature,
 // column = token.  Eight stages of W are in flight per CTA (six with 128 tokens), one CTA per SM.  When N / 128 tiles
 // do not fill the machine, a thread-block cluster of 2-8 CTAs shares a tile and splits K; the
-// partial accumulators (128 x BT fp32, at most 64 KB) meet in the leader's registers through
-// distributed shared memory, in rank order - no workspace, no atomics, deterministic, re-entrant
-// across streams.  The epilogue adds the bias and stores the transpose: for one token, the 32
+// partial accumulators (128 x BT fp32, at most 64 KB per CTA) are summed through distributed
+// shared memory as a reduce-scatter - every CTA of the cluster sums and stores its share of the
+// tokens, adding the ranks' partials in rank order - no workspace, no atomics, deterministic,
+// re-entrant across streams.  The epilogue adds the bias and stores the transpose: for one token, the 32
 // lanes of a warp hold 32 consecutive output features, i.e. 64 contiguous bytes of y.
 //
 // Waits are the bounded ones of ptx.cuh; the cluster barriers are reached by every thread on
-// every path; if any CTA of a cluster gave up, the leader stores nothing for the tile and bit 0
+// every path; if any CTA of a cluster gave up, none of them stores anything for the tile and bit 0
 // of the status word is set.  Sums over K slices are added in another order than the other GEMM
 // kernels use, so these results agree with theirs to rounding, not bit for bit.
 #pragma once
@@ -126,9 +127,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) ptx::tmem_ld32(t0 + 32 * c, acc[c]);
             have_acc = true;
-            if (rank != 0) {
-                // park it as BT / 4 float4 planes [plane][feature]: consecutive features are 16 bytes
-                // apart, so this store and the leader's remote load are contiguous across a warp
+            if (splits > 1) {
+                // park it as BT / 4 float4 planes [plane][feature] (plane q = tokens 4q..4q+3):
+                // consecutive features are 16 bytes apart, so this store and the remote loads of
+                // part 2 are contiguous across a warp
                 float4* part = reinterpret_cast<float4*>(gen);
                 const int row = quarter * 32 + lane;
 #pragma unroll
@@ -143,37 +145,48 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     ptx::cluster_arrive();                                          // every thread of every CTA, on every path
     ptx::cluster_wait();
 
-    bool peers_ok = true;
-    if (rank == 0 && warp >= 2) {
+    if (warp >= 2) {
+        // ---- epilogue, part 2: the sum over the cluster, bias, rounding, transposed store.  The
+        // token planes are dealt over the CTAs of the cluster (a reduce-scatter through distributed
+        // shared memory): every CTA sums its planes over all ranks, in rank order, and stores them.
+        bool all_ok = have_acc && !*abort_flag;
         const uint32_t flag_local = ptx::smem_addr(const_cast<int*>(abort_flag));
-        for (uint32_t r = 1; r < splits; ++r) peers_ok = peers_ok && ld_cluster_u32(ptx::map_to_cta(flag_local, r)) == 0u;
-        if (!peers_ok && threadIdx.x == 64) atomicOr(status, 1u);
-    }
-    if (rank == 0 && warp >= 2 && have_acc && !*abort_flag && peers_ok) {
-        // ---- epilogue, part 2 (leader): peers' partials in rank order, bias, round, transposed store
+        for (uint32_t r = 0; r < splits; ++r)
+            if (r != rank) all_ok = all_ok && ld_cluster_u32(ptx::map_to_cta(flag_local, r)) == 0u;
+        if (!all_ok && threadIdx.x == 64) atomicOr(status, 1u);
         const int row_in_tile = (warp & 3) * 32 + lane;
-        for (uint32_t r = 1; r < splits; ++r) {
-            const uint32_t remote = ptx::map_to_cta(base, r);
-#pragma unroll
-            for (int q = 0; q < BT / 4; ++q) {
-                const int c = q / 8, j = 4 * (q % 8);
-                const float4 v = ld_cluster_f4(remote + static_cast<uint32_t>((q * kBM + row_in_tile) * 16));
-                acc[c][j] += v.x;
-                acc[c][j + 1] += v.y;
-                acc[c][j + 2] += v.z;
-                acc[c][j + 3] += v.w;
-            }
-        }
         const int64_t feature = static_cast<int64_t>(n_tile) * kBM + row_in_tile;
-        if (feature < n) {
+        if (all_ok && feature < n) {
             const float b = bias != nullptr ? Store<T>::load1(bias + feature) : 0.0f;
+            if (splits == 1) {
 #pragma unroll
-            for (int t = 0; t < BT; ++t)
-                if (t < m) Store<T>::store1(y + static_cast<int64_t>(t) * n + feature, acc[t / 32][t % 32] + b);
+                for (int t = 0; t < BT; ++t)
+                    if (t < m) Store<T>::store1(y + static_cast<int64_t>(t) * n + feature, acc[t / 32][t % 32] + b);
+            } else {
+                constexpr int kPlanes = BT / 4;
+                const int q0 = static_cast<int>(rank) * kPlanes / static_cast<int>(splits);
+                const int q1 = (static_cast<int>(rank) + 1) * kPlanes / static_cast<int>(splits);
+                for (int q = q0; q < q1 && 4 * q < m; ++q) {
+                    const uint32_t off = static_cast<uint32_t>((q * kBM + row_in_tile) * 16);
+                    float4 sum = ld_cluster_f4(ptx::map_to_cta(base, 0) + off);
+                    for (uint32_t r = 1; r < splits; ++r) {
+                        const float4 v = ld_cluster_f4(ptx::map_to_cta(base, r) + off);
+                        sum.x += v.x;
+                        sum.y += v.y;
+                        sum.z += v.z;
+                        sum.w += v.w;
+                    }
+                    T* dst = y + static_cast<int64_t>(4 * q) * n + feature;
+                    Store<T>::store1(dst, sum.x + b);
+                    if (4 * q + 1 < m) Store<T>::store1(dst + n, sum.y + b);
+                    if (4 * q + 2 < m) Store<T>::store1(dst + 2 * n, sum.z + b);
+                    if (4 * q + 3 < m) Store<T>::store1(dst + 3 * n, sum.w + b);
+                }
+            }
         }
     }
 
-    ptx::cluster_arrive();                                          // the peers' shared memory outlives the leader's reads
+    ptx::cluster_arrive();                                          // every CTA's shared memory outlives its peers' reads
     ptx::cluster_wait();
 
     ptx::tc_fence_before_sync();
@@ -192,7 +205,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 }
 
 // K split for `tiles` 128-feature tiles: the largest power of two (up to 8) that keeps every CTA
-// resident at once (one per SM) and leaves each CTA at least four 64-element slabs.
+// resident at once (one per SM) and leaves each CTA at least four 64-element slabs.  Clusters that
+// run in more than one wave were measured and are not used: 86 tiles (N = 11008) as clusters of 5
+// in 3 waves - the shortest schedule on paper, 0.6 of the unsplit time - took 35.5 us against 21.3 us
+// unsplit.
 inline int decode_split(int64_t tiles, int k_blocks) {
     int s = 1;
     while (s < kSkMaxSplit && tiles * (2 * s) <= sm_count() && k_blocks / (2 * s) >= 4) s *= 2;
