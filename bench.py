@@ -795,7 +795,7 @@ def run_ours(args, rank, world, local):
     line["e2e"] = {"value": tokens * args.steps / e2e_secs, "unit": UNIT,
                    "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": out_host.numel() * 2 * world,
                    "ms_per_step": e2e_secs / args.steps * 1e3,
-                   "api": "LlamaBlock.forward_host_async(pinned x, pinned out).wait(): H2D, 7 library kernels + SDPA, D2H on 3 streams; "
+                   "api": "LlamaBlock.forward_host_async(pinned x, pinned out).wait(): H2D, the block (6 library kernels + SDPA), D2H on 3 streams; "
                           "the caller keeps 2 steps in flight (submit step i, then wait for step i-1), each with its own pinned "
                           "output buffer; every step's copies and the final wait are timed",
                    "blocking_call": {"value": tokens * args.steps / e2e_blocking_secs, "unit": UNIT,

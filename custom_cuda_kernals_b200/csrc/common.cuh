@@ -227,6 +227,16 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // Function attributes (dynamic shared memory limit) and occupancy figures belong to a
 // (function, device) pair: per-instantiation caches are indexed by the current device.
+// One rotary pair, fp32: (a, b) are elements i and i + head_dim / 2 of a head, (c, s) = cos / sin of
+// the position at i.  Every product and the sum / difference are rounded on their own (no fused
+// multiply-add), which is the op chain of the eager baseline (baselines/rope.py:129-138) and does
+// not depend on how the compiler would contract the expression in one kernel or another: the rope
+// kernels and the GEMM epilogue that applies RoPE share this function and give the same bits.
+__device__ __forceinline__ void rope_rotate(float a, float b, float c, float s, float& o1, float& o2) {
+    o1 = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+    o2 = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+}
+
 constexpr int kMaxDevices = 64;
 inline int current_device_slot() {
     int dev = 0;

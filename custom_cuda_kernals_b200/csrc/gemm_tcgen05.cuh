@@ -104,9 +104,14 @@ struct SchedGemm {
 // Reads one finished 128 x 256 accumulator (this thread's row) out of tensor memory and hands
 // it to the epilogue policy, 32 columns at a time.  A policy with kPairedHalves pairs column j
 // of the tile's first half with column j of its second half (gate / up of a fused SwiGLU GEMM)
-// and gets both 32-column pieces at once.
+// - or, with kPairStride = 64, column j of a 128-column head with column j + 64 (RoPE) - and gets
+// both 32-column pieces at once.
 template <class Epi, class = void> struct PairedHalves { static constexpr bool value = false; };
 template <class Epi> struct PairedHalves<Epi, std::enable_if_t<Epi::kPairedHalves>> { static constexpr bool value = true; };
+// Distance in columns between the two members of a pair: half the tile unless the policy says
+// otherwise with kPairStride (64: column j of every 128-column head with column j + 64, RoPE).
+template <class Epi, class = void> struct PairStride { static constexpr int value = kBN / 2; };
+template <class Epi> struct PairStride<Epi, std::void_t<decltype(Epi::kPairStride)>> { static constexpr int value = Epi::kPairStride; };
 
 template <class Epi, int BN = kBN>
 __device__ __forceinline__ void drain_tile(const typename Epi::Params& ep, typename Epi::Thread& th, const TileWork& w,
@@ -114,11 +119,13 @@ __device__ __forceinline__ void drain_tile(const typename Epi::Params& ep, typen
     if constexpr (PairedHalves<Epi>::value) {
         static_assert(BN == kBN, "paired halves need the full-width tile");
 #pragma unroll 1
+        constexpr int kStride = PairStride<Epi>::value;
         for (int c = 0; c < kBN / 64; ++c) {
+            const int lo_col = (c * 32 / kStride) * 2 * kStride + (c * 32) % kStride;
             float lo[32], hi[32];
-            ptx::tmem_ld32(t0 + c * 32, lo);
-            ptx::tmem_ld32(t0 + kBN / 2 + c * 32, hi);
-            Epi::chunk2(ep, th, w, row_in_tile, c * 32, lo, hi, scratch);
+            ptx::tmem_ld32(t0 + lo_col, lo);
+            ptx::tmem_ld32(t0 + lo_col + kStride, hi);
+            Epi::chunk2(ep, th, w, row_in_tile, lo_col, lo, hi, scratch);
         }
     } else {
 #pragma unroll 1

@@ -65,6 +65,65 @@ struct EpiSwiGLU {
     __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
 };
 
+// ---- epilogue: y = rope(round(acc + bias)) on the columns below rope_cols, round(acc + bias) on the rest
+// One projection for q, k and v with the rotary embedding applied where the accumulator is read:
+// rows are tokens (row = sequence * seq_len + position), columns are 128-wide heads, element j of
+// a head is rotated with element j + 64 (half-split convention, as in rope.cu).  The projection is
+// rounded to the storage type before the rotation, so the result equals rope(matmul_add_bias(...))
+// bit for bit.
+template <typename T>
+struct EpiBiasRope {
+    static constexpr bool kPairedHalves = true;
+    static constexpr int kPairStride = 64;
+    struct Params {
+        const T* bias;           // [N] or null
+        const float* cos_t;      // [seq_len, 64]
+        const float* sin_t;
+        T* y;                    // [M, N]
+        int64_t m, n, rope_cols; // n and rope_cols are multiples of 128
+        int seq_len;
+        int vec_ok;
+    };
+    struct Thread { int pos; };
+    __device__ static __forceinline__ void tile_begin(const Params& p, Thread& th, const TileWork& w, float* scratch,
+                                                      int lane, int row_in_tile) {
+#pragma unroll
+        for (int i = 0; i < kBN / 32; ++i) {
+            const int64_t col = static_cast<int64_t>(w.n0) + lane + 32 * i;
+            scratch[lane + 32 * i] = (p.bias != nullptr && col < p.n) ? Store<T>::load1(p.bias + col) : 0.0f;
+        }
+        th.pos = static_cast<int>((static_cast<int64_t>(w.m_tile) * kBM + row_in_tile) % p.seq_len);
+    }
+    __device__ static __forceinline__ void chunk2(const Params& p, Thread& th, const TileWork& w, int row_in_tile, int c0,
+                                                  float (&lo)[32], float (&hi)[32], const float* scratch) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        const int64_t col = static_cast<int64_t>(w.n0) + c0;          // a head never straddles n: n % 128 == 0
+        if (row >= p.m || col >= p.n) return;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            lo[j] = Store<T>::round(lo[j] + scratch[c0 + j]);
+            hi[j] = Store<T>::round(hi[j] + scratch[c0 + 64 + j]);
+        }
+        if (col < p.rope_cols) {
+            const int64_t t = static_cast<int64_t>(th.pos) * 64 + (c0 & 63);
+            const float4* cp = reinterpret_cast<const float4*>(p.cos_t + t);
+            const float4* sp = reinterpret_cast<const float4*>(p.sin_t + t);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 c = __ldg(cp + q), sn = __ldg(sp + q);
+                rope_rotate(lo[4 * q], hi[4 * q], c.x, sn.x, lo[4 * q], hi[4 * q]);
+                rope_rotate(lo[4 * q + 1], hi[4 * q + 1], c.y, sn.y, lo[4 * q + 1], hi[4 * q + 1]);
+                rope_rotate(lo[4 * q + 2], hi[4 * q + 2], c.z, sn.z, lo[4 * q + 2], hi[4 * q + 2]);
+                rope_rotate(lo[4 * q + 3], hi[4 * q + 3], c.w, sn.w, lo[4 * q + 3], hi[4 * q + 3]);
+            }
+        }
+        T* out = p.y + row * p.n + col;
+        store32<T>(out, lo, col, p.n, p.vec_ok);
+        store32<T>(out + 64, hi, col + 64, p.n, p.vec_ok);
+    }
+    __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
+};
+
 // ---- epilogue: y = round(acc + bias) + residual
 template <typename T>
 struct EpiBiasResidual {
@@ -450,6 +509,32 @@ extern "C" int32_t launch_matmul_swiglu_fwd(const void* x, const void* w_gate_up
     if (dtype == kF16) {
         EpiSwiGLU<__half>::Params ep{static_cast<__half*>(y), m, f, vec_ok};
         return run_fused<__half, EpiSwiGLU<__half>>(x, w_gate_up, m, k, 2 * f, ep, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+extern "C" int32_t launch_matmul_add_bias_rope_fwd(const void* x, const void* weight, const void* bias,
+                                                   const float* cos_table, const float* sin_table, void* y, int64_t m,
+                                                   int64_t k, int64_t n, int64_t rope_cols, int64_t seq_len,
+                                                   int32_t dtype, void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (m <= 0 || k <= 0 || n <= 0) return cudaSuccess;
+    if (cos_table == nullptr || sin_table == nullptr || n % 128 != 0 || rope_cols % 128 != 0 || rope_cols < 0 ||
+        rope_cols > n || seq_len <= 0 || seq_len >= (1LL << 31) || !aligned16(cos_table) || !aligned16(sin_table) ||
+        !tc_shape_ok(x, weight, m, k, n))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int vec_ok = aligned16(y) ? 1 : 0;
+    if (dtype == kBF16) {
+        EpiBiasRope<__nv_bfloat16>::Params ep{static_cast<const __nv_bfloat16*>(bias), cos_table, sin_table,
+                                              static_cast<__nv_bfloat16*>(y), m, n, rope_cols, static_cast<int>(seq_len), vec_ok};
+        return run_fused<__nv_bfloat16, EpiBiasRope<__nv_bfloat16>>(x, weight, m, k, n, ep, s);
+    }
+    if (dtype == kF16) {
+        EpiBiasRope<__half>::Params ep{static_cast<const __half*>(bias), cos_table, sin_table, static_cast<__half*>(y),
+                                       m, n, rope_cols, static_cast<int>(seq_len), vec_ok};
+        return run_fused<__half, EpiBiasRope<__half>>(x, weight, m, k, n, ep, s);
     }
     return cudaErrorInvalidValue;
 }

@@ -655,6 +655,44 @@ void matmul_add_bias_residual_fwd(const at::Tensor& x, const at::Tensor& weight,
                                                      residual.data_ptr(), y.data_ptr(), m, k, n, dt, l.stream));
 }
 
+void matmul_add_bias_rope_fwd(const at::Tensor& x, const at::Tensor& weight, const c10::optional<at::Tensor>& bias,
+                              const at::Tensor& cos, const at::Tensor& sin, const at::Tensor& y, int64_t rope_cols) {
+    const int32_t dt = tag_of("x", x);
+    if (dt != CCK_BF16 && dt != CCK_F16)
+        value_error(std::string("unsupported dtype '") + tag_name(dt) + "' for the fused path; expected float16 or bfloat16");
+    expect_same_dtype("weight", tag_of("weight", weight), dt);
+    expect_same_dtype("y", tag_of("y", y), dt);
+    expect_f32("cos", tag_of("cos", cos), " (RoPE tables are always fp32)");
+    expect_f32("sin", tag_of("sin", sin), " (RoPE tables are always fp32)");
+    const bool has_bias = bias.has_value() && bias->defined();
+    if (has_bias) expect_same_dtype("bias", tag_of("bias", *bias), dt);
+    if (x.dim() != 2 || weight.dim() != 2)
+        value_error("shape mismatch: x and weight must be 2-D; got x=" + shape_str(x) + ", weight=" + shape_str(weight));
+    const int64_t m = x.size(0), k = x.size(1), n = weight.size(0);
+    if (weight.size(1) != k)
+        value_error("shape mismatch: weight's in_features (" + std::to_string(weight.size(1)) +
+                    ") must match x's last dim (" + std::to_string(k) + ")");
+    if (k % 8 != 0) value_error("shape mismatch: the fused path needs K to be a multiple of 8");
+    if (n % 128 != 0 || rope_cols % 128 != 0 || rope_cols < 0 || rope_cols > n)
+        value_error("shape mismatch: heads are 128 columns wide: weight rows (" + std::to_string(n) + ") and rope_cols (" +
+                    std::to_string(rope_cols) + ") must be multiples of 128 with rope_cols <= rows");
+    if (y.dim() != 2 || y.size(0) != m || y.size(1) != n)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " + std::to_string(n) + "]");
+    if (cos.dim() != 2 || sin.dim() != 2 || cos.size(1) != 64 || sin.size(1) != 64 || cos.size(0) != sin.size(0) ||
+        cos.size(0) < 1 || m % cos.size(0) != 0)
+        value_error("shape mismatch: cos/sin must be [seq_len, 64] with x's rows (" + std::to_string(m) +
+                    ") a multiple of seq_len; got cos=" + shape_str(cos) + ", sin=" + shape_str(sin));
+    if (has_bias && (bias->dim() != 1 || bias->size(0) != n))
+        value_error("shape mismatch: bias shape " + shape_str(*bias) + " must be [" + std::to_string(n) + "]");
+    at::Tensor none;
+    Launch l(x, {&weight, &cos, &sin, &y, has_bias ? &*bias : &none});
+    check_launch("launch_matmul_add_bias_rope_fwd",
+                 launch_matmul_add_bias_rope_fwd(x.data_ptr(), weight.data_ptr(), has_bias ? bias->data_ptr() : nullptr,
+                                                 static_cast<const float*>(cos.data_ptr()),
+                                                 static_cast<const float*>(sin.data_ptr()), y.data_ptr(), m, k, n,
+                                                 rope_cols, cos.size(0), dt, l.stream));
+}
+
 // ------------------------------------------------------------------ src/kernels/linear_cross_entropy.rs:44-133
 void linear_ce_chunk_update(const at::Tensor& logits_chunk, const at::Tensor& targets, int64_t v_start,
                             const at::Tensor& running_max, const at::Tensor& running_sum,
@@ -1139,6 +1177,8 @@ PYBIND11_MODULE(_native, m) {
     m.def("rope_strided_fwd", &rope_strided_fwd, py::arg("q"), py::arg("k"), py::arg("cos"), py::arg("sin"),
           py::arg("q_out"), py::arg("k_out"));
     m.def("matmul_swiglu_fwd", &matmul_swiglu_fwd, py::arg("x"), py::arg("w_gate_up"), py::arg("y"));
+    m.def("matmul_add_bias_rope_fwd", &matmul_add_bias_rope_fwd, py::arg("x"), py::arg("weight"),
+          py::arg("bias").none(true), py::arg("cos"), py::arg("sin"), py::arg("y"), py::arg("rope_cols"));
     m.def("matmul_add_bias_residual_fwd", &matmul_add_bias_residual_fwd, py::arg("x"), py::arg("weight"),
           py::arg("bias").none(true), py::arg("residual"), py::arg("y"));
     m.def("linear_cross_entropy_fwd", &linear_cross_entropy_fwd, py::arg("hidden"), py::arg("weight"),

@@ -26,10 +26,7 @@ __device__ __forceinline__ void rotate_store(const Vec16& lo, const Vec16& hi,
     unpack<T>(lo, a);
     unpack<T>(hi, b);
 #pragma unroll
-    for (int e = 0; e < kPer; ++e) {
-        o1[e] = a[e] * c[e] - b[e] * s[e];
-        o2[e] = b[e] * c[e] + a[e] * s[e];
-    }
+    for (int e = 0; e < kPer; ++e) rope_rotate(a[e], b[e], c[e], s[e], o1[e], o2[e]);
     st_stream(out_lo, pack<T>(o1));
     st_stream(out_hi, pack<T>(o2));
 }
@@ -115,8 +112,10 @@ rope_scalar_kernel(const T* __restrict__ q, const T* __restrict__ k, const float
         const int64_t o = (tok * (is_q ? hq : hkv) + hh) * head_dim + i;
         const int64_t in = tok * (is_q ? q_tok_stride : k_tok_stride) + static_cast<int64_t>(hh) * head_dim + i;
         const float a = Store<T>::load1(src + in), b = Store<T>::load1(src + in + half);
-        Store<T>::store1(dst + o, a * c - b * sn);
-        Store<T>::store1(dst + o + half, b * c + a * sn);
+        float o1, o2;
+        rope_rotate(a, b, c, sn, o1, o2);
+        Store<T>::store1(dst + o, o1);
+        Store<T>::store1(dst + o + half, o2);
     }
 }
 

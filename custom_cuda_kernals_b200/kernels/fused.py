@@ -8,7 +8,7 @@ import torch
 
 from .. import _native
 
-__all__ = ["interleave_gate_up", "matmul_swiglu", "matmul_add_bias_residual", "matmul_add_bias_stats",
+__all__ = ["interleave_gate_up", "matmul_swiglu", "matmul_add_bias_residual", "matmul_add_bias_rope", "matmul_add_bias_stats",
            "rmsnorm_from_stats", "fp8_quant_token_from_amax", "matmul_general", "rmsnorm_fp8_quant",
            "matmul_swiglu_fp8", "matmul_add_bias_residual_fp8", "GATE_UP_BLOCK"]
 
@@ -41,6 +41,21 @@ def matmul_add_bias_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.
     """``x @ weight.T + bias + residual`` (residual ``[M, N]``), float16/bfloat16."""
     y = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
     _native.matmul_add_bias_residual_fwd(x, weight, bias, residual, y)
+    return y
+
+
+def matmul_add_bias_rope(x: torch.Tensor, w_qkv: torch.Tensor, bias: torch.Tensor | None, cos: torch.Tensor,
+                         sin: torch.Tensor, rope_cols: int) -> torch.Tensor:
+    """One projection for q, k and v with the rotary embedding applied in the GEMM epilogue:
+    ``y = x @ w_qkv.T + bias`` (``x [B*S, K]``, rows ordered sequence by sequence; ``w_qkv`` = q, k
+    and v weights concatenated along the output dimension, heads of 128), then RoPE with
+    ``cos, sin [S, 64]`` (row ``r`` is position ``r % S``) on the first ``rope_cols`` output columns
+    - the q and k heads.  Equals ``rope_strided`` applied to the q / k column ranges of
+    ``matmul_add_bias(x, w_qkv, bias)`` bit for bit, without the extra pass over q and k
+    (examples/llama_block.py:147-156 run three projections and a separate rope kernel).
+    Returns ``[B*S, N]``; q, k and v are column ranges of it."""
+    y = torch.empty((x.shape[0], w_qkv.shape[0]), dtype=x.dtype, device=x.device)
+    _native.matmul_add_bias_rope_fwd(x, w_qkv, bias, cos, sin, y, rope_cols)
     return y
 
 

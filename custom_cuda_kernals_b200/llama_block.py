@@ -13,8 +13,9 @@ library's tcgen05 GEMM (``matmul_add_bias`` with no bias), and by default two of
 them carry the neighbouring elementwise op in their epilogue - gate/up + SwiGLU in
 one GEMM, o_proj and down_proj + their residual adds in two more (so both norms read
 one tensor instead of two) - and q, k, v come from one
-projection whose q / k column ranges RoPE reads in place; results are identical to
-the unfused chain (``fused=False`` runs that chain).  The attention core stays
+projection that applies RoPE to its q / k columns in the epilogue (heads of 128;
+otherwise, or with ``rope_in_gemm=False``, a rope kernel reads the q / k column ranges
+in place); results are identical to the unfused chain (``fused=False`` runs that chain).  The attention core stays
 ``torch.nn.functional.scaled_dot_product_attention`` as in the reference.
 Forward only, no autograd.
 """
@@ -28,7 +29,8 @@ import torch.nn.functional as F
 
 from .kernels.fp8_quant import fp8_quant
 from .kernels.fused import (GATE_UP_BLOCK, fp8_quant_token_from_amax, interleave_gate_up, matmul_add_bias_residual,
-                            matmul_add_bias_residual_fp8, matmul_swiglu, matmul_swiglu_fp8, rmsnorm_fp8_quant)
+                            matmul_add_bias_residual_fp8, matmul_add_bias_rope, matmul_swiglu, matmul_swiglu_fp8,
+                            rmsnorm_fp8_quant)
 from .kernels.matmul_add_bias import matmul_add_bias, matmul_add_bias_fp8
 from .kernels.rmsnorm_residual import rmsnorm, rmsnorm_residual
 from .kernels.rope import rope, rope_strided
@@ -181,7 +183,8 @@ class LlamaBlock:
     (projections as ``[out_features, in_features]``, the nn.Linear layout)."""
 
     def __init__(self, weights: dict[str, torch.Tensor], n_heads: int = 32, n_kv_heads: int = 8,
-                 eps: float = 1e-5, theta: float = 500000.0, max_seq_len: int = 2048, fused: bool = True):
+                 eps: float = 1e-5, theta: float = 500000.0, max_seq_len: int = 2048, fused: bool = True,
+                 rope_in_gemm: bool = True):
         missing = [n for n in PARAM_NAMES if n not in weights]
         if missing:
             raise ValueError(f"missing block parameters: {missing}")
@@ -206,10 +209,12 @@ class LlamaBlock:
             self.ffn = ffn
             for name in ("gate_proj", "up_proj", "q_proj", "k_proj", "v_proj"):
                 del self.w[name]
+        #: the rotary embedding rides in the epilogue of the q/k/v projection (heads of 128 only)
+        self.rope_in_gemm = bool(self.fused and self.head_dim == 128 and rope_in_gemm)
         #: kernels of this library launched per forward call: 2 norms, rope, and either
         #: q + k + v + o + gate + up + swiglu + down (unfused: 11 in all) or
-        #: qkv + o + gate-up-swiglu + down-residual (fused: 7 in all)
-        self.launches_per_forward = 7 if self.fused else 11
+        #: qkv + o + gate-up-swiglu + down-residual (fused: 7 in all, 6 with the rope in the qkv GEMM)
+        self.launches_per_forward = (6 if self.rope_in_gemm else 7) if self.fused else 11
 
     def forward(self, x: torch.Tensor, timer: OpTimer | None = None, pos_offset: int = 0,
                 kv_cache: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
@@ -236,13 +241,17 @@ class LlamaBlock:
             zero = t.run("fill", torch.zeros_like, x2)
             h, res = t.run("rmsnorm", rmsnorm_residual, x2, zero, w["input_layernorm_weight"], self.eps)
         cos, sin = self.cos[pos_offset:pos_offset + s], self.sin[pos_offset:pos_offset + s]
-        if self.fused:       # one projection for q, k and v; rope reads its q / k column ranges in place
-            qkv = t.run("gemm", matmul_add_bias, h, self.w_qkv).view(b, s, -1)
+        if self.fused:       # one projection for q, k and v
             qc, kc = self.q_cols, self.kv_cols
+            if self.rope_in_gemm:    # ... with the rotary embedding applied in its epilogue
+                qkv = t.run("gemm_rope", matmul_add_bias_rope, h, self.w_qkv, None, cos, sin, qc + kc).view(b, s, -1)
+            else:
+                qkv = t.run("gemm", matmul_add_bias, h, self.w_qkv).view(b, s, -1)
             q = qkv[..., :qc].unflatten(-1, (self.n_heads, self.head_dim))
             k = qkv[..., qc:qc + kc].unflatten(-1, (self.n_kv_heads, self.head_dim))
             v = qkv[..., qc + kc:].unflatten(-1, (self.n_kv_heads, self.head_dim))
-            q, k = t.run("rope", rope_strided, q, k, cos, sin)
+            if not self.rope_in_gemm:    # rope reads its q / k column ranges in place
+                q, k = t.run("rope", rope_strided, q, k, cos, sin)
         else:
             q = t.run("gemm", matmul_add_bias, h, w["q_proj"]).view(b, s, self.n_heads, self.head_dim)
             k = t.run("gemm", matmul_add_bias, h, w["k_proj"]).view(b, s, self.n_kv_heads, self.head_dim)

@@ -145,6 +145,20 @@ int32_t launch_rope_strided_fwd(const void* q, const void* k, const void* cos_ta
 int32_t launch_matmul_swiglu_fwd(const void* x, const void* w_gate_up, void* y, int64_t m, int64_t k,
                                  int64_t f, int32_t dtype, void* stream);
 
+/* Fused q/k/v projection + rotary embedding: y[m, n] = x @ weight^T + bias with RoPE (half-split
+ * convention, heads of 128 columns: column j of a head rotates with column j + 64) applied to the
+ * columns below rope_cols - the q and k heads - and the rest (v) stored as projected.  Row r is
+ * position r % seq_len; cos_table / sin_table are [seq_len, 64] float32.  The projection is rounded
+ * to the storage type before the rotation, so the result is identical to launch_matmul_add_bias_fwd
+ * followed by launch_rope_strided_fwd on the q and k column ranges (the steps of
+ * examples/llama_block.py:147-156 for a concatenated q/k/v weight).  dtype CCK_BF16 or CCK_F16;
+ * n % 128 == 0, rope_cols % 128 == 0, rope_cols <= n, k % 8 == 0, 16-byte aligned operands and
+ * tables; otherwise cudaErrorInvalidValue.  No reference counterpart. */
+int32_t launch_matmul_add_bias_rope_fwd(const void* x, const void* weight, const void* bias,
+                                        const float* cos_table, const float* sin_table, void* y, int64_t m,
+                                        int64_t k, int64_t n, int64_t rope_cols, int64_t seq_len,
+                                        int32_t dtype, void* stream);
+
 /* y = x @ weight^T + bias + residual (residual [m, n], bias [n] or NULL), identical to
  * launch_matmul_add_bias_fwd followed by an elementwise add in the storage type.  dtype CCK_BF16
  * or CCK_F16; k % 8 == 0, 16-byte aligned x and weight; otherwise cudaErrorInvalidValue. */

@@ -268,6 +268,61 @@ def test_fused_residual_add_equals_unfused_chain(shape, with_bias):
     assert device_status_clean(fused)
 
 
+@pytest.mark.parametrize("cfg", [
+    # (batch, seq, hidden, q heads, kv heads, with_bias)
+    (2, 192, 1024, 8, 2, False),      # two heads per 256-column tile
+    (3, 100, 264, 2, 1, True),        # ragged rows and K; the last tile holds one k head (rotated) and one v head (not)
+    (1, 2048, 4096, 32, 8, False),    # one Llama-3-8B sequence
+    (2, 77, 512, 3, 3, True),         # odd head counts: tiles that start inside q, k and v
+])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_qkv_projection_with_rope_equals_unfused_chain(cfg, dtype):
+    """One projection for q, k and v with the rotary embedding in its epilogue gives, bit for bit,
+    what matmul_add_bias followed by the rope kernel on the q / k column ranges gives, and leaves the
+    v columns as projected."""
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
+    from custom_cuda_kernals_b200.kernels.fused import matmul_add_bias_rope
+    from custom_cuda_kernals_b200.kernels.rope import rope_strided
+    from custom_cuda_kernals_b200.llama_block import rope_tables
+    b, s, hidden, hq, hkv, with_bias = cfg
+    qc, kc = hq * 128, hkv * 128
+    n = qc + 2 * kc
+    g = torch.Generator().manual_seed(hidden + s)
+    x = torch.randn(b * s, hidden, generator=g).to(dtype).to(DEV)
+    w = (0.05 * torch.randn(n, hidden, generator=g)).to(dtype).to(DEV)
+    bias = torch.randn(n, generator=g).to(dtype).to(DEV) if with_bias else None
+    cos, sin = rope_tables(s + 5, 128, 10000.0, DEV)
+    cos, sin = cos[5:], sin[5:]                                   # a slice of positions, as a continuation passes it
+    fused = matmul_add_bias_rope(x, w, bias, cos, sin, qc + kc).view(b, s, n)
+    plain = matmul_add_bias(x, w, bias).view(b, s, n)
+    q, k = rope_strided(plain[..., :qc].unflatten(-1, (hq, 128)), plain[..., qc:qc + kc].unflatten(-1, (hkv, 128)), cos, sin)
+    assert torch.equal(fused[..., :qc], q.flatten(-2))
+    assert torch.equal(fused[..., qc:qc + kc], k.flatten(-2))
+    assert torch.equal(fused[..., qc + kc:], plain[..., qc + kc:])
+    assert not torch.equal(fused[..., :qc], plain[..., :qc])
+    assert device_status_clean(fused)
+
+
+def test_fused_qkv_rope_rejects_what_it_cannot_run():
+    from custom_cuda_kernals_b200.kernels.fused import matmul_add_bias_rope
+    from custom_cuda_kernals_b200.llama_block import rope_tables
+    x = torch.randn(256, 512, device=DEV).to(torch.bfloat16)
+    w = torch.randn(512, 512, device=DEV).to(torch.bfloat16)
+    cos, sin = rope_tables(128, 128, 10000.0, DEV)
+    with pytest.raises(ValueError, match="multiples of 128"):
+        matmul_add_bias_rope(x, w[:500].contiguous(), None, cos, sin, 256)
+    with pytest.raises(ValueError, match="multiples of 128"):
+        matmul_add_bias_rope(x, w, None, cos, sin, 640)
+    with pytest.raises(ValueError, match="multiple of seq_len"):
+        matmul_add_bias_rope(x[:200].contiguous(), w, None, cos, sin, 256)
+    with pytest.raises(ValueError, match="seq_len, 64"):
+        matmul_add_bias_rope(x, w, None, cos[:, :32].contiguous(), sin[:, :32].contiguous(), 256)
+    with pytest.raises(ValueError, match="fp32"):
+        matmul_add_bias_rope(x, w, None, cos.half(), sin.half(), 256)
+    with pytest.raises(ValueError, match="fused path"):
+        matmul_add_bias_rope(x.float(), w.float(), None, cos, sin, 256)
+
+
 def test_fused_ops_reject_what_they_cannot_run():
     from custom_cuda_kernals_b200.kernels.fused import interleave_gate_up, matmul_add_bias_residual, matmul_swiglu
     x = torch.randn(16, 64, device=DEV)
