@@ -783,7 +783,7 @@ def run_ours(args, rank, world, local):
                        + m_rank * hid + 2 * ffn * hid + m_rank * ffn                          # gate-up + SwiGLU
                        + m_rank * ffn + hid * ffn + 2 * m_rank * hid)                         # down + residual
     line["roofline"] = {"kernel": f"gemm_pair_kernel<bf16> (tcgen05 GEMM, {gemm_calls // args.steps} launches per step: "
-                                  "qkv projection, o + residual, gate-up + SwiGLU, down + residual)", "bound": "tensor",
+                                  "qkv projection + RoPE, o + residual, gate-up + SwiGLU, down + residual)", "bound": "tensor",
                         "achieved": round(ach, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
                         "traffic": int(NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * gemm_bytes / 4),
                         "traffic_note": "bytes per launch (average of the step's 4 GEMM launches), scaled from an ncu "
