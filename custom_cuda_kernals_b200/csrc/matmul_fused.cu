@@ -335,6 +335,68 @@ struct EpiScaledBiasResidual {
     __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
 };
 
+// y = rope(round(acc * a_scale[row] * w_scale[col] + bias)) on the columns below rope_cols: the FP8 GEMM's
+// own epilogue followed by the rotation of EpiBiasRope, rounding where that chain rounds.
+template <typename T>
+struct EpiScaledBiasRope {
+    static constexpr bool kPairedHalves = true;
+    static constexpr int kPairStride = 64;
+    struct Params {
+        const float* a_scale;   // [m]
+        const float* w_scale;   // [n]
+        const T* bias;          // [n] or null
+        const float* cos_t;     // [seq_len, 64]
+        const float* sin_t;
+        T* y;
+        int64_t m, n, rope_cols;
+        int seq_len;
+        int vec_ok;
+    };
+    struct Thread { float a_scale; int pos; };
+    __device__ static __forceinline__ void tile_begin(const Params& p, Thread& th, const TileWork& w, float* scratch,
+                                                      int lane, int row_in_tile) {
+        const int64_t n0 = static_cast<int64_t>(w.n_tile) * kBN;
+#pragma unroll
+        for (int i = 0; i < kBN / 32; ++i) {
+            const int64_t col = n0 + lane + 32 * i;
+            const bool in = col < p.n;
+            scratch[lane + 32 * i] = in ? p.w_scale[col] : 0.0f;
+            scratch[kBN + lane + 32 * i] = (in && p.bias != nullptr) ? Store<T>::load1(p.bias + col) : 0.0f;
+        }
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        th.a_scale = row < p.m ? p.a_scale[row] : 0.0f;
+        th.pos = static_cast<int>(row % p.seq_len);
+    }
+    __device__ static __forceinline__ void chunk2(const Params& p, Thread& th, const TileWork& w, int row_in_tile, int c0,
+                                                  float (&lo)[32], float (&hi)[32], const float* scratch) {
+        const int64_t row = static_cast<int64_t>(w.m_tile) * kBM + row_in_tile;
+        const int64_t col = static_cast<int64_t>(w.n_tile) * kBN + c0;
+        if (row >= p.m || col >= p.n) return;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            lo[j] = Store<T>::round(fmaf(lo[j] * th.a_scale, scratch[c0 + j], scratch[kBN + c0 + j]));
+            hi[j] = Store<T>::round(fmaf(hi[j] * th.a_scale, scratch[c0 + 64 + j], scratch[kBN + c0 + 64 + j]));
+        }
+        if (col < p.rope_cols) {
+            const int64_t t = static_cast<int64_t>(th.pos) * 64 + (c0 & 63);
+            const float4* cp = reinterpret_cast<const float4*>(p.cos_t + t);
+            const float4* sp = reinterpret_cast<const float4*>(p.sin_t + t);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 c = __ldg(cp + q), sn = __ldg(sp + q);
+                rope_rotate(lo[4 * q], hi[4 * q], c.x, sn.x, lo[4 * q], hi[4 * q]);
+                rope_rotate(lo[4 * q + 1], hi[4 * q + 1], c.y, sn.y, lo[4 * q + 1], hi[4 * q + 1]);
+                rope_rotate(lo[4 * q + 2], hi[4 * q + 2], c.z, sn.z, lo[4 * q + 2], hi[4 * q + 2]);
+                rope_rotate(lo[4 * q + 3], hi[4 * q + 3], c.w, sn.w, lo[4 * q + 3], hi[4 * q + 3]);
+            }
+        }
+        T* out = p.y + row * p.n + col;
+        store32<T>(out, lo, col, p.n, p.vec_ok);
+        store32<T>(out + 64, hi, col + 64, p.n, p.vec_ok);
+    }
+    __device__ static __forceinline__ void tile_end(const Params&, Thread&, const TileWork&, int) {}
+};
+
 // y = silu(gate) * up with gate / up = acc * a_scale[row] * w_scale[fused weight row], rounded where
 // the chain (two FP8 GEMMs, then swiglu) rounds; and, for the per-token quantiser of the down
 // projection's input, the largest stored magnitude per row and tile of 128 output columns
@@ -666,6 +728,36 @@ extern "C" int32_t launch_matmul_swiglu_fp8_fwd(const uint8_t* a_codes, const fl
         using T = __half;
         EpiScaledSwiGLU<T>::Params ep{a_scale, w_scale, static_cast<T*>(y), row_amax, m, f, vec_ok};
         return run_fused_fp8<EpiScaledSwiGLU<T>>(a_codes, w_gate_up, m, k, 2 * f, ep, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+extern "C" int32_t launch_matmul_add_bias_rope_fp8_fwd(const uint8_t* a_codes, const float* a_scale,
+                                                       const uint8_t* w_codes, const float* w_scale, const void* bias,
+                                                       const float* cos_table, const float* sin_table, void* y,
+                                                       int64_t m, int64_t k, int64_t n, int64_t rope_cols,
+                                                       int64_t seq_len, int32_t out_dtype, void* stream) {
+    using namespace cck;
+    using namespace cck::tc;
+    if (m <= 0 || k <= 0 || n <= 0) return cudaSuccess;
+    if (cos_table == nullptr || sin_table == nullptr || n % 128 != 0 || rope_cols % 128 != 0 || rope_cols < 0 ||
+        rope_cols > n || seq_len <= 0 || seq_len >= (1LL << 31) || !aligned16(cos_table) || !aligned16(sin_table) ||
+        k % 16 != 0 || !aligned16(a_codes) || !aligned16(w_codes) || m >= (1LL << 31) || n >= (1LL << 31) ||
+        k >= (1LL << 31))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int vec_ok = aligned16(y) ? 1 : 0;
+    if (out_dtype == kBF16) {
+        using T = __nv_bfloat16;
+        EpiScaledBiasRope<T>::Params ep{a_scale, w_scale, static_cast<const T*>(bias), cos_table, sin_table,
+                                        static_cast<T*>(y), m, n, rope_cols, static_cast<int>(seq_len), vec_ok};
+        return run_fused_fp8<EpiScaledBiasRope<T>>(a_codes, w_codes, m, k, n, ep, s);
+    }
+    if (out_dtype == kF16) {
+        using T = __half;
+        EpiScaledBiasRope<T>::Params ep{a_scale, w_scale, static_cast<const T*>(bias), cos_table, sin_table,
+                                        static_cast<T*>(y), m, n, rope_cols, static_cast<int>(seq_len), vec_ok};
+        return run_fused_fp8<EpiScaledBiasRope<T>>(a_codes, w_codes, m, k, n, ep, s);
     }
     return cudaErrorInvalidValue;
 }

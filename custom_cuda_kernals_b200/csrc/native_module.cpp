@@ -1107,6 +1107,41 @@ void matmul_add_bias_residual_fp8_fwd(const at::Tensor& a, const at::Tensor& a_s
                                                          m, k, n, odt, l.stream));
 }
 
+void matmul_add_bias_rope_fp8_fwd(const at::Tensor& a, const at::Tensor& a_scale, const at::Tensor& w,
+                                  const at::Tensor& w_scale, const c10::optional<at::Tensor>& bias, const at::Tensor& cos,
+                                  const at::Tensor& sin, const at::Tensor& y, int64_t rope_cols) {
+    auto [m, k, n] = check_fp8_operands(a, a_scale, w, w_scale);
+    const int32_t odt = tag_of("y", y);
+    if (odt != CCK_BF16 && odt != CCK_F16) value_error("unsupported dtype 'y must be bfloat16 or float16'");
+    expect_f32("cos", tag_of("cos", cos), " (RoPE tables are always fp32)");
+    expect_f32("sin", tag_of("sin", sin), " (RoPE tables are always fp32)");
+    const bool has_bias = bias.has_value() && bias->defined();
+    if (has_bias) expect_same_dtype("bias", tag_of("bias", *bias), odt);
+    if (k % 16 != 0) value_error("shape mismatch: the fused FP8 path needs K to be a multiple of 16");
+    if (n % 128 != 0 || rope_cols % 128 != 0 || rope_cols < 0 || rope_cols > n)
+        value_error("shape mismatch: heads are 128 columns wide: weight rows (" + std::to_string(n) + ") and rope_cols (" +
+                    std::to_string(rope_cols) + ") must be multiples of 128 with rope_cols <= rows");
+    if (y.dim() != 2 || y.size(0) != m || y.size(1) != n)
+        value_error("shape mismatch: y shape " + shape_str(y) + " must be [" + std::to_string(m) + ", " + std::to_string(n) + "]");
+    if (cos.dim() != 2 || sin.dim() != 2 || cos.size(1) != 64 || sin.size(1) != 64 || cos.size(0) != sin.size(0) ||
+        cos.size(0) < 1 || m % cos.size(0) != 0)
+        value_error("shape mismatch: cos/sin must be [seq_len, 64] with the rows of a_fp8 (" + std::to_string(m) +
+                    ") a multiple of seq_len; got cos=" + shape_str(cos) + ", sin=" + shape_str(sin));
+    if (has_bias && (bias->dim() != 1 || bias->size(0) != n))
+        value_error("shape mismatch: bias shape " + shape_str(*bias) + " must be [" + std::to_string(n) + "]");
+    at::Tensor none;
+    Launch l(a, {&a_scale, &w, &w_scale, &cos, &sin, &y, has_bias ? &*bias : &none});
+    check_launch("launch_matmul_add_bias_rope_fp8_fwd",
+                 launch_matmul_add_bias_rope_fp8_fwd(static_cast<const uint8_t*>(a.data_ptr()),
+                                                     static_cast<const float*>(a_scale.data_ptr()),
+                                                     static_cast<const uint8_t*>(w.data_ptr()),
+                                                     static_cast<const float*>(w_scale.data_ptr()),
+                                                     has_bias ? bias->data_ptr() : nullptr,
+                                                     static_cast<const float*>(cos.data_ptr()),
+                                                     static_cast<const float*>(sin.data_ptr()), y.data_ptr(), m, k, n,
+                                                     rope_cols, cos.size(0), odt, l.stream));
+}
+
 // y = op(a) op(b)^T with operands read as stored (transposed or not); see launch_matmul_general_fwd
 void matmul_general_fwd(const at::Tensor& a, const at::Tensor& b, const at::Tensor& y, bool a_is_km, bool b_is_kn,
                         bool accumulate) {
@@ -1223,6 +1258,9 @@ PYBIND11_MODULE(_native, m) {
           py::arg("w_scale"), py::arg("y"), py::arg("row_amax").none(true));
     m.def("matmul_add_bias_residual_fp8_fwd", &matmul_add_bias_residual_fp8_fwd, py::arg("a_fp8"), py::arg("a_scale"),
           py::arg("w_fp8"), py::arg("w_scale"), py::arg("bias").none(true), py::arg("residual"), py::arg("y"));
+    m.def("matmul_add_bias_rope_fp8_fwd", &matmul_add_bias_rope_fp8_fwd, py::arg("a_fp8"), py::arg("a_scale"),
+          py::arg("w_fp8"), py::arg("w_scale"), py::arg("bias").none(true), py::arg("cos"), py::arg("sin"), py::arg("y"),
+          py::arg("rope_cols"));
     m.def("matmul_general_fwd", &matmul_general_fwd, py::arg("a"), py::arg("b"), py::arg("y"), py::arg("a_is_km"),
           py::arg("b_is_kn"), py::arg("accumulate"));
     m.def("gemm_stat_tiles", [](int64_t n) { return cck_gemm_stat_tiles(n); }, py::arg("n"));

@@ -10,7 +10,7 @@ from .. import _native
 
 __all__ = ["interleave_gate_up", "matmul_swiglu", "matmul_add_bias_residual", "matmul_add_bias_rope", "matmul_add_bias_stats",
            "rmsnorm_from_stats", "fp8_quant_token_from_amax", "matmul_general", "rmsnorm_fp8_quant",
-           "matmul_swiglu_fp8", "matmul_add_bias_residual_fp8", "GATE_UP_BLOCK"]
+           "matmul_swiglu_fp8", "matmul_add_bias_residual_fp8", "matmul_add_bias_rope_fp8", "GATE_UP_BLOCK"]
 
 GATE_UP_BLOCK = 128
 
@@ -158,6 +158,16 @@ def matmul_swiglu_fp8(a_fp8: torch.Tensor, a_scale: torch.Tensor, w_gate_up_fp8:
     am = torch.empty((f // GATE_UP_BLOCK, m), dtype=torch.float32, device=a_fp8.device) if amax else None
     _native.matmul_swiglu_fp8_fwd(a_fp8, a_scale, w_gate_up_fp8, w_scale, y, am)
     return (y, am) if amax else y
+
+
+def matmul_add_bias_rope_fp8(a_fp8: torch.Tensor, a_scale: torch.Tensor, w_fp8: torch.Tensor, w_scale: torch.Tensor,
+                             bias: torch.Tensor | None, cos: torch.Tensor, sin: torch.Tensor, rope_cols: int,
+                             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``matmul_add_bias_rope`` with e4m3 operands (per-token / per-output-channel scales): equals
+    ``rope_strided`` on the q / k column ranges of ``matmul_add_bias_fp8(...)`` bit for bit."""
+    y = torch.empty((a_fp8.shape[0], w_fp8.shape[0]), dtype=out_dtype, device=a_fp8.device)
+    _native.matmul_add_bias_rope_fp8_fwd(a_fp8, a_scale, w_fp8, w_scale, bias, cos, sin, y, rope_cols)
+    return y
 
 
 def matmul_add_bias_residual_fp8(a_fp8: torch.Tensor, a_scale: torch.Tensor, w_fp8: torch.Tensor, w_scale: torch.Tensor,

@@ -29,8 +29,8 @@ import torch.nn.functional as F
 
 from .kernels.fp8_quant import fp8_quant
 from .kernels.fused import (GATE_UP_BLOCK, fp8_quant_token_from_amax, interleave_gate_up, matmul_add_bias_residual,
-                            matmul_add_bias_residual_fp8, matmul_add_bias_rope, matmul_swiglu, matmul_swiglu_fp8,
-                            rmsnorm_fp8_quant)
+                            matmul_add_bias_residual_fp8, matmul_add_bias_rope, matmul_add_bias_rope_fp8, matmul_swiglu,
+                            matmul_swiglu_fp8, rmsnorm_fp8_quant)
 from .kernels.matmul_add_bias import matmul_add_bias, matmul_add_bias_fp8
 from .kernels.rmsnorm_residual import rmsnorm, rmsnorm_residual
 from .kernels.rope import rope, rope_strided
@@ -412,8 +412,9 @@ class LlamaBlockFP8:
         self.down = quant(weights["down_proj"])
         if fused:
             del self.gate, self.up
-        #: this library's kernels per forward: 2 norm+quant, 2 quantisers, rope, 4 GEMMs
-        self.launches_per_forward = 9 if fused else 15
+        #: this library's kernels per forward: 2 norm+quant, 2 quantisers, 4 GEMMs, and a rope kernel
+        #: unless the heads are 128 wide (the rotation then rides in the QKV epilogue)
+        self.launches_per_forward = (8 if self.head_dim == 128 else 9) if fused else 15
 
     def forward(self, x: torch.Tensor, timer: OpTimer | None = None) -> torch.Tensor:
         t = timer if timer is not None else _NoTimer
@@ -423,12 +424,18 @@ class LlamaBlockFP8:
             h8, hs = t.run("rmsnorm_quant", rmsnorm_fp8_quant, x2, self.w_in, self.eps)
         else:
             h8, hs = fp8_quant(rmsnorm(x2, self.w_in, self.eps), "e4m3", "token")
-        qkv = t.run("gemm_fp8", matmul_add_bias_fp8, h8, hs, *self.qkv).view(b, s, -1)
         qc, kc = self.q_cols, self.kv_cols
+        rope_in_gemm = self.fused and self.head_dim == 128
+        if rope_in_gemm:
+            qkv = t.run("gemm_fp8_rope", matmul_add_bias_rope_fp8, h8, hs, *self.qkv, None, self.cos[:s], self.sin[:s],
+                        qc + kc).view(b, s, -1)
+        else:
+            qkv = t.run("gemm_fp8", matmul_add_bias_fp8, h8, hs, *self.qkv).view(b, s, -1)
         q = qkv[..., :qc].unflatten(-1, (self.n_heads, self.head_dim))
         k = qkv[..., qc:qc + kc].unflatten(-1, (self.n_kv_heads, self.head_dim))
         v = qkv[..., qc + kc:].unflatten(-1, (self.n_kv_heads, self.head_dim))
-        q, k = t.run("rope", rope_strided, q, k, self.cos[:s], self.sin[:s])
+        if not rope_in_gemm:
+            q, k = t.run("rope", rope_strided, q, k, self.cos[:s], self.sin[:s])
         att = t.run("sdpa", F.scaled_dot_product_attention, q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                     is_causal=True, enable_gqa=self.n_heads != self.n_kv_heads)
         att = att.transpose(1, 2).contiguous().view(b * s, hid)

@@ -313,6 +313,16 @@ int32_t launch_rmsnorm_fp8_quant_token_fwd(const void* x, const void* weight, co
                                            void* y, uint8_t* x_fp8, float* scale, int64_t rows, int64_t cols,
                                            float eps, int32_t dtype, int32_t fp8_format, void* stream);
 
+/* launch_matmul_add_bias_rope_fwd with e4m3 operands: y = rope(a_scale[row] * w_scale[col] * (codes @
+ * codes^T) + bias) on the columns below rope_cols, as projected on the rest; identical to
+ * launch_matmul_add_bias_fp8_fwd followed by launch_rope_strided_fwd on the q and k column ranges.
+ * out_dtype CCK_BF16 or CCK_F16; n % 128 == 0, rope_cols % 128 == 0, k % 16 == 0, 16-byte aligned
+ * codes and tables; otherwise cudaErrorInvalidValue.  No reference counterpart. */
+int32_t launch_matmul_add_bias_rope_fp8_fwd(const uint8_t* a_codes, const float* a_scale, const uint8_t* w_codes,
+                                            const float* w_scale, const void* bias, const float* cos_table,
+                                            const float* sin_table, void* y, int64_t m, int64_t k, int64_t n,
+                                            int64_t rope_cols, int64_t seq_len, int32_t out_dtype, void* stream);
+
 /* FP8 forms of launch_matmul_swiglu_fwd and launch_matmul_add_bias_residual_fwd: e4m3 codes with one
  * float32 scale per row of each operand (as launch_fp8_quant_token_fwd produces; the weight's scales
  * are per output channel).  Results equal, bit for bit, launch_matmul_add_bias_fp8_fwd followed by

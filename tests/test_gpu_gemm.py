@@ -303,6 +303,35 @@ def test_fused_qkv_projection_with_rope_equals_unfused_chain(cfg, dtype):
     assert device_status_clean(fused)
 
 
+@pytest.mark.parametrize("cfg", [(2, 192, 1024, 8, 2, False), (3, 100, 272, 2, 1, True), (1, 2048, 4096, 32, 8, False)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_fp8_qkv_projection_with_rope_equals_unfused_chain(cfg, dtype):
+    """The same with e4m3 operands: FP8 projection with RoPE in its epilogue == matmul_add_bias_fp8
+    followed by the rope kernel on the q / k column ranges, bit for bit."""
+    from custom_cuda.kernels.fp8_quant import fp8_quant
+    from custom_cuda.kernels.matmul_add_bias import matmul_add_bias_fp8
+    from custom_cuda_kernals_b200.kernels.fused import matmul_add_bias_rope_fp8
+    from custom_cuda_kernals_b200.kernels.rope import rope_strided
+    from custom_cuda_kernals_b200.llama_block import rope_tables
+    b, s, hidden, hq, hkv, with_bias = cfg
+    qc, kc = hq * 128, hkv * 128
+    n = qc + 2 * kc
+    g = torch.Generator().manual_seed(hidden + s)
+    x = torch.randn(b * s, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    w = (0.05 * torch.randn(n, hidden, generator=g)).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(n, generator=g).to(dtype).to(DEV) if with_bias else None
+    a8, a_s = fp8_quant(x, "e4m3", "token")
+    w8, w_s = fp8_quant(w, "e4m3", "token")
+    cos, sin = rope_tables(s, 128, 10000.0, DEV)
+    fused = matmul_add_bias_rope_fp8(a8, a_s, w8, w_s, bias, cos, sin, qc + kc, out_dtype=dtype).view(b, s, n)
+    plain = matmul_add_bias_fp8(a8, a_s, w8, w_s, bias, out_dtype=dtype).view(b, s, n)
+    q, k = rope_strided(plain[..., :qc].unflatten(-1, (hq, 128)), plain[..., qc:qc + kc].unflatten(-1, (hkv, 128)), cos, sin)
+    assert torch.equal(fused[..., :qc], q.flatten(-2))
+    assert torch.equal(fused[..., qc:qc + kc], k.flatten(-2))
+    assert torch.equal(fused[..., qc + kc:], plain[..., qc + kc:])
+    assert device_status_clean(fused)
+
+
 def test_fused_qkv_rope_rejects_what_it_cannot_run():
     from custom_cuda_kernals_b200.kernels.fused import matmul_add_bias_rope
     from custom_cuda_kernals_b200.llama_block import rope_tables
