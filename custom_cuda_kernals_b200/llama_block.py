@@ -308,7 +308,7 @@ class LlamaBlock:
         self.forward_host_async(x_host, out_host, chunks, seq_pieces).wait()
         return out_host
 
-    def forward_host_async(self, x_host: torch.Tensor, out_host: torch.Tensor, chunks: int | None = 1,
+    def forward_host_async(self, x_host: torch.Tensor, out_host: torch.Tensor, chunks: int | None = 2,
                            seq_pieces: int | None = 1) -> "HostStep":
         """``forward_host`` without the final wait: enqueues the copies and kernels of one step and
         returns a ``HostStep`` at once.  ``step.wait()`` blocks the host until ``out_host`` is
@@ -317,11 +317,13 @@ class LlamaBlock:
         under this step's kernels, this step's copy-out under the next step's - which is what hides
         the transfers when a step is a single sequence (one sequence per rank at 8 GPUs) and
         nothing inside the step can.  Give every step in flight its own ``out_host``; two in
-        flight are enough to keep all three streams busy.  By default the step is one item
-        (``chunks=1``, ``seq_pieces=1``): with the neighbouring steps to overlap with, cutting it
-        up only shrinks the GEMMs and adds launches.  Measured on one B200, per step: one
-        2048-token sequence 0.78 ms whole and 1.01 ms in two runs of positions, against 0.72 ms of
-        kernels and 1.32 ms for the blocking call; eight sequences 6.1 ms as one item or two,
+        flight are enough to keep all three streams busy.  By default the step is cut into two
+        halves of its sequences (``chunks=2``) and sequences stay whole (``seq_pieces=1``): with the
+        neighbouring steps to overlap with, finer cuts only shrink the GEMMs and add launches, while
+        two halves cost nothing in the steady state and halve what is exposed when the pipeline
+        starts and drains (the first copy-in, the last copy-out).  Measured on one B200, per step:
+        one 2048-token sequence 0.78 ms whole and 1.01 ms in two runs of positions, against 0.72 ms
+        of kernels and 1.32 ms for the blocking call; eight sequences 6.1 ms as one item or two,
         6.3-6.5 ms as four or as the blocking call's 1-2-2-2-1 plan, against 5.7 ms of kernels and
         6.7 ms for the blocking call.  ``chunks=None`` / ``seq_pieces=None`` select the blocking
         call's plan."""
