@@ -889,7 +889,7 @@ def run_ep_exchange(rank, world, tokens=8192, k=2, hidden=4096, iters=10):
         emit(line)
 
 
-PROFILE_CASES = ("gemm", "gemm_fp8", "gemm_transposed", "gemm_decode", "lce", "lce_dlogits", "swiglu", "rmsnorm", "rmsnorm_fp8", "rope",
+PROFILE_CASES = ("gemm", "gemm_fp8", "gemm_transposed", "gemm_decode", "gemm_rope", "lce", "lce_dlogits", "swiglu", "rmsnorm", "rmsnorm_fp8", "rope",
                  "fp8_token", "fp8_block", "swiglu_bwd", "rmsnorm_bwd", "moe_router", "token_gather", "token_combine")
 
 
@@ -924,6 +924,11 @@ def run_profile_case(name, launches=3):
     elif name == "gemm_decode":       # 64 tokens against a 4096 x 4096 weight (34 MB; the flush below evicts it between launches)
         a, w, b = rn(64, 4096), rn(4096, 4096, scale=0.02), rn(4096, scale=0.02)
         fn = lambda: matmul_add_bias(a, w, b)
+    elif name == "gemm_rope":         # the block's q/k/v projection with RoPE in the epilogue, two sequences: 34 + 50 + 50 MB
+        from custom_cuda_kernals_b200.kernels.fused import matmul_add_bias_rope
+        a, w = rn(4096, 4096), rn(6144, 4096, scale=0.02)
+        cos, sin = rope_tables(2048, 128, 500000.0, dev)
+        fn = lambda: matmul_add_bias_rope(a, w, None, cos, sin, 5120)
     elif name == "rmsnorm_fp8":       # norm + per-token quantiser in one pass, the block's token count: 134 MB in, 67 MB out
         from custom_cuda_kernals_b200.kernels.fused import rmsnorm_fp8_quant
         x, w = rn(16384, 4096), rn(4096)
