@@ -124,26 +124,44 @@ moe_router_kernel(const T* __restrict__ logits, float* __restrict__ topk_w, int6
         CCK_CE(2, 4) CCK_CE(3, 5)
         CCK_CE(3, 4)
 #undef CCK_CE
-        for (int j = 0; j < k; ++j) {
-            const uint32_t top = __reduce_max_sync(0xffffffffu, key[0]);
-            if (key[0] == top) {                 // keys are unique: exactly one lane
-#pragma unroll
-                for (int i = 0; i + 1 < kRouterVals; ++i) key[i] = key[i + 1];
-                key[kRouterVals - 1] = 0u;
-            }
+        auto decode = [&](uint32_t top, float& p, int& e) {
             const uint32_t ord = top >> 16;
             const float best = Bits16<T>::to_float((ord & 0x8000u) ? (ord & 0x7fffu) : (~ord & 0xffffu));
-            const float p = __expf(best - mx) * inv_sum;
-            picked += p;
-            const int e = 255 - static_cast<int>(top & 0xffu);
-            if (in_regs) {
-                if (sub == j) {
-                    my_p = p;
-                    my_e = e;
+            p = __expf(best - mx) * inv_sum;
+            e = 255 - static_cast<int>(top & 0xffu);
+        };
+        if (in_regs) {
+            // the rounds only move keys: lane j keeps the j-th winner's key and turns it into a
+            // probability and an expert id once, after the loop
+            uint32_t my_top = 0u;
+            for (int j = 0; j < k; ++j) {
+                const uint32_t top = __reduce_max_sync(0xffffffffu, key[0]);
+                if (key[0] == top) {             // keys are unique: exactly one lane
+#pragma unroll
+                    for (int i = 0; i + 1 < kRouterVals; ++i) key[i] = key[i + 1];
+                    key[kRouterVals - 1] = 0u;
                 }
-            } else if (live && sub == j % L) {
-                topk_w[token * k + j] = p;
-                topk_i[token * k + j] = e;
+                if (sub == j) my_top = top;
+            }
+            decode(my_top, my_p, my_e);
+            if (sub >= k) my_p = 0.0f;
+            for (int j = 0; j < k; ++j) picked += __shfl_sync(0xffffffffu, my_p, j);   // in selection order
+        } else {
+            for (int j = 0; j < k; ++j) {
+                const uint32_t top = __reduce_max_sync(0xffffffffu, key[0]);
+                if (key[0] == top) {
+#pragma unroll
+                    for (int i = 0; i + 1 < kRouterVals; ++i) key[i] = key[i + 1];
+                    key[kRouterVals - 1] = 0u;
+                }
+                float p;
+                int e;
+                decode(top, p, e);
+                picked += p;
+                if (live && sub == j % L) {
+                    topk_w[token * k + j] = p;
+                    topk_i[token * k + j] = e;
+                }
             }
         }
     } else {
