@@ -39,8 +39,8 @@ template <int BT> struct DecShape {
 template <typename T, int BT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                   const T* __restrict__ bias, T* __restrict__ y, int64_t m, int64_t n, int k_blocks, uint32_t idesc,
-                   unsigned int* status) {
+                   const T* __restrict__ bias, const T* __restrict__ residual, T* __restrict__ y, int64_t m, int64_t n,
+                   int k_blocks, uint32_t idesc, unsigned int* status) {
     constexpr int kStageBytes = DecShape<BT>::kStageBytes;
     constexpr int kDecStages = DecShape<BT>::kStages;
     constexpr int kDecTmemCols = DecShape<BT>::kTmemCols;
@@ -158,10 +158,16 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const int64_t feature = static_cast<int64_t>(n_tile) * kBM + row_in_tile;
         if (all_ok && feature < n) {
             const float b = bias != nullptr ? Store<T>::load1(bias + feature) : 0.0f;
+            // + bias, rounded; with a residual: + residual[t, feature], rounded again - the roundings of
+            // the bias epilogue followed by an elementwise add in the storage type
+            auto put = [&](int64_t at, float sum) {
+                if (residual == nullptr) Store<T>::store1(y + at, sum + b);
+                else Store<T>::store1(y + at, Store<T>::round(sum + b) + Store<T>::load1(residual + at));
+            };
             if (splits == 1) {
 #pragma unroll
                 for (int t = 0; t < BT; ++t)
-                    if (t < m) Store<T>::store1(y + static_cast<int64_t>(t) * n + feature, acc[t / 32][t % 32] + b);
+                    if (t < m) put(static_cast<int64_t>(t) * n + feature, acc[t / 32][t % 32]);
             } else {
                 constexpr int kPlanes = BT / 4;
                 const int q0 = static_cast<int>(rank) * kPlanes / static_cast<int>(splits);
@@ -176,11 +182,11 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                         sum.z += v.z;
                         sum.w += v.w;
                     }
-                    T* dst = y + static_cast<int64_t>(4 * q) * n + feature;
-                    Store<T>::store1(dst, sum.x + b);
-                    if (4 * q + 1 < m) Store<T>::store1(dst + n, sum.y + b);
-                    if (4 * q + 2 < m) Store<T>::store1(dst + 2 * n, sum.z + b);
-                    if (4 * q + 3 < m) Store<T>::store1(dst + 3 * n, sum.w + b);
+                    const int64_t at = static_cast<int64_t>(4 * q) * n + feature;
+                    put(at, sum.x);
+                    if (4 * q + 1 < m) put(at + n, sum.y);
+                    if (4 * q + 2 < m) put(at + 2 * n, sum.z);
+                    if (4 * q + 3 < m) put(at + 3 * n, sum.w);
                 }
             }
         }
@@ -216,8 +222,8 @@ inline int decode_split(int64_t tiles, int k_blocks) {
 }
 
 template <typename T, int BT>
-cudaError_t launch_decode_bt(const CUtensorMap& tw, const CUtensorMap& tx, const T* bias, T* y, int64_t m, int64_t n,
-                             int64_t k_elems, uint32_t fmt, cudaStream_t s) {
+cudaError_t launch_decode_bt(const CUtensorMap& tw, const CUtensorMap& tx, const T* bias, const T* residual, T* y,
+                             int64_t m, int64_t n, int64_t k_elems, uint32_t fmt, cudaStream_t s) {
     auto kern = gemm_decode_kernel<T, BT>;
     constexpr int kSmem = DecShape<BT>::kSmemBytes;
     static bool configured[kMaxDevices] = {};
@@ -246,13 +252,14 @@ cudaError_t launch_decode_bt(const CUtensorMap& tw, const CUtensorMap& tx, const
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     const uint32_t idesc = ptx::instr_desc(fmt, fmt, kBM, BT);
-    return cudaLaunchKernelEx(&cfg, kern, tw, tx, bias, y, m, n, k_blocks, idesc, st);
+    return cudaLaunchKernelEx(&cfg, kern, tw, tx, bias, residual, y, m, n, k_blocks, idesc, st);
 }
 
 // x [m <= 128, k], W [n, k], 16-bit; k % 8 == 0 and 16-byte aligned operands (the caller checked).
+// residual [m, n] (optional) is added after the bias epilogue's rounding.
 template <typename T>
 cudaError_t launch_decode(const void* x, const void* w, const T* bias, T* y, int64_t m, int64_t k, int64_t n,
-                          CUtensorMapDataType dt, uint32_t fmt, cudaStream_t s) {
+                          CUtensorMapDataType dt, uint32_t fmt, cudaStream_t s, const T* residual = nullptr) {
     const int bt = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
     CUtensorMap tw, tx;
     cudaError_t e = make_tmap(&tw, dt, 2, w, n, k, kBM);
@@ -260,10 +267,10 @@ cudaError_t launch_decode(const void* x, const void* w, const T* bias, T* y, int
     e = make_tmap(&tx, dt, 2, x, m, k, bt);
     if (e != cudaSuccess) return e;
     switch (bt) {
-        case 16: return launch_decode_bt<T, 16>(tw, tx, bias, y, m, n, k, fmt, s);
-        case 32: return launch_decode_bt<T, 32>(tw, tx, bias, y, m, n, k, fmt, s);
-        case 64: return launch_decode_bt<T, 64>(tw, tx, bias, y, m, n, k, fmt, s);
-        default: return launch_decode_bt<T, 128>(tw, tx, bias, y, m, n, k, fmt, s);
+        case 16: return launch_decode_bt<T, 16>(tw, tx, bias, residual, y, m, n, k, fmt, s);
+        case 32: return launch_decode_bt<T, 32>(tw, tx, bias, residual, y, m, n, k, fmt, s);
+        case 64: return launch_decode_bt<T, 64>(tw, tx, bias, residual, y, m, n, k, fmt, s);
+        default: return launch_decode_bt<T, 128>(tw, tx, bias, residual, y, m, n, k, fmt, s);
     }
 }
 

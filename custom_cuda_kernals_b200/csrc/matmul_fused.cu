@@ -20,7 +20,7 @@
 // read again for gate/up, M*N*sizeof(T) written and read again for the residual add.
 #include <type_traits>
 
-#include "gemm_tcgen05.cuh"
+#include "gemm_decode.cuh"
 
 namespace cck {
 namespace tc {
@@ -611,12 +611,19 @@ extern "C" int32_t launch_matmul_add_bias_residual_fwd(const void* x, const void
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int vec_ok = (n % 8 == 0 && aligned16(y) && aligned16(residual)) ? 1 : 0;
     if (dtype == kBF16) {
+        if (m <= kDecMaxTokens && splitk_enabled(m))        // decode-sized batch: weight rows on the M side, K split over a cluster
+            return launch_decode<__nv_bfloat16>(x, weight, static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(y),
+                                                m, k, n, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 1u, s,
+                                                static_cast<const __nv_bfloat16*>(residual));
         EpiBiasResidual<__nv_bfloat16>::Params ep{static_cast<const __nv_bfloat16*>(bias),
                                                   static_cast<const __nv_bfloat16*>(residual),
                                                   static_cast<__nv_bfloat16*>(y), m, n, vec_ok};
         return run_fused<__nv_bfloat16, EpiBiasResidual<__nv_bfloat16>>(x, weight, m, k, n, ep, s);
     }
     if (dtype == kF16) {
+        if (m <= kDecMaxTokens && splitk_enabled(m))
+            return launch_decode<__half>(x, weight, static_cast<const __half*>(bias), static_cast<__half*>(y), m, k, n,
+                                         CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 0u, s, static_cast<const __half*>(residual));
         EpiBiasResidual<__half>::Params ep{static_cast<const __half*>(bias), static_cast<const __half*>(residual),
                                            static_cast<__half*>(y), m, n, vec_ok};
         return run_fused<__half, EpiBiasResidual<__half>>(x, weight, m, k, n, ep, s);

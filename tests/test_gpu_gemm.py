@@ -252,7 +252,8 @@ def test_fused_gate_up_swiglu_equals_unfused_chain(shape, dtype):
     assert device_status_clean(fused)
 
 
-@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 1408, 1024), (131, 72, 777), (4096, 14336, 4096)])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 1408, 1024), (131, 72, 777), (4096, 14336, 4096),
+                                   (16, 4096, 4096), (100, 1032, 520), (128, 512, 1024), (1, 14336, 4096)])   # the last four: decode kernel
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_fused_residual_add_equals_unfused_chain(shape, with_bias):
     from custom_cuda.kernels.matmul_add_bias import matmul_add_bias
