@@ -243,14 +243,18 @@ class LlamaBlock:
         cos, sin = self.cos[pos_offset:pos_offset + s], self.sin[pos_offset:pos_offset + s]
         if self.fused:       # one projection for q, k and v
             qc, kc = self.q_cols, self.kv_cols
-            if self.rope_in_gemm:    # ... with the rotary embedding applied in its epilogue
+            # ... with the rotary embedding applied in its epilogue - except for decode-sized calls
+            # (at most 128 tokens), where the plain projection runs on the weight-streaming decode
+            # kernel, three times as fast as full-width tiles there, and a rope kernel follows
+            rope_in_gemm = self.rope_in_gemm and b * s > 128
+            if rope_in_gemm:
                 qkv = t.run("gemm_rope", matmul_add_bias_rope, h, self.w_qkv, None, cos, sin, qc + kc).view(b, s, -1)
             else:
                 qkv = t.run("gemm", matmul_add_bias, h, self.w_qkv).view(b, s, -1)
             q = qkv[..., :qc].unflatten(-1, (self.n_heads, self.head_dim))
             k = qkv[..., qc:qc + kc].unflatten(-1, (self.n_kv_heads, self.head_dim))
             v = qkv[..., qc + kc:].unflatten(-1, (self.n_kv_heads, self.head_dim))
-            if not self.rope_in_gemm:    # rope reads its q / k column ranges in place
+            if not rope_in_gemm:         # rope reads its q / k column ranges in place
                 q, k = t.run("rope", rope_strided, q, k, cos, sin)
         else:
             q = t.run("gemm", matmul_add_bias, h, w["q_proj"]).view(b, s, self.n_heads, self.head_dim)
