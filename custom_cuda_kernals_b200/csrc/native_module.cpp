@@ -440,8 +440,10 @@ int64_t token_stride_of(const char* name, const at::Tensor& t) {
                     c10::DeviceTypeName(t.device().type(), true) + "'");
     if (t.dim() != 4) value_error(std::string("shape mismatch: ") + name + " must be 4-D [batch, seq_len, heads, head_dim], got " + shape_str(t));
     const int64_t s = t.size(1), h = t.size(2), d = t.size(3);
-    const int64_t ts = t.stride(1);
-    const bool ok = t.stride(3) == 1 && (h == 1 || t.stride(2) == d) && (t.size(0) == 1 || t.stride(0) == s * ts) && ts >= h * d;
+    // a dimension of size 1 carries no usable stride: one position per sequence is spaced by the batch stride
+    const int64_t ts = s > 1 ? t.stride(1) : (t.size(0) > 1 ? t.stride(0) : h * d);
+    const bool ok = t.stride(3) == 1 && (h == 1 || t.stride(2) == d) &&
+                    (t.size(0) == 1 || s == 1 || t.stride(0) == s * ts) && ts >= h * d;
     if (!ok) value_error(std::string("argument '") + name + "' must have contiguous heads per token and evenly spaced tokens");
     return ts;
 }

@@ -120,6 +120,32 @@ def test_block_is_deterministic_and_batch_independent():
         steps[-1].input_consumed.synchronize()
 
 
+def test_decode_sized_steps_through_a_kv_cache_match_the_whole_sequence():
+    """One new token per sequence against a filled KV cache (the decode-sized path: plain QKV
+    projection and projection + residual on the weight-streaming kernel, a rope kernel on views
+    with one position per sequence) gives the rows the whole-sequence call gives, to the block
+    tolerance.  The unfused chain agrees to that tolerance as well, not bit for bit: at these sizes
+    its gate / up projections split K over a cluster while the fused gate-up GEMM does not."""
+    from custom_cuda_kernals_b200.llama_block import LlamaBlock
+    cfg = dict(workloads.LLAMA3_8B, hidden=1024, ffn=2816, n_heads=8, n_kv_heads=2, head_dim=128)
+    wd = {k: v.to(DEV) for k, v in workloads.block_weights(cfg).items()}
+    block = LlamaBlock(wd, 8, 2, cfg["eps"], cfg["theta"], max_seq_len=256)
+    chain = LlamaBlock(wd, 8, 2, cfg["eps"], cfg["theta"], max_seq_len=256, fused=False)
+    x = workloads.block_input(3, 200, 1024).to(DEV)
+    with torch.no_grad():
+        whole = block(x)
+        caches = [tuple(torch.zeros(3, 256, 2, 128, dtype=torch.bfloat16, device=DEV) for _ in range(2)) for _ in range(2)]
+        first = block(x[:, :197].contiguous(), kv_cache=caches[0])
+        chain(x[:, :197].contiguous(), kv_cache=caches[1])
+        assert torch.equal(first, whole[:, :197])
+        for pos in (197, 198, 199):
+            step = block(x[:, pos:pos + 1].contiguous(), pos_offset=pos, kv_cache=caches[0])
+            same = chain(x[:, pos:pos + 1].contiguous(), pos_offset=pos, kv_cache=caches[1])
+            assert step.shape == (3, 1, 1024)
+            ops.assert_close_with_outliers(step, same, rtol=1e-2, atol=2e-2, max_outlier_fraction=0.01)
+            ops.assert_close_with_outliers(step, whole[:, pos:pos + 1], rtol=1e-2, atol=2e-2, max_outlier_fraction=0.01)
+
+
 def test_block_config4_full_size():
     """Benchmark config 4 at full size (batch 8 x seq 2048), all 16384 tokens: against the CPU
     oracle block, against the same block on torch's own GPU ops (bf16, and fp32 as the common

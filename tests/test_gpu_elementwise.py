@@ -154,7 +154,7 @@ def test_rope_config2b_full_size_and_position_slices():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("dims", [(2, 33, 8, 2, 64), (1, 128, 32, 8, 128), (3, 5, 3, 1, 6)])
+@pytest.mark.parametrize("dims", [(2, 33, 8, 2, 64), (1, 128, 32, 8, 128), (3, 5, 3, 1, 6), (16, 1, 32, 8, 128), (1, 1, 4, 2, 64)])
 def test_rope_strided_views_equal_packed_inputs(dims, dtype):
     """q and k as column ranges of one fused QKV buffer [tokens, (Hq + 2 Hkv) * D] give exactly
     what packed copies give (vector path and, for head_dim 6, the scalar path)."""
