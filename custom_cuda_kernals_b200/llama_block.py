@@ -123,6 +123,8 @@ def _continuation_attention(q, k, v, gqa: bool):
     device, an explicit boolean mask gives the same result (slower)."""
     global _LOWER_RIGHT_OK
     seq_q, seq_k = q.shape[-2], k.shape[-2]
+    if seq_q == 1:       # a single new position sees every key: no mask at all
+        return F.scaled_dot_product_attention(q, k, v, enable_gqa=gqa)
     if _LOWER_RIGHT_OK:
         try:
             from torch.nn.attention.bias import causal_lower_right
