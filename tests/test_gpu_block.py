@@ -146,6 +146,31 @@ def test_decode_sized_steps_through_a_kv_cache_match_the_whole_sequence():
             ops.assert_close_with_outliers(step, whole[:, pos:pos + 1], rtol=1e-2, atol=2e-2, max_outlier_fraction=0.01)
 
 
+def test_captured_block_replays_the_eager_result_on_new_inputs():
+    """``LlamaBlock.capture`` returns a CUDA-graph replay of the forward call: after new data is
+    copied into the staging input it gives, bit for bit, what the eager call gives - for a whole
+    sequence and for a decode-sized step against a KV cache."""
+    from custom_cuda_kernals_b200.llama_block import LlamaBlock
+    cfg = dict(workloads.LLAMA3_8B, hidden=1024, ffn=2816, n_heads=8, n_kv_heads=2, head_dim=128)
+    wd = {k: v.to(DEV) for k, v in workloads.block_weights(cfg).items()}
+    block = LlamaBlock(wd, 8, 2, cfg["eps"], cfg["theta"], max_seq_len=256)
+    x = workloads.block_input(2, 200, 1024).to(DEV)
+    stage = torch.zeros(2, 192, 1024, dtype=x.dtype, device=DEV)
+    replay = block.capture(stage)
+    with torch.no_grad():
+        for lo in (0, 8):
+            stage.copy_(x[:, lo:lo + 192])
+            assert torch.equal(replay(), block(x[:, lo:lo + 192].contiguous()))
+        cache = tuple(torch.zeros(2, 256, 2, 128, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+        block(x[:, :199].contiguous(), kv_cache=cache)
+        want = block(x[:, 199:200].contiguous(), pos_offset=199, kv_cache=cache)
+        token = torch.zeros(2, 1, 1024, dtype=x.dtype, device=DEV)
+        step = block.capture(token, pos_offset=199, kv_cache=cache)
+        token.copy_(x[:, 199:200])
+        assert torch.equal(step(), want)
+    assert device_status_clean(x)
+
+
 def test_block_config4_full_size():
     """Benchmark config 4 at full size (batch 8 x seq 2048), all 16384 tokens: against the CPU
     oracle block, against the same block on torch's own GPU ops (bf16, and fp32 as the common
