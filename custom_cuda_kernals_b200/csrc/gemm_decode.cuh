@@ -173,6 +173,13 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 const int q0 = static_cast<int>(rank) * kPlanes / static_cast<int>(splits);
                 const int q1 = (static_cast<int>(rank) + 1) * kPlanes / static_cast<int>(splits);
                 for (int q = q0; q < q1 && 4 * q < m; ++q) {
+                    const int64_t at = static_cast<int64_t>(4 * q) * n + feature;
+                    float res[4] = {0.0f, 0.0f, 0.0f, 0.0f};        // fetched first: they travel while the partials are summed
+                    if (residual != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (4 * q + j < m) res[j] = Store<T>::load1(residual + at + j * n);
+                    }
                     const uint32_t off = static_cast<uint32_t>((q * kBM + row_in_tile) * 16);
                     float4 sum = ld_cluster_f4(ptx::map_to_cta(base, 0) + off);
                     for (uint32_t r = 1; r < splits; ++r) {
@@ -182,11 +189,11 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                         sum.z += v.z;
                         sum.w += v.w;
                     }
-                    const int64_t at = static_cast<int64_t>(4 * q) * n + feature;
-                    put(at, sum.x);
-                    if (4 * q + 1 < m) put(at + n, sum.y);
-                    if (4 * q + 2 < m) put(at + 2 * n, sum.z);
-                    if (4 * q + 3 < m) put(at + 3 * n, sum.w);
+                    const float out[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (4 * q + j < m)
+                            Store<T>::store1(y + at + j * n, residual == nullptr ? out[j] + b : Store<T>::round(out[j] + b) + res[j]);
                 }
             }
         }
