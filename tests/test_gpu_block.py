@@ -146,6 +146,27 @@ def test_decode_sized_steps_through_a_kv_cache_match_the_whole_sequence():
             ops.assert_close_with_outliers(step, whole[:, pos:pos + 1], rtol=1e-2, atol=2e-2, max_outlier_fraction=0.01)
 
 
+def test_rope_in_the_qkv_epilogue_equals_the_rope_kernel_path():
+    """The block with RoPE in the QKV GEMM's epilogue (default for heads of 128), with the rope
+    kernel on the QKV buffer's column ranges (``rope_in_gemm=False``) and the unfused chain give the
+    same bits; heads of 64 take the rope-kernel path by themselves."""
+    from custom_cuda_kernals_b200.llama_block import LlamaBlock
+    cfg = dict(workloads.LLAMA3_8B, hidden=1024, ffn=2816, n_heads=8, n_kv_heads=2, head_dim=128)
+    wd = {k: v.to(DEV) for k, v in workloads.block_weights(cfg).items()}
+    x = workloads.block_input(2, 160, 1024).to(DEV)
+    with torch.no_grad():
+        a = LlamaBlock(wd, 8, 2, cfg["eps"], cfg["theta"], max_seq_len=256)
+        b = LlamaBlock(wd, 8, 2, cfg["eps"], cfg["theta"], max_seq_len=256, rope_in_gemm=False)
+        c = LlamaBlock(wd, 8, 2, cfg["eps"], cfg["theta"], max_seq_len=256, fused=False)
+        assert a.rope_in_gemm and not b.rope_in_gemm and a.launches_per_forward == 6 and b.launches_per_forward == 7
+        ya = a(x)
+        assert torch.equal(ya, b(x)) and torch.equal(ya, c(x))
+        d = LlamaBlock(wd, 16, 4, cfg["eps"], cfg["theta"], max_seq_len=256)          # the same weights read as heads of 64
+        e = LlamaBlock(wd, 16, 4, cfg["eps"], cfg["theta"], max_seq_len=256, fused=False)
+        assert not d.rope_in_gemm and torch.equal(d(x), e(x))
+    assert device_status_clean(x)
+
+
 def test_captured_block_replays_the_eager_result_on_new_inputs():
     """``LlamaBlock.capture`` returns a CUDA-graph replay of the forward call: after new data is
     copied into the staging input it gives, bit for bit, what the eager call gives - for a whole
